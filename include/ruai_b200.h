@@ -1,0 +1,212 @@
+/* ruai_b200 — C ABI of the B200 (sm_100a) quantized-inference path.
+ *
+ * This library stands behind the three quantized-matmul methods of ruai's
+ * `trait Backend` (src/nn/backend/mod.rs:675-704: matmul_int8, dequant_int4,
+ * matmul_int4), whose CUDA bodies are src/nn/backend/cuda.rs:788-833, and behind
+ * the model surface that drives them (`Linear::quantize_int8/int4`,
+ * src/nn/modules/layers.rs:112-165; `Llama` / `GPT2` `forward_cached`,
+ * `generate`, `quantize_int8/int4`, src/nn/modules/{llama,gpt2}.rs).
+ *
+ * Conventions
+ *  - every entry point returns an int status (RUAI_OK == 0).  The reference
+ *    panics on error (cuda.rs:256, ops.rs:694-699); a binding turns a non-zero
+ *    status plus ruai_last_error() into that panic.
+ *  - pointers named *_dev are device pointers on the context's GPU; pointers
+ *    named *_host are host pointers; plain names accept either (the library
+ *    asks the driver which it is).
+ *  - all work is issued on the context's stream and is asynchronous unless a
+ *    host buffer has to be filled.
+ *  - matrices are row-major.  Weights are `[in, out]` = `[k, n]` as in the
+ *    reference (`Linear::weight`, layers.rs:29).
+ *  - there is no CPU fallback: without a CUDA device every call that touches
+ *    data fails with RUAI_ERR_CUDA.
+ */
+#ifndef RUAI_B200_H
+#define RUAI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ruai_ctx ruai_ctx;         /* one per device: stream, scratch, error text */
+typedef struct ruai_qweight ruai_qweight; /* repacked quantized weight, device resident, immutable */
+typedef struct ruai_model ruai_model;     /* a Llama or GPT-2 with its KV cache */
+
+enum {
+  RUAI_OK = 0,
+  RUAI_ERR_SHAPE = 1,       /* the reference's shape / group asserts */
+  RUAI_ERR_CUDA = 2,        /* a CUDA call failed or no device / library */
+  RUAI_ERR_COMM = 3,        /* tensor-parallel exchange failed */
+  RUAI_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out */
+  RUAI_ERR_UNSUPPORTED = 5,
+  RUAI_ERR_ARG = 6
+};
+
+/* Activation dtypes; mirrors DType::{F32,F16,BF16} (mod.rs:32-44). */
+enum { RUAI_F32 = 0, RUAI_F16 = 1, RUAI_BF16 = 2 };
+
+/* ---- context ------------------------------------------------------------ */
+
+/* Replaces `cuda::backend(ordinal)` (cuda.rs:82-86, 262-281): one context and
+ * stream per device ordinal.  `stream_or_null` is a cudaStream_t to adopt. */
+int ruai_ctx_create(int ordinal, void* stream_or_null, ruai_ctx** out);
+int ruai_ctx_destroy(ruai_ctx* ctx);
+/* Text of the last failure on this context (or the last context-less failure
+ * when ctx is NULL).  Valid until the next failing call. */
+const char* ruai_last_error(const ruai_ctx* ctx);
+/* `Backend::synchronize` (cuda.rs:447-452). */
+int ruai_ctx_synchronize(ruai_ctx* ctx);
+/* `Device::is_available` (cuda.rs:73-79): number of CUDA devices, 0 if none. */
+int ruai_device_count(void);
+/* Library version string. */
+const char* ruai_version(void);
+
+/* Device memory for callers without their own allocator (cuda.rs:288-300). */
+int ruai_malloc(ruai_ctx* ctx, size_t bytes, void** out_dev);
+int ruai_free(ruai_ctx* ctx, void* ptr_dev);
+int ruai_memcpy_h2d(ruai_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int ruai_memcpy_d2h(ruai_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+
+/* Timing on the context's stream with CUDA events. */
+int ruai_timer_start(ruai_ctx* ctx);
+int ruai_timer_stop_ms(ruai_ctx* ctx, float* ms_out); /* records, synchronizes, returns elapsed */
+
+/* ---- quantizer (Linear::quantize_int8 / quantize_int4) --------------------
+ * Bit-exact with layers.rs:112-129 and layers.rs:139-165: f32 absmax, true
+ * division, round-half-away, clamp.  The reference runs these loops on the
+ * host after a device-to-host copy; here they run on the device.
+ *   int8: q[k,n] i8, scale[n] f32           (per output column)
+ *   int4: q[k/2,n] packed, scale[k/group,n] (low nibble = even row)          */
+int ruai_quantize_int8(ruai_ctx* ctx, const float* w_dev, uint32_t k, uint32_t n,
+                       int8_t* q_dev, float* scale_dev);
+int ruai_quantize_int4(ruai_ctx* ctx, const float* w_dev, uint32_t k, uint32_t n, uint32_t group,
+                       int8_t* q_dev, float* scale_dev);
+
+/* ---- repack: reference layout -> kernel layout ----------------------------
+ * Inputs are the reference's buffers `weight_int8`/`weight_scale` and
+ * `weight_int4`/`weight_int4_scale` (layers.rs:205-211), host or device.
+ * The kernel layout stores, for every output column j and every run c of 16
+ * bytes along k, one 16-byte chunk at ((c * n + j) * 16): a warp that owns 32
+ * neighbouring columns reads 512 contiguous bytes, and one chunk is 16 int8
+ * rows, or the 32 int4 rows of one scale group.  Scales keep the reference's
+ * values and order.  ruai_unpack() restores the reference bytes exactly.     */
+int ruai_repack_int8(ruai_ctx* ctx, const int8_t* q, const float* scale, uint32_t k, uint32_t n,
+                     ruai_qweight** out);
+int ruai_repack_int4(ruai_ctx* ctx, const int8_t* q, const float* scale, uint32_t k, uint32_t n,
+                     uint32_t group, ruai_qweight** out);
+int ruai_unpack(ruai_ctx* ctx, const ruai_qweight* w, int8_t* q_out, float* scale_out);
+int ruai_qweight_free(ruai_qweight* w);
+/* k, n, bits (8 or 4), group (0 for int8). */
+int ruai_qweight_info(const ruai_qweight* w, uint32_t* k, uint32_t* n, uint32_t* bits, uint32_t* group);
+
+/* ---- Backend-trait equivalents -------------------------------------------- */
+
+/* `Backend::matmul_int8` / `matmul_int4` (mod.rs:675-682, 700-704; CPU
+ * definition cpu.rs:897-927, 1035-1067) followed by `Linear::forward`'s bias
+ * add (layers.rs:184-189).  x_dev is [m,k] in x_dtype, out_dev is [m,n] in
+ * x_dtype, bias_dev_or_null is f32 [n].  Arithmetic is f32.                 */
+int ruai_matmul_q(ruai_ctx* ctx, int x_dtype, const void* x_dev, const ruai_qweight* w,
+                  const float* bias_dev_or_null, void* out_dev, uint32_t m);
+/* `Backend::dequant_int4` (mod.rs:689-693, cpu.rs:1023-1033): exact f32 [k,n]. */
+int ruai_dequant_int4(ruai_ctx* ctx, const ruai_qweight* w, float* out_dev);
+/* Same on reference-layout device buffers, without a repack (any even group). */
+int ruai_dequant_int4_ref(ruai_ctx* ctx, const int8_t* q_dev, const float* scale_dev,
+                          uint32_t k, uint32_t n, uint32_t group, float* out_dev);
+
+/* ---- models ---------------------------------------------------------------- */
+
+/* Field names follow `LlamaConfig` (llama.rs:48-75). */
+typedef struct {
+  uint32_t vocab_size, hidden_size, intermediate_size, num_hidden_layers;
+  uint32_t num_attention_heads, num_key_value_heads, head_dim, max_position_embeddings;
+  float rms_norm_eps, rope_theta;
+  uint32_t tie_word_embeddings;
+} ruai_llama_config;
+
+/* Field names follow `GPT2Config` (gpt2.rs:30-44). */
+typedef struct {
+  uint32_t vocab_size, n_positions, n_embd, n_layer, n_head;
+} ruai_gpt2_config;
+
+/* Tensor-parallel placement of one model replica: this process owns rank
+ * `rank` of `world` (1 = no sharding).  Column-split q/k/v/gate/up and the
+ * head, row-split o/down, one sum exchange after o_proj and down_proj.      */
+typedef struct {
+  uint32_t rank, world;
+} ruai_tp;
+
+int ruai_llama_create(ruai_ctx* ctx, const ruai_llama_config* cfg, const ruai_tp* tp_or_null,
+                      ruai_model** out);
+int ruai_gpt2_create(ruai_ctx* ctx, const ruai_gpt2_config* cfg, ruai_model** out);
+int ruai_model_destroy(ruai_model* m);
+
+/* Fill the model with the seeded synthetic weights of include/ruai_b200_synth.h
+ * (N(0, 0.02^2) matrices and GPT-2 biases, unit norm gains), generated in f32
+ * on the device, then quantized exactly as `Llama::quantize_int8` /
+ * `quantize_int4(group)` (llama.rs:522-554, gpt2.rs:306-335) do: every block
+ * Linear to `bits`, the output head to int8, embeddings left in f32.        */
+int ruai_model_load_synthetic(ruai_model* m, uint64_t seed, uint32_t bits, uint32_t group);
+
+/* Set one f32 tensor from host memory before quantizing (ids: ruai_b200_synth.h,
+ * plus RUAI_TN_* below for norm parameters). `count` must match the shape.  */
+#define RUAI_TN_FINAL_NORM   0x40000000ull /* Llama `norm.weight` / GPT-2 `ln_f.weight` */
+#define RUAI_TN_FINAL_NORM_B 0x40000001ull /* GPT-2 `ln_f.bias` */
+#define RUAI_TN_LAYER_NORM1  0x50000000ull /* + layer: input_layernorm / ln_1 weight */
+#define RUAI_TN_LAYER_NORM1B 0x51000000ull /* + layer: ln_1 bias */
+#define RUAI_TN_LAYER_NORM2  0x52000000ull /* + layer: post_attention_layernorm / ln_2 weight */
+#define RUAI_TN_LAYER_NORM2B 0x53000000ull /* + layer: ln_2 bias */
+int ruai_model_set_f32(ruai_model* m, uint64_t tensor_id, const float* data_host, size_t count);
+/* `Llama::quantize_int8` / `quantize_int4(group)` over the f32 tensors set so far. */
+int ruai_model_quantize(ruai_model* m, uint32_t bits, uint32_t group);
+/* Read back one block Linear (or the head, tensor id RUAI_T_LMHEAD) in the
+ * reference's buffer layout — what `state_dict()` would hold (layers.rs:205-211). */
+int ruai_model_get_linear(ruai_model* m, uint64_t tensor_id, int8_t* q_host, float* scale_host);
+
+/* `forward_cached` (llama.rs:434-463, gpt2.rs:214-241): logits for the new
+ * tokens `ids_host` [B,T] after the cached positions; the cache is extended.
+ * logits_host_or_null receives [B,V] (last position) or, with all_positions,
+ * [B,T,V].  The batch size is fixed by the first call after a cache reset.  */
+int ruai_model_forward_cached(ruai_model* m, const int32_t* ids_host, uint32_t B, uint32_t T,
+                              float* logits_host_or_null, int all_positions);
+/* `KvCache::clear` (transformer.rs:160-165) and `KvCache::len`. */
+int ruai_model_cache_clear(ruai_model* m);
+int ruai_model_cache_len(const ruai_model* m, uint32_t* len, uint32_t* capacity);
+
+/* `generate` with `Sampler::greedy()` (generation.rs:83-113, llama.rs:467-477):
+ * batch 1, argmax with the last-maximum tie rule, sliding window past the
+ * maximum context.  out_ids_host receives T + n_new ids (prompt first).     */
+int ruai_model_generate(ruai_model* m, const int32_t* prompt_host, uint32_t T, uint32_t n_new,
+                        int32_t* out_ids_host);
+
+/* One decode step that never leaves the device: the ids are read from
+ * ids_dev_or_null [B] (NULL: the argmax of the previous step), the argmax of
+ * the new logits is left on the device and, if next_ids_host_or_null is given,
+ * copied out.  Batched greedy decode for B independent sequences.           */
+int ruai_model_decode_step(ruai_model* m, const int32_t* ids_dev_or_null, uint32_t B,
+                           int32_t* next_ids_host_or_null);
+/* Pretend `len` positions are cached for batch B (contents: whatever the
+ * buffers hold, zero-filled when fresh); used to time decode at a given
+ * context length without running the prompt. */
+int ruai_model_cache_assume(ruai_model* m, uint32_t B, uint32_t len);
+/* Algorithmic bytes of one decode step at batch B with `len` cached positions:
+ * packed weights + scales + head + norm/bias parameters + B * (embedding row +
+ * KV read + KV write). */
+int ruai_model_step_bytes(const ruai_model* m, uint32_t B, uint32_t len, double* bytes);
+/* Kernels launched by one decode step (for launch accounting). */
+int ruai_model_step_launches(const ruai_model* m, uint32_t* launches);
+
+/* ---- tensor parallel -------------------------------------------------------
+ * The exchange buffers of every rank are mapped into every other rank through
+ * CUDA IPC handles that the caller carries between processes (any transport:
+ * torch.distributed object gather, a file, MPI).                            */
+#define RUAI_IPC_HANDLE_BYTES 64
+int ruai_tp_export(ruai_model* m, void* handle_out /* RUAI_IPC_HANDLE_BYTES */);
+int ruai_tp_connect(ruai_model* m, const void* handles /* world * RUAI_IPC_HANDLE_BYTES */);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RUAI_B200_H */
