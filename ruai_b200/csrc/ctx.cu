@@ -1,0 +1,148 @@
+// Context, device memory and timing entry points.
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+thread_local std::string g_ruai_global_err;
+
+int ruai_fail(ruai_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  g_ruai_global_err = buf;
+  return code;
+}
+
+RUAI_API const char* ruai_version(void) { return "ruai_b200 0.1 (sm_100a)"; }
+
+RUAI_API int ruai_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+RUAI_API const char* ruai_last_error(const ruai_ctx* ctx) { return ctx ? ctx->err.c_str() : g_ruai_global_err.c_str(); }
+
+RUAI_API int ruai_ctx_create(int ordinal, void* stream_or_null, ruai_ctx** out) {
+  if (!out) return ruai_fail(nullptr, RUAI_ERR_ARG, "ruai_ctx_create: out is NULL");
+  *out = nullptr;
+  int n = ruai_device_count();
+  if (n <= 0) return ruai_fail(nullptr, RUAI_ERR_CUDA, "no CUDA device: this library has no CPU fallback");
+  if (ordinal < 0 || ordinal >= n) return ruai_fail(nullptr, RUAI_ERR_ARG, "device ordinal %d out of range (%d devices)", ordinal, n);
+  RUAI_CUDA(nullptr, cudaSetDevice(ordinal));
+  cudaDeviceProp prop;
+  RUAI_CUDA(nullptr, cudaGetDeviceProperties(&prop, ordinal));
+  if (prop.major != 10)
+    return ruai_fail(nullptr, RUAI_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", ordinal, prop.major, prop.minor);
+  ruai_ctx* c = new ruai_ctx();
+  c->ordinal = ordinal;
+  c->sm_count = prop.multiProcessorCount;
+  if (stream_or_null) c->stream = (cudaStream_t)stream_or_null;
+  else {
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete c; return ruai_fail(nullptr, RUAI_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    c->own_stream = true;
+  }
+  cudaEventCreate(&c->ev0);
+  cudaEventCreate(&c->ev1);
+  const char* pdl = getenv("RUAI_B200_PDL");
+  if (pdl && pdl[0] == '0') c->use_pdl = false;
+  int rc = ruai_ctx_reserve(c, 8u << 20, 4096);
+  if (rc != RUAI_OK) { g_ruai_global_err = c->err; delete c; return rc; }
+  *out = c;
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_ctx_destroy(ruai_ctx* c) {
+  if (!c) return RUAI_OK;
+  DeviceGuard g(c->ordinal);
+  cudaStreamSynchronize(c->stream);
+  cudaFree(c->partial);
+  cudaFree(c->counters);
+  cudaEventDestroy(c->ev0);
+  cudaEventDestroy(c->ev1);
+  if (c->own_stream) cudaStreamDestroy(c->stream);
+  delete c;
+  return RUAI_OK;
+}
+
+int ruai_ctx_reserve(ruai_ctx* c, size_t partial_bytes, size_t counters) {
+  DeviceGuard g(c->ordinal);
+  if (partial_bytes > c->partial_bytes) {
+    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->partial) cudaFree(c->partial);
+    c->partial = nullptr;
+    c->partial_bytes = 0;
+    RUAI_CUDA(c, cudaMalloc(&c->partial, partial_bytes));
+    c->partial_bytes = partial_bytes;
+  }
+  if (counters > c->counters_n) {
+    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->counters) cudaFree(c->counters);
+    c->counters = nullptr;
+    c->counters_n = 0;
+    RUAI_CUDA(c, cudaMalloc(&c->counters, counters * sizeof(unsigned)));
+    RUAI_CUDA(c, cudaMemset(c->counters, 0, counters * sizeof(unsigned)));
+    c->counters_n = counters;
+  }
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_ctx_synchronize(ruai_ctx* c) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_malloc(ruai_ctx* c, size_t bytes, void** out) {
+  if (!c || !out) return ruai_fail(c, RUAI_ERR_ARG, "ruai_malloc: NULL argument");
+  DeviceGuard g(c->ordinal);
+  *out = nullptr;
+  RUAI_CUDA(c, cudaMalloc(out, bytes ? bytes : 1));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_free(ruai_ctx* c, void* p) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  DeviceGuard g(c->ordinal);
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  RUAI_CUDA(c, cudaFree(p));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_memcpy_h2d(ruai_ctx* c, void* dst, const void* src, size_t bytes) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  DeviceGuard g(c->ordinal);
+  RUAI_CUDA(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_memcpy_d2h(ruai_ctx* c, void* dst, const void* src, size_t bytes) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  DeviceGuard g(c->ordinal);
+  RUAI_CUDA(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_timer_start(ruai_ctx* c) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  RUAI_CUDA(c, cudaEventRecord(c->ev0, c->stream));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_timer_stop_ms(ruai_ctx* c, float* ms) {
+  if (!c || !ms) return ruai_fail(c, RUAI_ERR_ARG, "NULL argument");
+  RUAI_CUDA(c, cudaEventRecord(c->ev1, c->stream));
+  RUAI_CUDA(c, cudaEventSynchronize(c->ev1));
+  RUAI_CUDA(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
+  return RUAI_OK;
+}

@@ -1,0 +1,241 @@
+"""Host-side mirror of the `ruai::nn` surface the quantized path goes through.
+
+Same names, argument meaning and error behaviour as the reference:
+`Device::Cuda(i)` (device.rs), `Tensor` as an immutable device buffer
+(tensor.rs), `Linear::quantize_int8 / quantize_int4 / forward / dims /
+state_dict` (layers.rs:24-212), `Tensor::matmul_int8 / matmul_int4`
+(ops.rs:689-735) and the `Llama` / `GPT2` inference methods (llama.rs,
+gpt2.rs).  Every computation is a call into libruai_b200.so through its C ABI;
+nothing here computes on the host.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import F32, F16, BF16, GPT2Config, LlamaConfig, RuaiError, TP  # noqa: F401
+
+_NP_OF = {F32: np.float32, F16: np.float16, BF16: np.uint16}  # bf16 travels as raw 16-bit words
+
+
+class Device:
+    """`Device::Cuda(ordinal)`; owns one library context (stream + scratch) like cuda.rs:82-86."""
+    _by_ordinal = {}
+
+    def __init__(self, ordinal=0):
+        self.ordinal = ordinal
+        self.L = _lib.load()
+        h = C.c_void_p()
+        _lib.check(self.L.ruai_ctx_create(ordinal, None, C.byref(h)))
+        self.ctx = h
+
+    @classmethod
+    def cuda(cls, ordinal=0):
+        if ordinal not in cls._by_ordinal:
+            cls._by_ordinal[ordinal] = cls(ordinal)
+        return cls._by_ordinal[ordinal]
+
+    @staticmethod
+    def is_available():
+        """`Device::is_available` (cuda.rs:73-79)."""
+        return _lib.load().ruai_device_count() > 0
+
+    def check(self, rc):
+        _lib.check(rc, self.ctx)
+
+    def synchronize(self):
+        self.check(self.L.ruai_ctx_synchronize(self.ctx))
+
+    def timer_start(self):
+        self.check(self.L.ruai_timer_start(self.ctx))
+
+    def timer_stop_ms(self):
+        ms = C.c_float()
+        self.check(self.L.ruai_timer_stop_ms(self.ctx, C.byref(ms)))
+        return ms.value
+
+
+class Tensor:
+    """A contiguous row-major device buffer with a shape and a dtype (F32 / F16 / BF16 / int8 / int32)."""
+
+    def __init__(self, dev, shape, np_dtype, rdtype=None):
+        self.dev, self.shape, self.np_dtype, self.rdtype = dev, tuple(int(s) for s in shape), np.dtype(np_dtype), rdtype
+        self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.np_dtype.itemsize
+        p = C.c_void_p()
+        dev.check(dev.L.ruai_malloc(dev.ctx, self.nbytes, C.byref(p)))
+        self.ptr = p
+
+    @classmethod
+    def from_numpy(cls, dev, a, rdtype=None):
+        a = np.ascontiguousarray(a)
+        if rdtype is None and a.dtype == np.float32:
+            rdtype = F32
+        if rdtype is None and a.dtype == np.float16:
+            rdtype = F16
+        t = cls(dev, a.shape, a.dtype, rdtype)
+        if t.nbytes:
+            dev.check(dev.L.ruai_memcpy_h2d(dev.ctx, t.ptr, a.ctypes.data_as(C.c_void_p), t.nbytes))
+        return t
+
+    def numpy(self):
+        a = np.empty(self.shape, self.np_dtype)
+        if self.nbytes:
+            self.dev.check(self.dev.L.ruai_memcpy_d2h(self.dev.ctx, a.ctypes.data_as(C.c_void_p), self.ptr, self.nbytes))
+        return a
+
+    def free(self):
+        if self.ptr:
+            self.dev.L.ruai_free(self.dev.ctx, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    # ops.rs:693-710
+    def matmul_int8(self, q, scales):
+        return _matmul_q(self, QWeight.int8(self.dev, q, scales))
+
+    # ops.rs:716-735
+    def matmul_int4(self, q, scales):
+        k = 2 * q.shape[0]
+        if scales.ndim != 2 or q.ndim != 2:
+            raise ValueError("matmul_int4: q must be [k/2, n] and scales [k/group, n]")
+        if scales.shape[0] == 0 or k % scales.shape[0]:
+            raise ValueError(f"matmul_int4: {scales.shape[0]} scale rows do not divide k = {k}")
+        return _matmul_q(self, QWeight.int4(self.dev, q, scales, k // scales.shape[0]))
+
+
+class QWeight:
+    """A repacked quantized weight (`ruai_qweight`), built once from the reference-layout buffers."""
+
+    def __init__(self, dev, handle, k, n, bits, group):
+        self.dev, self.h, self.k, self.n, self.bits, self.group = dev, handle, k, n, bits, group
+
+    @classmethod
+    def int8(cls, dev, q, scale):
+        q, scale = np.ascontiguousarray(q, np.int8), np.ascontiguousarray(scale, np.float32)
+        if q.ndim != 2:
+            raise ValueError("matmul_int8: weights must be [k, n]")
+        k, n = q.shape
+        if scale.shape != (n,):
+            raise ValueError("matmul_int8: scales must be [n]")
+        h = C.c_void_p()
+        dev.check(dev.L.ruai_repack_int8(dev.ctx, q.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p), k, n, C.byref(h)))
+        return cls(dev, h, k, n, 8, 0)
+
+    @classmethod
+    def int4(cls, dev, q, scale, group):
+        q, scale = np.ascontiguousarray(q, np.int8), np.ascontiguousarray(scale, np.float32)
+        k, n = 2 * q.shape[0], q.shape[1]
+        if scale.shape[1] != n:
+            raise ValueError(f"matmul_int4: scales must have {n} columns")
+        h = C.c_void_p()
+        dev.check(dev.L.ruai_repack_int4(dev.ctx, q.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p), k, n, group, C.byref(h)))
+        return cls(dev, h, k, n, 4, group)
+
+    def unpack(self):
+        """The reference-layout buffers back, byte for byte."""
+        q = np.empty((self.k if self.bits == 8 else self.k // 2, self.n), np.int8)
+        s = np.empty((self.n,) if self.bits == 8 else (self.k // self.group, self.n), np.float32)
+        self.dev.check(self.dev.L.ruai_unpack(self.dev.ctx, self.h, q.ctypes.data_as(C.c_void_p), s.ctypes.data_as(C.c_void_p)))
+        return q, s
+
+    def dequant(self):
+        """`Backend::dequant_int4` (mod.rs:689-693)."""
+        out = Tensor(self.dev, (self.k, self.n), np.float32, F32)
+        self.dev.check(self.dev.L.ruai_dequant_int4(self.dev.ctx, self.h, out.ptr))
+        return out.numpy()
+
+    def free(self):
+        if self.h:
+            self.dev.L.ruai_qweight_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _matmul_q(x, w, bias=None):
+    if x.rdtype not in (F32, F16, BF16):
+        raise TypeError("matmul_int8/int4: activations must be a float tensor")
+    if x.shape[-1] != w.k:
+        raise ValueError(f"inner dims differ ({x.shape} @ int{w.bits} [{w.k}, {w.n}])")
+    m = int(np.prod(x.shape[:-1], dtype=np.int64))
+    out = Tensor(x.dev, x.shape[:-1] + (w.n,), x.np_dtype, x.rdtype)
+    x.dev.check(x.dev.L.ruai_matmul_q(x.dev.ctx, x.rdtype, x.ptr, w.h, bias.ptr if bias is not None else None, out.ptr, m))
+    return out
+
+
+def quantize_int8_device(dev, w):
+    """`Linear::quantize_int8`'s loops (layers.rs:112-129) run on the device; returns numpy (q, scale)."""
+    w = np.ascontiguousarray(w, np.float32)
+    k, n = w.shape
+    wt = Tensor.from_numpy(dev, w)
+    q, s = Tensor(dev, (k, n), np.int8), Tensor(dev, (n,), np.float32, F32)
+    dev.check(dev.L.ruai_quantize_int8(dev.ctx, wt.ptr, k, n, q.ptr, s.ptr))
+    return q.numpy(), s.numpy()
+
+
+def quantize_int4_device(dev, w, group):
+    """`Linear::quantize_int4` (layers.rs:139-165) on the device; returns numpy (packed, scale)."""
+    w = np.ascontiguousarray(w, np.float32)
+    k, n = w.shape
+    if not (group >= 2 and group % 2 == 0 and k % group == 0):
+        raise ValueError(f"int4 group {group} must be even and divide in_features {k}")
+    wt = Tensor.from_numpy(dev, w)
+    q, s = Tensor(dev, (k // 2, n), np.int8), Tensor(dev, (k // group, n), np.float32, F32)
+    dev.check(dev.L.ruai_quantize_int4(dev.ctx, wt.ptr, k, n, group, q.ptr, s.ptr))
+    return q.numpy(), s.numpy()
+
+
+class Linear:
+    """`Linear` (layers.rs:24-212): y = x @ W + b with W [in, out]; inference-only quantized forms."""
+
+    def __init__(self, dev, weight, bias=None):
+        self.dev = dev
+        self.weight = np.ascontiguousarray(weight, np.float32)
+        self.bias = None if bias is None else Tensor.from_numpy(dev, np.ascontiguousarray(bias, np.float32))
+        self.int8 = self.int4 = None
+        self._q = None
+
+    def is_quantized(self):
+        return self._q is not None
+
+    def dims(self):
+        return (self._q.k, self._q.n) if self._q else self.weight.shape
+
+    def quantize_int8(self):
+        if self.is_quantized():
+            return
+        q, s = quantize_int8_device(self.dev, self.weight)
+        self.int8, self._q = (q, s), QWeight.int8(self.dev, q, s)
+        self.weight = np.zeros((0,), np.float32)
+
+    def quantize_int4(self, group):
+        if self.is_quantized():
+            return
+        q, s = quantize_int4_device(self.dev, self.weight, group)
+        self.int4, self._q = (q, s), QWeight.int4(self.dev, q, s, group)
+        self.weight = np.zeros((0,), np.float32)
+
+    def forward(self, x):
+        if not self.is_quantized():
+            raise RuaiError(_lib.ERR_UNSUPPORTED, "only the quantized Linear is implemented on this path")
+        return _matmul_q(x, self._q, self.bias)
+
+    def state_dict(self):
+        """Buffer names of layers.rs:205-211."""
+        d = {}
+        if self.bias is not None:
+            d["bias"] = self.bias.numpy()
+        if self.int8:
+            d["weight_int8"], d["weight_scale"] = self.int8
+        if self.int4:
+            d["weight_int4"], d["weight_int4_scale"] = self.int4
+        return d
