@@ -256,7 +256,14 @@ class Model:
             raise RuntimeError(f"oracle generate failed ({rc})")
         return (out, tr) if trace else out
 
-    def get_linear(self, tensor_id):
+    def get_linear(self, tensor_id, bits, group=32):
+        """(q, scale) of one Linear in the reference's buffer layout; tensor ids as in ruai_b200_synth.h."""
         k, n = u32(), u32()
-        lib().orc_model_get_linear(self.h, tensor_id, None, None, C.byref(k), C.byref(n))
-        return k.value, n.value
+        rc = lib().orc_model_get_linear(self.h, tensor_id, None, None, C.byref(k), C.byref(n))
+        if rc:
+            raise KeyError(tensor_id)
+        k, n = k.value, n.value
+        q = np.empty((k if bits == 8 else k // 2, n), np.int8)
+        s = np.empty((n,) if bits == 8 else (k // group, n), np.float32)
+        lib().orc_model_get_linear(self.h, tensor_id, q.ctypes.data_as(C.c_void_p), s.ctypes.data_as(C.c_void_p), None, None)
+        return q, s

@@ -236,18 +236,26 @@ __global__ void gemv_int4_reference_layout_kernel(const int8_t* __restrict__ q, 
                                                   uint32_t x_ld, uint32_t m, uint32_t k, uint32_t n, uint32_t group, void* out,
                                                   GemvEpilogue e) {
   grid_dependency_wait();
-  const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
+  const bool glu = e.act == ACT_SWIGLU;
+  const uint32_t j = glu ? 2 * t : t;
   if (j >= n || i >= m) return;
-  float acc = 0.0f;
-  for (uint32_t g = 0; g < k / group; ++g) {
-    float part = 0.0f;
-    for (uint32_t l = g * group; l < (g + 1) * group; ++l)
-      part = fmaf(load_as_f32(x, x_dtype, (size_t)i * x_ld + l), (float)int4_of((uint8_t)q[(size_t)(l / 2) * n + j], l & 1), part);
-    acc = fmaf(part, scale[(size_t)g * n + j], acc);
-  }
-  if (e.bias) acc += e.bias[j];
-  if (e.act == ACT_GELU) acc = gelu_ref(acc);
-  const size_t o = (size_t)i * e.out_ld + j;
+  auto column = [&](uint32_t col) {
+    float acc = 0.0f;
+    for (uint32_t g = 0; g < k / group; ++g) {
+      float part = 0.0f;
+      for (uint32_t l = g * group; l < (g + 1) * group; ++l)
+        part = fmaf(load_as_f32(x, x_dtype, (size_t)i * x_ld + l), (float)int4_of((uint8_t)q[(size_t)(l / 2) * n + col], l & 1), part);
+      acc = fmaf(part, scale[(size_t)g * n + col], acc);
+    }
+    return e.bias ? acc + e.bias[col] : acc;
+  };
+  float acc = column(j);
+  size_t o = (size_t)i * e.out_ld + j;
+  if (glu) {
+    acc = silu_ref(acc) * column(j + 1);
+    o = (size_t)i * e.out_ld + t;
+  } else if (e.act == ACT_GELU) acc = gelu_ref(acc);
   if (e.resid) acc = e.resid[o] + acc;
   store_from_f32(out, e.out_dtype, o, acc);
 }
@@ -277,7 +285,6 @@ int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dt
   if (epi.act == ACT_SWIGLU && (w->n & 1)) return ruai_fail(c, RUAI_ERR_SHAPE, "SwiGLU epilogue needs an even column count, got %u", w->n);
   if (epi.out_ld == 0) epi.out_ld = epi.act == ACT_SWIGLU ? w->n / 2 : w->n;
   if (w->layout == QL_REFERENCE) {
-    if (epi.act == ACT_SWIGLU) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "SwiGLU epilogue on a reference-layout weight");
     if (m > 65535) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "m too large");
     RUAI_CUDA(c, ruai_launch(c, gemv_int4_reference_layout_kernel, dim3((w->n + 127) / 128, m), dim3(128), 0, true, (const int8_t*)w->data,
                              (const float*)w->scale, x, x_dtype, x_ld, m, w->k, w->n, w->group, out, epi));

@@ -239,3 +239,120 @@ class Linear:
         if self.int4:
             d["weight_int4"], d["weight_int4_scale"] = self.int4
         return d
+
+
+class _Model:
+    """Shared inference surface of `Llama` and `GPT2`: quantize, forward_cached, generate."""
+
+    def __init__(self, dev, handle, cfg):
+        self.dev, self.h, self.config = dev, handle, cfg
+        self.vocab = cfg.vocab_size
+
+    def close(self):
+        if self.h:
+            self.dev.L.ruai_model_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load_synthetic(self, seed=0, bits=8, group=32):
+        """Seeded N(0, 0.02^2) weights generated and quantized on the device (see include/ruai_b200_synth.h)."""
+        self.dev.check(self.dev.L.ruai_model_load_synthetic(self.h, seed, bits, group if bits == 4 else 0))
+
+    def set_f32(self, tensor_id, a):
+        a = np.ascontiguousarray(a, np.float32)
+        self.dev.check(self.dev.L.ruai_model_set_f32(self.h, tensor_id, a.ctypes.data_as(C.c_void_p), a.size))
+
+    def quantize_int8(self):
+        """`Llama::quantize_int8` (llama.rs:522-531) / `GPT2::quantize_int8` (gpt2.rs:306-315)."""
+        self.dev.check(self.dev.L.ruai_model_quantize(self.h, 8, 0))
+
+    def quantize_int4(self, group):
+        """`Llama::quantize_int4(group)` (llama.rs:533-542): block Linears int4, head int8."""
+        self.dev.check(self.dev.L.ruai_model_quantize(self.h, 4, group))
+
+    def get_linear(self, tensor_id, k, n, bits, group=32):
+        """One quantized Linear in the reference's buffer layout (`weight_int8`/`weight_scale`, ...)."""
+        q = np.empty((k if bits == 8 else k // 2, n), np.int8)
+        s = np.empty((n,) if bits == 8 else (k // group, n), np.float32)
+        self.dev.check(self.dev.L.ruai_model_get_linear(self.h, tensor_id, q.ctypes.data_as(C.c_void_p), s.ctypes.data_as(C.c_void_p)))
+        return q, s
+
+    def forward_cached(self, ids, all_positions=False, want_logits=True):
+        """`forward_cached` (llama.rs:434-463, gpt2.rs:214-241): ids [B,T] -> logits [B,V] (last) or [B,T,V]."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        B, T = ids.shape
+        out = np.empty((B, T, self.vocab) if all_positions else (B, self.vocab), np.float32) if want_logits else None
+        self.dev.check(self.dev.L.ruai_model_forward_cached(self.h, ids.ctypes.data_as(C.c_void_p), B, T,
+                                                           out.ctypes.data_as(C.c_void_p) if want_logits else None, int(all_positions)))
+        return out
+
+    def cache_clear(self):
+        self.dev.check(self.dev.L.ruai_model_cache_clear(self.h))
+
+    def cache_len(self):
+        a, b = C.c_uint32(), C.c_uint32()
+        self.dev.check(self.dev.L.ruai_model_cache_len(self.h, C.byref(a), C.byref(b)))
+        return a.value
+
+    def cache_capacity(self):
+        a, b = C.c_uint32(), C.c_uint32()
+        self.dev.check(self.dev.L.ruai_model_cache_len(self.h, C.byref(a), C.byref(b)))
+        return b.value
+
+    def generate(self, prompt, n):
+        """Greedy `generate` (generation.rs:83-113): prompt followed by n new ids."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.empty(prompt.size + n, np.int32)
+        self.dev.check(self.dev.L.ruai_model_generate(self.h, prompt.ctypes.data_as(C.c_void_p), prompt.size, n, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def decode_step(self, B, ids_dev=None, fetch=True):
+        """One greedy step for B sequences that stays on the device; returns the next ids if fetch."""
+        out = np.empty(B, np.int32) if fetch else None
+        self.dev.check(self.dev.L.ruai_model_decode_step(self.h, ids_dev, B, out.ctypes.data_as(C.c_void_p) if fetch else None))
+        return out
+
+    def cache_assume(self, B, length):
+        self.dev.check(self.dev.L.ruai_model_cache_assume(self.h, B, length))
+
+    def step_bytes(self, B, length):
+        v = C.c_double()
+        self.dev.check(self.dev.L.ruai_model_step_bytes(self.h, B, length, C.byref(v)))
+        return v.value
+
+    def step_launches(self):
+        v = C.c_uint32()
+        self.dev.check(self.dev.L.ruai_model_step_launches(self.h, C.byref(v)))
+        return v.value
+
+    def tp_export(self):
+        buf = C.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        self.dev.check(self.dev.L.ruai_tp_export(self.h, buf))
+        return bytes(buf.raw)
+
+    def tp_connect(self, handles):
+        blob = b"".join(handles)
+        self.dev.check(self.dev.L.ruai_tp_connect(self.h, blob))
+
+
+class Llama(_Model):
+    """`Llama` (llama.rs): RMSNorm + RoPE + GQA + SwiGLU decoder, inference methods only."""
+
+    def __init__(self, dev, cfg, tp=None):
+        h = C.c_void_p()
+        dev.check(dev.L.ruai_llama_create(dev.ctx, C.byref(cfg), C.byref(tp) if tp is not None else None, C.byref(h)))
+        super().__init__(dev, h, cfg)
+
+
+class GPT2(_Model):
+    """`GPT2` (gpt2.rs): LayerNorm + learned positions + GELU decoder, inference methods only."""
+
+    def __init__(self, dev, cfg):
+        h = C.c_void_p()
+        dev.check(dev.L.ruai_gpt2_create(dev.ctx, C.byref(cfg), C.byref(h)))
+        super().__init__(dev, h, cfg)

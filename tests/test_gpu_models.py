@@ -1,0 +1,238 @@
+"""GPU parity of the model-level C ABI (Llama / GPT-2 forward_cached, generate, decode_step) against the CPU checker.
+
+Tolerance on logits is the one the task states for this path: max-abs 1e-2 and relative 1e-3
+(relative to the largest |logit| of the row set), with identical greedy tokens for at least the
+first 32 generated tokens.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from ruai_b200 import nn
+
+pytestmark = pytest.mark.gpu
+
+TOL_ABS, TOL_REL = 1e-2, 1e-3
+T_LMHEAD = 0x10000001
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert nn.Device.is_available(), "these tests need a CUDA device"
+    return nn.Device.cuda(0)
+
+
+def close(want, got, what=""):
+    want, got = np.asarray(want, np.float64), np.asarray(got, np.float64)
+    assert want.shape == got.shape
+    err = np.abs(want - got).max()
+    assert err <= TOL_ABS and err <= TOL_REL * max(np.abs(want).max(), 1e-6), f"{what}: max-abs {err}, scale {np.abs(want).max()}"
+    return err
+
+
+def llama_cfg(V, d, ffn, L, H, KV, hd, max_pos, theta=10000.0, tied=False):
+    return (oracle.LlamaConfig(V, d, ffn, L, H, KV, hd, max_pos, 1e-5, theta, int(tied)),
+            nn.LlamaConfig(V, d, ffn, L, H, KV, hd, max_pos, 1e-5, theta, int(tied)))
+
+
+def gpt2_cfg(V, n_pos, d, L, H):
+    return oracle.GPT2Config(V, n_pos, d, L, H), nn.GPT2Config(V, n_pos, d, L, H)
+
+
+def build(dev, cfgs, seed, bits, group=32):
+    oc, gc = cfgs
+    om = oracle.Model(oc, seed=seed, bits=bits, group=group)
+    gm = nn.Llama(dev, gc) if isinstance(gc, nn.LlamaConfig) else nn.GPT2(dev, gc)
+    gm.load_synthetic(seed, bits, group)
+    return om, gm
+
+
+TINY_LLAMA = dict(V=41, d=32, ffn=96, L=2, H=4, KV=2, hd=8, max_pos=160)
+
+
+@pytest.mark.parametrize("bits,group", [(8, 0), (4, 32), (4, 16)])
+def test_tiny_llama_weights_are_bit_exact(dev, bits, group):
+    om, gm = build(dev, llama_cfg(**TINY_LLAMA), 1, bits, group)
+    c = TINY_LLAMA
+    shapes = {0: (c["d"], c["H"] * c["hd"]), 1: (c["d"], c["KV"] * c["hd"]), 2: (c["d"], c["KV"] * c["hd"]), 3: (c["H"] * c["hd"], c["d"]),
+              4: (c["d"], c["ffn"]), 5: (c["d"], c["ffn"]), 6: (c["ffn"], c["d"])}
+    for layer in range(c["L"]):
+        for kind, (k, n) in shapes.items():
+            q, s = gm.get_linear(layer * 16 + kind, k, n, bits, group)
+            qo, so = om.get_linear(layer * 16 + kind, bits, group)
+            assert np.array_equal(q, qo) and np.array_equal(s, so), (layer, kind)
+    q, s = gm.get_linear(T_LMHEAD, c["d"], c["V"], 8)
+    qo, so = om.get_linear(T_LMHEAD, 8)
+    assert np.array_equal(q, qo) and np.array_equal(s, so)  # the head stays int8 (llama.rs:535-542)
+
+
+@pytest.mark.parametrize("kind", ["llama", "llama_tied", "gpt2"])
+@pytest.mark.parametrize("bits,group", [(8, 0), (4, 32), (4, 16)])
+def test_tiny_models_cached_decode(dev, kind, bits, group):
+    """tests/llama.rs:139-170, tests/inference.rs:50-68: full forward, chunked [5,1,4,2] and 1-by-1, all vs the checker."""
+    if kind == "gpt2":
+        cfgs = gpt2_cfg(41, 160, 64, 2, 2)
+    else:
+        cfgs = llama_cfg(**dict(TINY_LLAMA, tied=(kind == "llama_tied")))
+    om, gm = build(dev, cfgs, 2, bits, group)
+    ids = np.array([[(i * 5 + 1) % 41 for i in range(12)]], np.int32)
+    want = om.forward_cached(ids, all_positions=True)
+    close(want, gm.forward_cached(ids, all_positions=True), "full")
+    for chunks in ([5, 1, 4, 2], [1] * 12):
+        gm.cache_clear()
+        pos, rows = 0, []
+        for c in chunks:
+            rows.append(gm.forward_cached(ids[:, pos:pos + c], all_positions=True))
+            pos += c
+        close(want, np.concatenate(rows, 1), str(chunks))
+    assert gm.cache_len() == 12
+
+
+def test_cache_capacity_doubles_and_long_decode(dev):
+    """tests/kvcache.rs:84-102: 100 single-token steps; capacity 16 -> 32 -> 64 -> 128; logits track the checker."""
+    om, gm = build(dev, llama_cfg(**TINY_LLAMA), 3, 8)
+    seen = set()
+    tok = np.array([[1]], np.int32)
+    for step in range(100):
+        got = gm.forward_cached(tok)
+        seen.add(gm.cache_capacity())
+        want = om.forward_cached(tok)
+        if step % 9 == 0 or step == 99:
+            close(want, got, f"step {step}")
+        tok = np.array([[int(np.argmax(want[0]))]], np.int32)
+    assert seen == {16, 32, 64, 128}
+
+
+def test_causal_and_batched(dev):
+    """tests/llama.rs:172-191: a batch of 2 equals two separate passes."""
+    om, gm = build(dev, llama_cfg(**TINY_LLAMA), 4, 8)
+    a = np.array([[1, 2, 3, 4, 5]], np.int32)
+    b = np.array([[7, 8, 9, 10, 11]], np.int32)
+    both = gm.forward_cached(np.concatenate([a, b]), all_positions=True)
+    close(om.forward_cached(np.concatenate([a, b]), all_positions=True), both, "batch")
+    gm.cache_clear()
+    la = gm.forward_cached(a, all_positions=True)
+    gm.cache_clear()
+    lb = gm.forward_cached(b, all_positions=True)
+    assert np.abs(both[0] - la[0]).max() < 1e-5 and np.abs(both[1] - lb[0]).max() < 1e-5
+
+
+def test_errors_mirror_the_reference_asserts(dev):
+    _, gm = build(dev, llama_cfg(**dict(TINY_LLAMA, max_pos=8)), 5, 8)
+    with pytest.raises(nn.RuaiError, match="exceeds max_position_embeddings"):
+        gm.forward_cached(np.zeros((1, 9), np.int32))
+    with pytest.raises(nn.RuaiError, match="out of range"):
+        gm.forward_cached(np.array([[41]], np.int32))
+    gm.cache_clear()
+    gm.forward_cached(np.array([[1, 2]], np.int32))
+    with pytest.raises(nn.RuaiError, match="do not match the cached"):
+        gm.forward_cached(np.array([[1], [2]], np.int32))
+    fresh = nn.Llama(dev, llama_cfg(**TINY_LLAMA)[1])
+    with pytest.raises(nn.RuaiError, match="quantize"):
+        fresh.forward_cached(np.array([[1]], np.int32))
+
+
+@pytest.mark.parametrize("kind", ["llama", "gpt2"])
+def test_generate_slides_the_window(dev, kind):
+    """generation.rs:96-101 with a context of 8."""
+    cfgs = gpt2_cfg(41, 8, 64, 2, 2) if kind == "gpt2" else llama_cfg(**dict(TINY_LLAMA, max_pos=8))
+    om, gm = build(dev, cfgs, 6, 8)
+    prompt = np.array([1, 2, 3], np.int32)
+    assert gm.generate(prompt, 14).tolist() == om.generate(prompt, 14).tolist()
+
+
+def test_set_weights_then_quantize_matches_load_synthetic(dev):
+    """The `set f32 weights -> quantize_int4(group)` route (what a checkpoint loader uses) equals the synthetic loader."""
+    oc, gc = llama_cfg(**TINY_LLAMA)
+    c = TINY_LLAMA
+    gm = nn.Llama(dev, gc)
+    shapes = {0: (c["d"], c["H"] * c["hd"]), 1: (c["d"], c["KV"] * c["hd"]), 2: (c["d"], c["KV"] * c["hd"]), 3: (c["H"] * c["hd"], c["d"]),
+              4: (c["d"], c["ffn"]), 5: (c["d"], c["ffn"]), 6: (c["ffn"], c["d"])}
+    for layer in range(c["L"]):
+        for kind, shp in shapes.items():
+            gm.set_f32(layer * 16 + kind, oracle.synth_normal(7, layer * 16 + kind, shp))
+        gm.set_f32(0x50000000 + layer, np.ones(c["d"], np.float32))
+        gm.set_f32(0x52000000 + layer, np.ones(c["d"], np.float32))
+    gm.set_f32(0x10000000, oracle.synth_normal(7, 0x10000000, (c["V"], c["d"])))
+    gm.set_f32(T_LMHEAD, oracle.synth_normal(7, T_LMHEAD, (c["d"], c["V"])))
+    gm.set_f32(0x40000000, np.ones(c["d"], np.float32))
+    with pytest.raises(nn.RuaiError, match="must be even and divide"):
+        gm.quantize_int4(5)
+    gm2 = nn.Llama(dev, gc)
+    gm2.load_synthetic(7, 4, 16)
+    om = oracle.Model(oc, seed=7, bits=4, group=16)
+    ids = np.array([[3, 1, 4, 1, 5, 9]], np.int32)
+    want = om.forward_cached(ids, all_positions=True)
+    close(want, gm2.forward_cached(ids, all_positions=True), "synthetic")
+
+
+# ---- the benchmark configurations --------------------------------------------------------
+
+def greedy_parity(om, gm, prompt, n_new, min_same=32):
+    ids_o, trace = om.generate(prompt, n_new, trace=True)
+    ids_g = gm.generate(prompt, n_new)
+    same = 0
+    for a, b in zip(ids_o[prompt.size:], ids_g[prompt.size:]):
+        if a != b:
+            break
+        same += 1
+    if same < n_new:
+        row = np.sort(trace[same])[::-1]
+        msg = f"first divergence at generated token {same}; checker top-2 margin there {row[0] - row[1]:.3e}"
+    else:
+        msg = ""
+    assert same >= min(min_same, n_new), msg
+    return same, trace
+
+
+def test_config1_gpt2_small_int8_greedy(dev):
+    """GPT-2-small-shaped int8: 12 layers, d 768, 12 heads, vocab 50257, ctx 1024; prompt 16, 32 greedy tokens."""
+    om, gm = build(dev, gpt2_cfg(50257, 1024, 768, 12, 12), 0, 8)
+    prompt = oracle.synth_tokens(0, 0x20000000, 16, 50257)
+    same, trace = greedy_parity(om, gm, prompt, 32)
+    assert same == 32
+    # logits of the prompt's last position and of a decode step
+    gm.cache_clear()
+    got = gm.forward_cached(prompt[None, :])
+    close(trace[0:1], got, "prompt logits")
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_config2_3_smollm2_shaped(dev, bits):
+    """SmolLM2-135M-shaped Llama (30 layers, d 576, 9/3 heads, ffn 1536, vocab 49152, tied), int8 and int4 g32."""
+    om, gm = build(dev, llama_cfg(49152, 576, 1536, 30, 9, 3, 64, 2048, tied=True), 0, bits, 32)
+    prompt = oracle.synth_tokens(0, 0x20000000, 64, 49152)
+    same, trace = greedy_parity(om, gm, prompt, 40)
+    gm.cache_clear()
+    close(trace[0:1], gm.forward_cached(prompt[None, :]), "prompt logits")
+    # batch 16: sixteen different prompts, forward_cached([B, 1]) steps with per-row argmax
+    B, T = 16, 8
+    prompts = np.stack([oracle.synth_tokens(0, 0x20000000 + b, T, 49152) for b in range(B)])
+    om.cache_clear()
+    gm.cache_clear()
+    lo = om.forward_cached(prompts)
+    close(lo, gm.forward_cached(prompts), "batch-16 prefill")
+    nxt = np.array([oracle.argmax(r) for r in lo], np.int32)
+    ids_dev = nn.Tensor.from_numpy(dev, nxt)
+    for step in range(3):
+        lo = om.forward_cached(nxt[:, None])
+        want_next = np.array([oracle.argmax(r) for r in lo], np.int32)
+        got_next = gm.decode_step(B, ids_dev.ptr if step == 0 else None)
+        assert got_next.tolist() == want_next.tolist(), f"batched greedy step {step}"
+        nxt = want_next
+    assert gm.step_launches() > 0
+
+
+@pytest.mark.parametrize("name,cfg", [
+    ("tinyllama-1.1b-shaped, 2 of 22 layers", dict(V=32000, d=2048, ffn=5632, L=2, H=32, KV=4, hd=64, max_pos=2048)),
+    ("llama-3-8b-shaped, 2 of 32 layers", dict(V=128256, d=4096, ffn=14336, L=2, H=32, KV=8, hd=128, max_pos=2048, theta=500000.0)),
+])
+@pytest.mark.parametrize("bits", [8, 4])
+def test_config4_5_full_width_layer_reduced(dev, name, cfg, bits):
+    """Full layer widths, vocabulary and head geometry of configs 4 and 5 with the layer count cut to 2 so the
+    CPU checker finishes in seconds: prompt 12, then 6 greedy tokens and their logits."""
+    om, gm = build(dev, llama_cfg(**cfg), 0, bits, 32)
+    prompt = oracle.synth_tokens(0, 0x20000000, 12, cfg["V"])
+    same, trace = greedy_parity(om, gm, prompt, 6, min_same=6)
+    gm.cache_clear()
+    close(trace[0:1], gm.forward_cached(prompt[None, :]), name)
