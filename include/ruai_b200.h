@@ -197,6 +197,13 @@ int ruai_model_cache_assume(ruai_model* m, uint32_t B, uint32_t len);
 int ruai_model_step_bytes(const ruai_model* m, uint32_t B, uint32_t len, double* bytes);
 /* Kernels launched by one decode step (for launch accounting). */
 int ruai_model_step_launches(const ruai_model* m, uint32_t* launches);
+/* Times `iters` passes over every quantized Linear of the model for B rows (the
+ * weight-streaming kernels of a decode step and nothing else) with CUDA events on
+ * the context stream.  Reports the elapsed milliseconds, the launches of one pass
+ * and the algorithmic bytes of one pass (packed weights + scales + biases +
+ * activations read and written). */
+int ruai_model_time_linears(ruai_model* m, uint32_t B, uint32_t iters, float* ms_total,
+                            uint32_t* launches_per_pass, double* bytes_per_pass);
 
 /* ---- tensor parallel -------------------------------------------------------
  * The exchange buffers of every rank are mapped into every other rank through

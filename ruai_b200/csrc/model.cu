@@ -559,6 +559,8 @@ int prepare_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions) {
 
 // ---- C ABI ---------------------------------------------------------------------------------
 
+static int run_decode_graph(ruai_model* m, uint32_t B);
+
 RUAI_API int ruai_llama_create(ruai_ctx* c, const ruai_llama_config* cfg, const ruai_tp* tp, ruai_model** out) {
   if (!c || !cfg || !out) return ruai_fail(c, RUAI_ERR_ARG, "ruai_llama_create: NULL argument");
   *out = nullptr;
@@ -719,8 +721,11 @@ RUAI_API int ruai_model_forward_cached(ruai_model* m, const int32_t* ids, uint32
   RUAI_CUDA(c, cudaMemcpyAsync(m->d_ids.p, ids, (size_t)B * T * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
   const int32_t len = (int32_t)m->len;
   RUAI_CUDA(c, cudaMemcpyAsync(m->d_len.p, &len, sizeof len, cudaMemcpyHostToDevice, c->stream));
-  RUAI_TRY(issue_step(m, B, T, all_positions != 0, false));
-  m->len += T;
+  if (T == 1) RUAI_TRY(run_decode_graph(m, B));  // single-token steps replay the captured graph
+  else {
+    RUAI_TRY(issue_step(m, B, T, all_positions != 0, false));
+    m->len += T;
+  }
   if (logits_host) {
     if (m->world > 1) return model_fail(m, RUAI_ERR_UNSUPPORTED, "full logits of a sharded head are not gathered; use decode_step / generate");
     const size_t rows = all_positions ? (size_t)B * T : B;
@@ -755,16 +760,13 @@ RUAI_API int ruai_model_cache_assume(ruai_model* m, uint32_t B, uint32_t len) {
   return RUAI_OK;
 }
 
-RUAI_API int ruai_model_decode_step(ruai_model* m, const int32_t* ids_dev, uint32_t B, int32_t* next_host) {
-  if (!m) return ruai_fail(nullptr, RUAI_ERR_ARG, "model is NULL");
+// Replays (capturing first if needed) the graph of one greedy decode step for batch B.
+static int run_decode_graph(ruai_model* m, uint32_t B) {
   ruai_ctx* c = m->ctx;
-  DeviceGuard g(c->ordinal);
-  RUAI_TRY(prepare_step(m, B, 1, false));
-  if (ids_dev) RUAI_CUDA(c, cudaMemcpyAsync(m->d_ids.p, ids_dev, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, c->stream));
   if (!m->graph || m->graph_B != B || m->graph_cap != m->cap) {
     drop_graph(m);
-    // make sure the scratch is large enough before capturing (no allocation inside a capture)
-    // split-K partials of one GEMV never exceed (3 * SMs + column tiles) * 256 floats per row
+    // split-K partials of one GEMV never exceed (3 * SMs + column tiles) * 256 floats per row;
+    // reserve before capturing (no allocation inside a capture)
     uint32_t max_n = m->head.w->n;
     for (Layer& L : m->layers) max_n = std::max(max_n, std::max(L.up.w->n, L.qkv.w->n));
     const size_t tiles = (max_n + 255) / 256;
@@ -785,10 +787,65 @@ RUAI_API int ruai_model_decode_step(ruai_model* m, const int32_t* ids_dev, uint3
   }
   RUAI_CUDA(c, cudaGraphLaunch(m->graph, c->stream));
   m->len += 1;
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_model_decode_step(ruai_model* m, const int32_t* ids_dev, uint32_t B, int32_t* next_host) {
+  if (!m) return ruai_fail(nullptr, RUAI_ERR_ARG, "model is NULL");
+  ruai_ctx* c = m->ctx;
+  DeviceGuard g(c->ordinal);
+  RUAI_TRY(prepare_step(m, B, 1, false));
+  if (ids_dev) RUAI_CUDA(c, cudaMemcpyAsync(m->d_ids.p, ids_dev, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, c->stream));
+  RUAI_TRY(run_decode_graph(m, B));
   if (next_host) {
     RUAI_CUDA(c, cudaMemcpyAsync(next_host, m->d_ids.p, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
     return check_device_status(m);
   }
+  return RUAI_OK;
+}
+
+// Times `iters` passes over every quantized Linear of the model (the weight-streaming
+// kernels of one decode step, nothing else) for B rows, with CUDA events on the stream.
+RUAI_API int ruai_model_time_linears(ruai_model* m, uint32_t B, uint32_t iters, float* ms_total, uint32_t* launches, double* bytes_per_pass) {
+  if (!m || !ms_total) return ruai_fail(nullptr, RUAI_ERR_ARG, "NULL argument");
+  if (!m->quantized) return model_fail(m, RUAI_ERR_UNSUPPORTED, "the model is not quantized");
+  ruai_ctx* c = m->ctx;
+  DeviceGuard g(c->ordinal);
+  RUAI_TRY(ensure_activations(m, B, B, B, 1));
+  float *xn = m->xn.as<float>(), *qkv = m->qkv.as<float>(), *att = m->att.as<float>(), *hb = m->hbuf.as<float>(), *xl = m->xl.as<float>();
+  RUAI_CUDA(c, cudaMemsetAsync(xn, 0, (size_t)B * m->d * sizeof(float), c->stream));
+  RUAI_CUDA(c, cudaMemsetAsync(att, 0, (size_t)B * m->Hl * m->hd * sizeof(float), c->stream));
+  RUAI_CUDA(c, cudaMemsetAsync(hb, 0, (size_t)B * m->fl * sizeof(float), c->stream));
+  double bytes = 0.0;
+  uint32_t n_launch = 0;
+  auto pass = [&](bool count) -> int {
+    for (Layer& Ly : m->layers) {
+      GemvEpilogue e0, e1, e2, e3;
+      e0.bias = Ly.qkv.bias.as<float>(); e1.bias = Ly.o.bias.as<float>(); e2.bias = Ly.up.bias.as<float>(); e3.bias = Ly.down.bias.as<float>();
+      e2.act = m->llama ? ACT_SWIGLU : ACT_GELU;
+      RUAI_TRY(ruai_gemv_launch(c, Ly.qkv.w, xn, RUAI_F32, m->d, B, qkv, e0));
+      RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, m->Hl * m->hd, B, xl, e1));
+      RUAI_TRY(ruai_gemv_launch(c, Ly.up.w, xn, RUAI_F32, m->d, B, hb, e2));
+      RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, B, xl, e3));
+      if (count) {
+        for (const Lin* l : {&Ly.qkv, &Ly.o, &Ly.up, &Ly.down}) bytes += l->bytes() + 4.0 * B * (l->w->k + l->w->n);
+        n_launch += 4;
+      }
+    }
+    GemvEpilogue eh;
+    RUAI_TRY(ruai_gemv_launch(c, m->head.w, xn, RUAI_F32, m->d, B, m->logits.as<float>(), eh));
+    if (count) { bytes += m->head.bytes() + 4.0 * B * (m->head.w->k + m->head.w->n); n_launch += 1; }
+    return RUAI_OK;
+  };
+  RUAI_TRY(pass(true));  // warm-up, also sizes the scratch
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  RUAI_CUDA(c, cudaEventRecord(c->ev0, c->stream));
+  for (uint32_t i = 0; i < iters; ++i) RUAI_TRY(pass(false));
+  RUAI_CUDA(c, cudaEventRecord(c->ev1, c->stream));
+  RUAI_CUDA(c, cudaEventSynchronize(c->ev1));
+  RUAI_CUDA(c, cudaEventElapsedTime(ms_total, c->ev0, c->ev1));
+  if (launches) *launches = n_launch;
+  if (bytes_per_pass) *bytes_per_pass = bytes;
   return RUAI_OK;
 }
 

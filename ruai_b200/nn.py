@@ -330,6 +330,12 @@ class _Model:
         self.dev.check(self.dev.L.ruai_model_step_launches(self.h, C.byref(v)))
         return v.value
 
+    def time_linears(self, B, iters):
+        """(ms per pass, launches per pass, algorithmic bytes per pass) of the quantized Linears alone."""
+        ms, n, b = C.c_float(), C.c_uint32(), C.c_double()
+        self.dev.check(self.dev.L.ruai_model_time_linears(self.h, B, iters, C.byref(ms), C.byref(n), C.byref(b)))
+        return ms.value / iters, n.value, b.value
+
     def tp_export(self):
         buf = C.create_string_buffer(_lib.IPC_HANDLE_BYTES)
         self.dev.check(self.dev.L.ruai_tp_export(self.h, buf))
