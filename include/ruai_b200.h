@@ -110,6 +110,17 @@ int ruai_qweight_info(const ruai_qweight* w, uint32_t* k, uint32_t* n, uint32_t*
  * x_dtype, bias_dev_or_null is f32 [n].  Arithmetic is f32.                 */
 int ruai_matmul_q(ruai_ctx* ctx, int x_dtype, const void* x_dev, const ruai_qweight* w,
                   const float* bias_dev_or_null, void* out_dev, uint32_t m);
+/* ruai_matmul_q for hosts that cannot let this library allocate device memory at run time
+ * (a serving process whose framework already owns the whole device, or a loop that cannot
+ * afford cudaMalloc's implicit synchronisation).  Same arguments, same results.  It has no
+ * counterpart in the reference.  The split-K scratch lives in a fixed 8 MiB + 16 KiB array
+ * inside the loaded module (held on every GPU that loads the library until exit); a call
+ * whose split plan needs more fails with RUAI_ERR_UNSUPPORTED and says so.  The first call
+ * on a device looks the array's address up once; make that call before starting any stream
+ * capture.  All calls on a device share the array: calls that overlap on the GPU race.
+ * Only chunk-layout weights (int8, or int4 with group 32). */
+int ruai_matmul_q_static(ruai_ctx* ctx, int x_dtype, const void* x_dev, const ruai_qweight* w,
+                         const float* bias_dev_or_null, void* out_dev, uint32_t m);
 /* `Backend::dequant_int4` (mod.rs:689-693, cpu.rs:1023-1033): exact f32 [k,n]. */
 int ruai_dequant_int4(ruai_ctx* ctx, const ruai_qweight* w, float* out_dev);
 /* Same on reference-layout device buffers, without a repack (any even group). */

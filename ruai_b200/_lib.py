@@ -62,6 +62,7 @@ _PROTOS = {
     "ruai_qweight_free": (C.c_int, [vp]),
     "ruai_qweight_info": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
     "ruai_matmul_q": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32]),
+    "ruai_matmul_q_static": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32]),
     "ruai_dequant_int4": (C.c_int, [vp, vp, vp]),
     "ruai_dequant_int4_ref": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
     "ruai_llama_create": (C.c_int, [vp, C.POINTER(LlamaConfig), C.POINTER(TP), C.POINTER(vp)]),

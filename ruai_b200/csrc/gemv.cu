@@ -326,3 +326,86 @@ RUAI_API int ruai_matmul_q(ruai_ctx* c, int x_dtype, const void* x, const ruai_q
   e.out_dtype = x_dtype;
   return ruai_gemv_launch(c, w, x, x_dtype, w->k, m, out, e);
 }
+
+// ---------------------------------------------------------------------------------------
+// Quantized matmul for callers that must not allocate.
+//
+// Some hosts of this library cannot let it call cudaMalloc at run time: a serving process
+// whose framework has already claimed the whole device for its own caching allocator (a
+// later cudaMalloc simply fails), or a latency-critical loop in which the implicit device
+// synchronisation of cudaMalloc / cudaFree is not acceptable.  ruai_matmul_q grows the
+// context's split-K scratch on demand; this variant instead keeps its split-K scratch in a
+// fixed array that is part of the loaded module, so it never allocates.
+//
+// The array costs kStaticScratchBytes (8 MiB + 16 KiB) of device memory on every GPU that
+// loads the library, from load until exit.  All calls on a device share it, and it keeps
+// whatever the last call left: the arrival counters are cleared on the stream before every
+// launch, the partial sums are always written before they are read.  Two calls that overlap
+// on the GPU (different streams or contexts on one device) would race on it.
+namespace {
+
+constexpr size_t kStaticCounters = 4096;                                 // column tiles x row tiles
+constexpr size_t kStaticPartialBytes = 8u << 20;                         // split-K partial sums
+constexpr size_t kStaticScratchBytes = kStaticCounters * sizeof(unsigned) + kStaticPartialBytes;
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device ordinal.  In host code the array's name is
+// only a handle for the runtime, never an address a kernel may be given.
+static void* g_static_scratch_addr[kMaxDevices] = {};
+
+}  // namespace
+
+RUAI_API int ruai_matmul_q_static(ruai_ctx* c, int x_dtype, const void* x, const ruai_qweight* w, const float* bias, void* out, uint32_t m) {
+  if (!c || !w || (m && (!x || !out))) return ruai_fail(c, RUAI_ERR_ARG, "ruai_matmul_q_static: NULL argument");
+  if (x_dtype != RUAI_F32 && x_dtype != RUAI_F16 && x_dtype != RUAI_BF16) return ruai_fail(c, RUAI_ERR_ARG, "ruai_matmul_q_static: bad dtype %d", x_dtype);
+  if (w->ctx != c) return ruai_fail(c, RUAI_ERR_ARG, "ruai_matmul_q_static: weight belongs to another context");
+  if (w->layout != QL_CHUNK16) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "ruai_matmul_q_static: int4 weights need group 32");
+  if (c->ordinal < 0 || c->ordinal >= kMaxDevices) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "ruai_matmul_q_static: device ordinal %d", c->ordinal);
+  if (m == 0) return RUAI_OK;
+  DeviceGuard g(c->ordinal);
+  // set-up, once per device, with that device current: ask the runtime where the array lives
+  if (!g_static_scratch_addr[c->ordinal]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return ruai_fail(c, RUAI_ERR_CUDA, "ruai_matmul_q_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_static_scratch_addr[c->ordinal] = p;
+  }
+  unsigned char* base = (unsigned char*)g_static_scratch_addr[c->ordinal];
+  // the same work split as ruai_matmul_q, so both give the same bits
+  const int mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16;
+  const uint32_t row_tiles = (m + mt - 1) / mt;
+  const uint32_t col_tiles = (w->n + kThreads - 1) / kThreads;
+  if (row_tiles > 65535) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "m too large");
+  const uint32_t want = (uint32_t)c->sm_count * 3u;
+  uint32_t splits = (want + col_tiles * row_tiles - 1) / (col_tiles * row_tiles);
+  const uint32_t max_splits = (w->chunks + kAhead - 1) / kAhead;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  uint32_t cps = (w->chunks + splits - 1) / splits;
+  cps = (cps + kAhead - 1) / kAhead * kAhead;
+  splits = (w->chunks + cps - 1) / cps;
+  const size_t need_partial = splits > 1 ? (size_t)splits * m * w->n * sizeof(float) : 0;
+  const size_t need_counters = splits > 1 ? (size_t)col_tiles * row_tiles : 0;
+  if (need_partial > kStaticPartialBytes || need_counters > kStaticCounters)
+    return ruai_fail(c, RUAI_ERR_UNSUPPORTED,
+                     "ruai_matmul_q_static: m=%u x n=%u needs %zu bytes of split-K scratch and %zu counters; the fixed scratch holds %zu bytes and %zu "
+                     "counters (use ruai_matmul_q, which allocates)",
+                     m, w->n, need_partial, need_counters, kStaticPartialBytes, kStaticCounters);
+  GemvParams p;
+  p.w = (const uint4*)w->data; p.scale = w->scale; p.x = x; p.x_dtype = x_dtype; p.x_ld = w->k;
+  p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_split = cps; p.splits = splits;
+  p.out = out;
+  p.epi = GemvEpilogue();
+  p.epi.bias = bias;
+  p.epi.out_dtype = x_dtype;
+  p.epi.out_ld = w->n;
+  p.counters = (unsigned*)base;
+  p.partial = (float*)(base + kStaticCounters * sizeof(unsigned));
+  if (need_counters) RUAI_CUDA(c, cudaMemsetAsync(p.counters, 0, need_counters * sizeof(unsigned), c->stream));
+  const dim3 grid(col_tiles, splits, row_tiles);
+  cudaError_t e = w->bits == 8 ? launch_mt<8>(c, p, grid, mt) : launch_mt<4>(c, p, grid, mt);
+  if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "ruai_matmul_q_static: launch failed: %s", cudaGetErrorString(e));
+  return RUAI_OK;
+}
