@@ -221,6 +221,7 @@ def main():
     ids_dev = nn.Tensor.from_numpy(dev, ids0)
 
     # ---- device-resident decode: `value` ----
+    m.cache_reserve(B, min(dims.get("max_pos", dims.get("n_pos")), ctx + K + W + 8))  # no growth, no re-capture while timing
     m.cache_assume(B, ctx)
     m.decode_step(B, ids_dev.ptr, fetch=True)            # captures the graph
     for _ in range(W - 1):

@@ -198,6 +198,9 @@ int ruai_model_generate(ruai_model* m, const int32_t* prompt_host, uint32_t T, u
  * copied out.  Batched greedy decode for B independent sequences.           */
 int ruai_model_decode_step(ruai_model* m, const int32_t* ids_dev_or_null, uint32_t B,
                            int32_t* next_ids_host_or_null);
+/* Grow the cache now to hold `positions` per sequence for batch B (same growth rule), so that
+ * later steps neither reallocate nor re-capture the decode graph. */
+int ruai_model_cache_reserve(ruai_model* m, uint32_t B, uint32_t positions);
 /* Pretend `len` positions are cached for batch B (contents: whatever the
  * buffers hold, zero-filled when fresh); used to time decode at a given
  * context length without running the prompt. */

@@ -78,6 +78,7 @@ _PROTOS = {
     "ruai_model_generate": (C.c_int, [vp, vp, u32, u32, vp]),
     "ruai_model_decode_step": (C.c_int, [vp, vp, u32, vp]),
     "ruai_model_cache_assume": (C.c_int, [vp, u32, u32]),
+    "ruai_model_cache_reserve": (C.c_int, [vp, u32, u32]),
     "ruai_model_step_bytes": (C.c_int, [vp, u32, u32, C.POINTER(C.c_double)]),
     "ruai_model_step_launches": (C.c_int, [vp, C.POINTER(u32)]),
     "ruai_model_time_linears": (C.c_int, [vp, u32, u32, C.POINTER(C.c_float), C.POINTER(u32), C.POINTER(C.c_double)]),

@@ -145,9 +145,28 @@ struct GemvEpilogue {
   int act = ACT_NONE;            // ACT_SWIGLU: columns (2i, 2i+1) = (gate_i, up_i), out is [m, n/2]
   int out_dtype = RUAI_F32;
   uint32_t out_ld = 0;           // row stride of out in elements (0: n, or n/2 for SWIGLU)
-  float* sumsq = nullptr;        // optional [col_tiles][m]: per column tile sum of squares of out
+  float* sumsq = nullptr;        // optional [col_tiles][m]: per 256-column tile, the sum of squares of the stored row
+  // optional greedy pick over the stored rows (generation.rs:6-8, last maximum): every column tile leaves its
+  // best (ordered value, column) in argmax_slots [col_tiles][m]; the last tile to finish picks per row, writes
+  // argmax_out [m] and adds len_add to *len_ptr.  Needs m <= 16.
+  int32_t* argmax_out = nullptr;
+  int2* argmax_slots = nullptr;
+  unsigned* argmax_counter = nullptr;
+  int32_t* len_ptr = nullptr;
+  int32_t len_add = 0;
 };
+
+// RMSNorm folded into the GEMV's load of x (functional.rs:151-165): x * rstd * w with
+// rstd = 1/sqrt(sum(x^2) * (1/k) + eps), the sum given as per-tile partial sums [tiles][m].
+struct GemvPrologue {
+  const float* norm_w = nullptr;  // f32 [k]; NULL: x is used as it is
+  const float* sumsq = nullptr;
+  uint32_t tiles = 0;
+  float eps = 0.0f;
+};
+
+constexpr int kGemvTileCols = 256;  // columns per GEMV CTA, and per sumsq / argmax tile
 
 // y = x @ W for m rows; x is [m, k] (row stride x_ld) in x_dtype.
 int ruai_gemv_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
-                     const GemvEpilogue& epi);
+                     const GemvEpilogue& epi, const GemvPrologue& pro = GemvPrologue());

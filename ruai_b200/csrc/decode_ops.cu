@@ -8,6 +8,8 @@
 // functional.rs:176-192; logits copied out for the host argmax, generation.rs:104).
 // Positions and token ids are read from device memory so that a captured graph of
 // the step can be replayed without host involvement.
+#include <algorithm>
+
 #include "decode_ops.cuh"
 
 namespace {
@@ -39,7 +41,8 @@ __device__ float block_sum(float v, float* red) {
 // Row r = b*T + t; position = *len + t.
 __global__ void embed_kernel(const int32_t* __restrict__ ids, const float* __restrict__ embed, const float* __restrict__ wpe,
                              const int32_t* __restrict__ len, uint32_t T, uint32_t d, uint32_t vocab, float* __restrict__ x,
-                             int* __restrict__ err) {
+                             int* __restrict__ err, float* __restrict__ sumsq) {
+  __shared__ float red[32];
   grid_dependency_wait();
   grid_launch_dependents();
   const uint32_t r = blockIdx.x;
@@ -50,7 +53,16 @@ __global__ void embed_kernel(const int32_t* __restrict__ ids, const float* __res
   }
   const float* e = embed + (size_t)id * d;
   const float* p = wpe ? wpe + (size_t)(*len + (r % T)) * d : nullptr;
-  for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) x[(size_t)r * d + i] = p ? e[i] + p[i] : e[i];
+  float ss = 0.0f;
+  for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = p ? e[i] + p[i] : e[i];
+    x[(size_t)r * d + i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (sumsq) {  // one tile per row: the sum of squares the next RMSNorm needs
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) sumsq[r] = ss;
+  }
 }
 
 // F::rms_norm (functional.rs:151-165): x * (1/sqrt(sum(x^2) * (1/d) + eps)) * w.
@@ -140,30 +152,68 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 // softmax(q k^T / sqrt(hd) + causal mask) v.  The `rep` query heads of one KV head are
 // handled together so the cached rows are read once (the reference's
 // [B, H_kv, rep*T, hd] view, llama.rs:264-268).  Keys are split over gridDim.z CTAs and
-// over the warps of a CTA; each keeps an online-softmax state (max, sum, weighted V)
-// and the states are merged at the end: within the CTA through shared memory, across
-// CTAs by the last one to arrive.
+// over the warps of a CTA; a warp takes kKeys keys per iteration (all their loads are
+// issued before any arithmetic) and keeps an online-softmax state (max, sum, weighted V).
+// States are merged at the end: within the CTA through shared memory, across CTAs by the
+// last one to arrive.
+// With p.fuse (single new token per sequence) the kernel also does apply_rope
+// (functional.rs:197-204) on q and on the new key and appends the new key / value to the
+// cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
 template <int EPL, int REP>
 __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
-  constexpr int kWarps = 4;
-  extern __shared__ float sm[];  // q [REP][hd] | merge [kWarps][REP][hd + 2]
+  constexpr int kWarps = 4, kKeys = 4;
+  extern __shared__ float sm[];  // q [REP][hd] | new k [hd] | new v [hd] | merge [kWarps][REP][hd + 2]
   __shared__ unsigned s_last;
-  const uint32_t hd = p.hd;
+  const uint32_t hd = p.hd, half = hd / 2;
   float* qs = sm;
-  float* mg = sm + REP * hd;
+  float* knew = sm + REP * hd;
+  float* vnew = knew + hd;
+  float* mg = vnew + hd;
   const uint32_t bk = blockIdx.x, b = bk / p.KV, kvh = bk % p.KV, t = blockIdx.y, split = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   grid_dependency_wait();
   grid_launch_dependents();
   const uint32_t past = (uint32_t)*p.len;
-  const uint32_t n_keys = past + t + 1;  // causal_mask_offset, functional.rs:238-247
-  const uint32_t per = (n_keys + gridDim.z - 1) / gridDim.z;
-  const uint32_t k0 = split * per, k1 = min(n_keys, k0 + per);
-  const float* qrow = p.q + (size_t)(b * p.T + t) * p.q_ld + (size_t)kvh * REP * hd;
-  for (uint32_t i = threadIdx.x; i < REP * hd; i += blockDim.x) qs[i] = qrow[i];
+  const uint32_t pos = past + t;
+  const uint32_t n_keys = pos + 1;  // causal_mask_offset, functional.rs:238-247
+  const uint32_t n_cached = p.fuse ? n_keys - 1 : n_keys;
+  const uint32_t per = (n_cached + gridDim.z - 1) / gridDim.z;
+  const uint32_t k0 = min(n_cached, split * per), k1 = min(n_cached, k0 + per);
+  const bool owns_new = p.fuse && split == gridDim.z - 1;
+  const float* row = p.q + (size_t)(b * p.T + t) * p.q_ld;
+  const float* qrow = row + (size_t)kvh * REP * hd;
+  const bool rot = p.fuse && p.table != nullptr;
+  for (uint32_t i = threadIdx.x; i < REP * hd; i += blockDim.x) {
+    float v = qrow[i];
+    if (rot) {
+      const uint32_t r = i / hd, e = i % hd, f = e < half ? e : e - half;
+      const float2 cs = p.table[(size_t)pos * half + f];
+      const float x1 = qrow[r * hd + f], x2 = qrow[r * hd + f + half];
+      v = e < half ? x1 * cs.x + (-x2) * cs.y : x2 * cs.x + x1 * cs.y;
+    }
+    qs[i] = v;
+  }
+  float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
+  float* vbase = p.vcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
+  if (owns_new) {
+    const float* kr = row + p.k_off + (size_t)kvh * hd;
+    const float* vr = row + p.v_off + (size_t)kvh * hd;
+    for (uint32_t e = threadIdx.x; e < hd; e += blockDim.x) {
+      float kvv = kr[e];
+      if (rot) {
+        const uint32_t f = e < half ? e : e - half;
+        const float2 cs = p.table[(size_t)pos * half + f];
+        const float x1 = kr[f], x2 = kr[f + half];
+        kvv = e < half ? x1 * cs.x + (-x2) * cs.y : x2 * cs.x + x1 * cs.y;
+      }
+      const float vv = vr[e];
+      knew[e] = kvv;
+      vnew[e] = vv;
+      kbase[(size_t)pos * hd + e] = kvv;
+      vbase[(size_t)pos * hd + e] = vv;
+    }
+  }
   __syncthreads();
-  const float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
-  const float* vbase = p.vcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
   float mx[REP], l[REP], o[REP][EPL];
 #pragma unroll
   for (int r = 0; r < REP; ++r) {
@@ -172,31 +222,75 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i) o[r][i] = 0.0f;
   }
-  for (uint32_t key = k0 + warp; key < k1; key += kWarps) {
-    float kv[EPL], vv[EPL];
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const uint32_t e = lane + 32 * i;
-      kv[i] = e < hd ? kbase[(size_t)key * hd + e] : 0.0f;
-      vv[i] = e < hd ? vbase[(size_t)key * hd + e] : 0.0f;
-    }
+  // one online-softmax update with up to kKeys keys whose rows are in registers
+  auto update = [&](const float (&kv)[kKeys][EPL], const float (&vv)[kKeys][EPL], int nk) {
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
-      float s = 0.0f;
+      float s[kKeys];
+#pragma unroll
+      for (int u = 0; u < kKeys; ++u) {
+        float a = 0.0f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          const uint32_t e = lane + 32 * i;
+          if (e < hd) a = fmaf(qs[r * hd + e], kv[u][i], a);
+        }
+        s[u] = a;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], off);
+      }
+      float nm = mx[r];
+#pragma unroll
+      for (int u = 0; u < kKeys; ++u) {
+        s[u] = u < nk ? s[u] * p.scale : -INFINITY;
+        nm = fmaxf(nm, s[u]);
+      }
+      const float c = expf(mx[r] - nm);  // exp(-inf) = 0 on the first keys
+      float ls = l[r] * c;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) o[r][i] *= c;
+#pragma unroll
+      for (int u = 0; u < kKeys; ++u) {
+        const float pr = expf(s[u] - nm);
+        ls += pr;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[r][i] = fmaf(pr, vv[u][i], o[r][i]);
+      }
+      l[r] = ls;
+      mx[r] = nm;
+    }
+  };
+  for (uint32_t key = k0 + warp * kKeys; key < k1; key += kWarps * kKeys) {
+    float kv[kKeys][EPL], vv[kKeys][EPL];
+    const int nk = (int)min((uint32_t)kKeys, k1 - key);
+#pragma unroll
+    for (int u = 0; u < kKeys; ++u) {
 #pragma unroll
       for (int i = 0; i < EPL; ++i) {
         const uint32_t e = lane + 32 * i;
-        if (e < hd) s = fmaf(qs[r * hd + e], kv[i], s);
+        const bool ok = u < nk && e < hd;
+        kv[u][i] = ok ? __ldcs(kbase + (size_t)(key + u) * hd + e) : 0.0f;
+        vv[u][i] = ok ? __ldcs(vbase + (size_t)(key + u) * hd + e) : 0.0f;
       }
-      s = warp_sum(s) * p.scale;
-      const float nm = fmaxf(mx[r], s);
-      const float c = expf(mx[r] - nm);  // exp(-inf) = 0 on the first key
-      const float pr = expf(s - nm);
-      l[r] = l[r] * c + pr;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) o[r][i] = o[r][i] * c + pr * vv[i];
-      mx[r] = nm;
     }
+    update(kv, vv, nk);
+  }
+  if (owns_new && warp == 0) {
+    float kv[kKeys][EPL], vv[kKeys][EPL];
+#pragma unroll
+    for (int u = 0; u < kKeys; ++u) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const uint32_t e = lane + 32 * i;
+        const bool ok = u == 0 && e < hd;
+        kv[u][i] = ok ? knew[e] : 0.0f;
+        vv[u][i] = ok ? vnew[e] : 0.0f;
+      }
+    }
+    update(kv, vv, 1);
   }
   // ---- merge the warps ----
   const uint32_t stride = hd + 2;
@@ -211,7 +305,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     if (lane == 0) { dst[hd] = mx[r]; dst[hd + 1] = l[r]; }
   }
   __syncthreads();
-  const uint32_t rows = REP, total = rows * hd;
+  const uint32_t total = REP * hd;
   float* sc = p.scratch + ((((size_t)bk * p.T + t) * gridDim.z + split) * REP) * stride;
   for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
     const uint32_t r = idx / hd, e = idx % hd;
@@ -245,19 +339,44 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
   __threadfence();
   if (threadIdx.x == 0) *counter = 0;
   const float* base = p.scratch + (((size_t)bk * p.T + t) * gridDim.z) * REP * stride;
+  // weights of the splits first (one parallel round of loads), then the weighted sums with
+  // eight independent loads in flight per thread; `mg` is free again and holds the weights
+  const uint32_t ns = gridDim.z;  // <= 64
+  float* wgt = mg;                // [ns][REP] max, then coefficient
+  float* lsum = mg + 64 * REP;    // [ns][REP]
+  for (uint32_t i = threadIdx.x; i < ns * REP; i += blockDim.x) {
+    const float* src = base + (size_t)i * stride;  // i = s * REP + r
+    wgt[i] = __ldcg(src + hd);
+    lsum[i] = __ldcg(src + hd + 1);
+  }
+  __syncthreads();
+  float* inv = lsum + 64 * REP;   // [REP] 1 / total
+  if (threadIdx.x < REP) {
+    const uint32_t r = threadIdx.x;
+    float M = -INFINITY;
+    for (uint32_t s2 = 0; s2 < ns; ++s2) M = fmaxf(M, wgt[s2 * REP + r]);
+    float L = 0.0f;
+    for (uint32_t s2 = 0; s2 < ns; ++s2) {
+      const float ms = wgt[s2 * REP + r];
+      const float c = ms == -INFINITY ? 0.0f : expf(ms - M);
+      L += lsum[s2 * REP + r] * c;
+      wgt[s2 * REP + r] = c;
+    }
+    inv[r] = 1.0f / L;
+  }
+  __syncthreads();
   for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
     const uint32_t r = idx / hd, e = idx % hd;
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < gridDim.z; ++s) M = fmaxf(M, __ldcg(base + ((size_t)s * REP + r) * stride + hd));
-    float L = 0.0f, O = 0.0f;
-    for (uint32_t s = 0; s < gridDim.z; ++s) {
-      const float* src = base + ((size_t)s * REP + r) * stride;
-      const float ms = __ldcg(src + hd);
-      const float c = ms == -INFINITY ? 0.0f : expf(ms - M);
-      L += __ldcg(src + hd + 1) * c;
-      O += __ldcg(src + e) * c;
+    float O = 0.0f;
+    for (uint32_t s0 = 0; s0 < ns; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s0 + u < ns ? __ldcg(base + ((size_t)(s0 + u) * REP + r) * stride + e) : 0.0f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < ns) O = fmaf(v[u], wgt[(s0 + u) * REP + r], O);
     }
-    p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = O / L;
+    p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = O * inv[r];
   }
 }
 
@@ -335,8 +454,8 @@ cudaError_t launch_attn_rep(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t 
 }  // namespace
 
 int ruai_embed(ruai_ctx* c, const int32_t* ids, const float* embed, const float* wpe, const int32_t* len, uint32_t rows, uint32_t T, uint32_t d,
-               uint32_t vocab, float* x, int* err) {
-  RUAI_CUDA(c, ruai_launch(c, embed_kernel, dim3(rows), dim3(256), 0, true, ids, embed, wpe, len, T, d, vocab, x, err));
+               uint32_t vocab, float* x, int* err, float* sumsq) {
+  RUAI_CUDA(c, ruai_launch(c, embed_kernel, dim3(rows), dim3(256), 0, true, ids, embed, wpe, len, T, d, vocab, x, err, sumsq));
   return RUAI_OK;
 }
 
@@ -367,7 +486,8 @@ int ruai_rope_kv(ruai_ctx* c, float* qkv, uint32_t qkv_ld, uint32_t k_off, uint3
 
 int ruai_attention(ruai_ctx* c, const AttnParams& p, uint32_t B, uint32_t rep, uint32_t splits) {
   const uint32_t epl = (p.hd + 31) / 32;
-  const size_t smem = ((size_t)rep * p.hd + 4 * (size_t)rep * (p.hd + 2)) * sizeof(float);
+  const size_t merge = std::max<size_t>(4 * (size_t)rep * (p.hd + 2), 128 * (size_t)rep + rep);
+  const size_t smem = ((size_t)rep * p.hd + 2 * (size_t)p.hd + merge) * sizeof(float);
   const dim3 grid(B * p.KV, p.T, splits);
   cudaError_t e;
   if (epl <= 1) e = launch_attn_rep<1>(c, p, grid, smem, rep);

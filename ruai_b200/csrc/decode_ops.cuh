@@ -5,8 +5,13 @@
 struct AttnParams {
   const float* q;       // [B*T, q_ld]; the rep query heads of KV head g at column g*rep*hd
   uint32_t q_ld;
-  const float* kcache;  // [B, KV, cap, hd]
-  const float* vcache;
+  float* kcache;        // [B, KV, cap, hd]
+  float* vcache;
+  // fuse != 0 (T == 1 only): rotate q and the new key with `table` (may be NULL: no RoPE) and append the
+  // new key / value, read from the row of q at columns k_off / v_off, to the cache at position *len
+  int fuse;
+  const float2* table;
+  uint32_t k_off, v_off;
   const int32_t* len;   // device: positions already cached before this step
   uint32_t T, KV, hd, cap;
   float scale;          // 1/sqrt(hd)
@@ -17,7 +22,7 @@ struct AttnParams {
 };
 
 int ruai_embed(ruai_ctx* c, const int32_t* ids, const float* embed, const float* wpe, const int32_t* len, uint32_t rows, uint32_t T, uint32_t d,
-               uint32_t vocab, float* x, int* err);
+               uint32_t vocab, float* x, int* err, float* sumsq);
 int ruai_rms_norm(ruai_ctx* c, const float* x, const float* w, uint32_t rows, uint32_t d, float eps, float* y);
 int ruai_layer_norm(ruai_ctx* c, const float* x, const float* w, const float* b, uint32_t rows, uint32_t d, float eps, float* y);
 int ruai_rope_table(ruai_ctx* c, const float* inv_freq, uint32_t half, uint32_t max_pos, float2* table);

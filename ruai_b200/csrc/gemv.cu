@@ -34,7 +34,13 @@ struct GemvParams {
   unsigned* counters;
   void* out;
   GemvEpilogue epi;
+  GemvPrologue pro;
 };
+
+__device__ __forceinline__ int32_t ordered_bits(float v) {  // total_cmp order as a signed integer
+  int32_t i = __float_as_int(v);
+  return i ^ (int32_t)(((uint32_t)(i >> 31)) >> 1);
+}
 
 // Byte `b` of `w` as an exact float: the byte becomes the low mantissa byte of
 // 2^23, then 2^23 + offset is subtracted.
@@ -59,6 +65,9 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
   constexpr int kStageChunks = kStageK / CK;    // chunks per shared-memory stage
   extern __shared__ __align__(16) float xs[];   // [MT][kStageK]
   __shared__ unsigned s_last;
+  __shared__ float s_rstd[MT];
+  __shared__ float s_red[kThreads / 32];
+  __shared__ int2 s_arg[kThreads / 32];
 
   const int tid = threadIdx.x;
   const uint32_t j = blockIdx.x * kThreads + tid;
@@ -88,6 +97,13 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
   }
   grid_dependency_wait();
   grid_launch_dependents();
+  const bool normed = p.pro.norm_w != nullptr;
+  if (normed && tid < MT) {
+    float ss = 0.0f;
+    if (tid < (int)rows)
+      for (uint32_t t = 0; t < p.pro.tiles; ++t) ss += p.pro.sumsq[(size_t)t * p.m + m0 + tid];
+    s_rstd[tid] = 1.0f / sqrtf(ss * (1.0f / (float)p.k) + p.pro.eps);
+  }
 
   for (uint32_t c0 = c_begin; c0 < c_end; c0 += kStageChunks) {
     const uint32_t c1 = min(c_end, c0 + kStageChunks);
@@ -97,7 +113,10 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
       const uint32_t r = idx / len, kk = idx - r * len;
       const uint32_t kidx = c0 * CK + kk;
       float v = 0.0f;
-      if (r < rows && kidx < p.k) v = load_as_f32(p.x, p.x_dtype, (size_t)(m0 + r) * p.x_ld + kidx);
+      if (r < rows && kidx < p.k) {
+        v = load_as_f32(p.x, p.x_dtype, (size_t)(m0 + r) * p.x_ld + kidx);
+        if (normed) v = v * s_rstd[r] * p.pro.norm_w[kidx];
+      }
       xs[r * kStageK + kk] = v;
     }
     __syncthreads();
@@ -193,10 +212,21 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
 #pragma unroll
     for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
     if (active) {
-      for (uint32_t s = 0; s < p.splits; ++s) {
+      if (MT == 1) {  // eight independent loads in flight, added in split order
+        for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+          float v[8];
 #pragma unroll
-        for (int r = 0; r < MT; ++r)
-          if (r < (int)rows) acc[r] += __ldcg(&p.partial[((size_t)s * p.m + m0 + r) * p.n + j]);
+          for (int u = 0; u < 8; ++u) v[u] = s0 + u < p.splits ? __ldcg(&p.partial[((size_t)(s0 + u) * p.m + m0) * p.n + j]) : 0.0f;
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (s0 + u < p.splits) acc[0] += v[u];
+        }
+      } else {
+        for (uint32_t s = 0; s < p.splits; ++s) {
+#pragma unroll
+          for (int r = 0; r < MT; ++r)
+            if (r < (int)rows) acc[r] += __ldcg(&p.partial[((size_t)s * p.m + m0 + r) * p.n + j]);
+        }
       }
     }
   }
@@ -205,6 +235,8 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
   const GemvEpilogue& e = p.epi;
   const float col_scale = (BITS == 8 && active) ? p.scale[j] : 1.0f;
   const float bias = (e.bias && active) ? e.bias[j] : 0.0f;
+  const int lane = tid & 31, warp = tid >> 5;
+  bool last_tile = false;
 #pragma unroll
   for (int r = 0; r < MT; ++r) {
     if (r >= (int)rows) break;  // uniform across the CTA
@@ -220,11 +252,72 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
         const size_t o = row * e.out_ld + (j >> 1);
         store_from_f32(p.out, e.out_dtype, o, e.resid ? e.resid[o] + h : h);
       }
-    } else if (active) {
+      continue;
+    }
+    if (active) {
       if (e.act == ACT_GELU) v = gelu_ref(v);
       const size_t o = row * e.out_ld + j;
       if (e.resid) v = e.resid[o] + v;
       store_from_f32(p.out, e.out_dtype, o, v);
+    }
+    if (e.sumsq) {  // sum of squares of this tile's part of the stored row, in a fixed order
+      float q = active ? v * v : 0.0f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xFFFFFFFFu, q, off);
+      __syncthreads();
+      if (lane == 0) s_red[warp] = q;
+      __syncthreads();
+      if (tid == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < kThreads / 32; ++w) t += s_red[w];
+        e.sumsq[(size_t)blockIdx.x * p.m + row] = t;
+      }
+    }
+    if (e.argmax_out) {  // best (value, column) of this tile; ties go to the larger column
+      int32_t bv = active ? ordered_bits(v) : INT32_MIN;
+      int32_t bj = active ? (int32_t)j : -1;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const int32_t ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+        const int32_t oj = __shfl_xor_sync(0xFFFFFFFFu, bj, off);
+        if (ov > bv || (ov == bv && oj > bj)) { bv = ov; bj = oj; }
+      }
+      __syncthreads();
+      if (lane == 0) s_arg[warp] = make_int2(bv, bj);
+      __syncthreads();
+      if (tid == 0) {
+        int2 b = s_arg[0];
+        for (int w = 1; w < kThreads / 32; ++w)
+          if (s_arg[w].x > b.x || (s_arg[w].x == b.x && s_arg[w].y > b.y)) b = s_arg[w];
+        e.argmax_slots[(size_t)blockIdx.x * p.m + row] = b;
+      }
+    }
+  }
+  if (e.argmax_out) {
+    // the last column tile to finish picks the winners
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned a = atomicAdd(e.argmax_counter, 1u);
+      s_last = a == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    last_tile = s_last != 0;
+    if (last_tile) {
+      __threadfence();
+      if (tid < (int)p.m) {
+        const volatile int* sl = (const volatile int*)e.argmax_slots;
+        int bv = INT32_MIN, bj = -1;
+        for (uint32_t t = 0; t < gridDim.x; ++t) {
+          const int v = sl[2 * ((size_t)t * p.m + tid)], jj = sl[2 * ((size_t)t * p.m + tid) + 1];
+          if (v > bv || (v == bv && jj > bj)) { bv = v; bj = jj; }
+        }
+        e.argmax_out[tid] = bj;
+      }
+      if (tid == 0) {
+        *e.argmax_counter = 0;
+        if (e.len_ptr) *e.len_ptr += e.len_add;
+      }
     }
   }
 }
@@ -279,12 +372,13 @@ cudaError_t launch_mt(ruai_ctx* c, const GemvParams& p, dim3 grid, int mt) {
 }  // namespace
 
 int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
-                     const GemvEpilogue& epi_in) {
+                     const GemvEpilogue& epi_in, const GemvPrologue& pro) {
   if (m == 0) return RUAI_OK;
   GemvEpilogue epi = epi_in;
   if (epi.act == ACT_SWIGLU && (w->n & 1)) return ruai_fail(c, RUAI_ERR_SHAPE, "SwiGLU epilogue needs an even column count, got %u", w->n);
   if (epi.out_ld == 0) epi.out_ld = epi.act == ACT_SWIGLU ? w->n / 2 : w->n;
   if (w->layout == QL_REFERENCE) {
+    if (pro.norm_w || epi.sumsq || epi.argmax_out) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "fused norm / argmax on a reference-layout weight");
     if (m > 65535) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "m too large");
     RUAI_CUDA(c, ruai_launch(c, gemv_int4_reference_layout_kernel, dim3((w->n + 127) / 128, m), dim3(128), 0, true, (const int8_t*)w->data,
                              (const float*)w->scale, x, x_dtype, x_ld, m, w->k, w->n, w->group, out, epi));
@@ -306,7 +400,9 @@ int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dt
   GemvParams p;
   p.w = (const uint4*)w->data; p.scale = w->scale; p.x = x; p.x_dtype = x_dtype; p.x_ld = x_ld;
   p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_split = cps; p.splits = splits;
-  p.out = out; p.epi = epi;
+  p.out = out; p.epi = epi; p.pro = pro;
+  if (epi.argmax_out && (row_tiles != 1 || epi.act == ACT_SWIGLU)) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "fused argmax needs m <= 16");
+  if (epi.sumsq && epi.act == ACT_SWIGLU) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "sum of squares with the SwiGLU epilogue");
   if (splits > 1) RUAI_TRY(ruai_ctx_reserve(c, (size_t)splits * m * w->n * sizeof(float), (size_t)col_tiles * row_tiles));
   p.partial = c->partial; p.counters = c->counters;
   const dim3 grid(col_tiles, splits, row_tiles);
@@ -398,6 +494,7 @@ RUAI_API int ruai_matmul_q_static(ruai_ctx* c, int x_dtype, const void* x, const
   p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_split = cps; p.splits = splits;
   p.out = out;
   p.epi = GemvEpilogue();
+  p.pro = GemvPrologue();
   p.epi.bias = bias;
   p.epi.out_dtype = x_dtype;
   p.epi.out_ld = w->n;

@@ -105,7 +105,7 @@ struct ruai_model {
   // cache state
   uint32_t B = 0, len = 0, cap = 0;
   // device state
-  DevBuf d_ids, d_len, d_err, x, xn, qkv, att, hbuf, xl, logits, attn_scratch, attn_counters;
+  DevBuf d_ids, d_len, d_err, x, xn, qkv, att, hbuf, xl, logits, attn_scratch, attn_counters, sumsq, arg_slots, arg_counter;
   uint32_t act_rows = 0, logit_rows = 0;
   // decode graph
   cudaGraphExec_t graph = nullptr;
@@ -435,6 +435,12 @@ int ensure_activations(ruai_model* m, uint32_t rows, uint32_t out_rows, uint32_t
     RUAI_TRY(m->att.alloc(c, (size_t)rows * m->Hl * m->hd * sizeof(float)));
     RUAI_TRY(m->hbuf.alloc(c, (size_t)rows * m->fl * sizeof(float)));
     RUAI_TRY(m->xl.alloc(c, (size_t)rows * m->d * sizeof(float)));
+    RUAI_TRY(m->sumsq.alloc(c, (size_t)rows * ((m->d + kGemvTileCols - 1) / kGemvTileCols) * sizeof(float)));
+    RUAI_TRY(m->arg_slots.alloc(c, (size_t)16 * ((m->Vl + kGemvTileCols - 1) / kGemvTileCols) * sizeof(int2)));
+    if (!m->arg_counter.p) {
+      RUAI_TRY(m->arg_counter.alloc(c, sizeof(unsigned)));
+      RUAI_CUDA(c, cudaMemsetAsync(m->arg_counter.p, 0, sizeof(unsigned), c->stream));
+    }
     m->act_rows = rows;
     drop_graph(m);
   }
@@ -469,23 +475,39 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
   ruai_ctx* c = m->ctx;
   const uint32_t rows = B * T, d = m->d, hd = m->hd;
   const uint32_t nql = m->Hl * hd, nkvl = m->KVl * hd, nqkv = nql + 2 * nkvl, rep = m->Hl / m->KVl;
-  const int32_t* len = m->d_len.as<int32_t>();
+  int32_t* len = m->d_len.as<int32_t>();
   float *x = m->x.as<float>(), *xn = m->xn.as<float>(), *qkv = m->qkv.as<float>(), *att = m->att.as<float>(), *hb = m->hbuf.as<float>();
   const uint32_t splits = attn_splits(m, B, T);
   const bool tp = m->world > 1;
+  // RMSNorm rides in the prologue of the GEMV that consumes it: the producer of x (embedding, o_proj, down_proj)
+  // leaves per-tile sums of squares.  LayerNorm (GPT-2) and the sharded model (x is produced by the exchange
+  // kernel) keep the standalone norm kernels.
+  const bool fold = m->llama && !tp && (m->bits == 8 || m->group == 32);  // the chunk-layout kernel only
+  float* ss = fold ? m->sumsq.as<float>() : nullptr;
+  const uint32_t d_tiles = (d + kGemvTileCols - 1) / kGemvTileCols;
+  uint32_t ss_tiles = 1;
   RUAI_TRY(ruai_embed(c, m->d_ids.as<int32_t>(), m->embed.as<float>(), m->llama ? nullptr : m->wpe.as<float>(), len, rows, T, d, m->V, x,
-                      m->d_err.as<int>()));
+                      m->d_err.as<int>(), ss));
   for (uint32_t l = 0; l < m->L; ++l) {
     Layer& Ly = m->layers[l];
-    if (m->llama) RUAI_TRY(ruai_rms_norm(c, x, Ly.n1w.as<float>(), rows, d, m->eps, xn));
-    else RUAI_TRY(ruai_layer_norm(c, x, Ly.n1w.as<float>(), Ly.n1b.as<float>(), rows, d, 1e-5f, xn));
     GemvEpilogue e;
     e.bias = Ly.qkv.bias.as<float>();
-    RUAI_TRY(ruai_gemv_launch(c, Ly.qkv.w, xn, RUAI_F32, d, rows, qkv, e));
-    RUAI_TRY(ruai_rope_kv(c, qkv, nqkv, nql, nql + nkvl, m->llama ? m->rope_table.as<float2>() : nullptr, len, rows, T, m->Hl, m->KVl, hd, m->cap,
-                          Ly.kc.as<float>(), Ly.vc.as<float>()));
+    if (fold) {
+      GemvPrologue pr;
+      pr.norm_w = Ly.n1w.as<float>(); pr.sumsq = ss; pr.tiles = ss_tiles; pr.eps = m->eps;
+      RUAI_TRY(ruai_gemv_launch(c, Ly.qkv.w, x, RUAI_F32, d, rows, qkv, e, pr));
+    } else {
+      if (m->llama) RUAI_TRY(ruai_rms_norm(c, x, Ly.n1w.as<float>(), rows, d, m->eps, xn));
+      else RUAI_TRY(ruai_layer_norm(c, x, Ly.n1w.as<float>(), Ly.n1b.as<float>(), rows, d, 1e-5f, xn));
+      RUAI_TRY(ruai_gemv_launch(c, Ly.qkv.w, xn, RUAI_F32, d, rows, qkv, e));
+    }
+    const float2* table = m->llama ? m->rope_table.as<float2>() : nullptr;
+    const bool fuse = T == 1;  // rotate + append inside the attention kernel
+    if (!fuse)
+      RUAI_TRY(ruai_rope_kv(c, qkv, nqkv, nql, nql + nkvl, table, len, rows, T, m->Hl, m->KVl, hd, m->cap, Ly.kc.as<float>(), Ly.vc.as<float>()));
     AttnParams ap;
     ap.q = qkv; ap.q_ld = nqkv; ap.kcache = Ly.kc.as<float>(); ap.vcache = Ly.vc.as<float>(); ap.len = len;
+    ap.fuse = fuse ? 1 : 0; ap.table = table; ap.k_off = nql; ap.v_off = nql + nkvl;
     ap.T = T; ap.KV = m->KVl; ap.hd = hd; ap.cap = m->cap; ap.scale = 1.0f / sqrtf((float)hd);
     ap.out = att; ap.out_ld = nql; ap.scratch = m->attn_scratch.as<float>(); ap.counters = m->attn_counters.as<unsigned>();
     RUAI_TRY(ruai_attention(c, ap, B, rep, splits));
@@ -493,21 +515,30 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
     eo.bias = Ly.o.bias.as<float>();
     if (!tp) {
       eo.resid = x;
+      eo.sumsq = ss;
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, nql, rows, x, eo));
     } else {
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, nql, rows, m->tp.local_partial(), eo));
       RUAI_TRY(ruai_tp_allreduce_add(c, &m->tp, x, rows, d, m->d_err.as<int>()));
     }
-    if (m->llama) RUAI_TRY(ruai_rms_norm(c, x, Ly.n2w.as<float>(), rows, d, m->eps, xn));
-    else RUAI_TRY(ruai_layer_norm(c, x, Ly.n2w.as<float>(), Ly.n2b.as<float>(), rows, d, 1e-5f, xn));
+    ss_tiles = d_tiles;
     GemvEpilogue eu;
     eu.bias = Ly.up.bias.as<float>();
     eu.act = m->llama ? ACT_SWIGLU : ACT_GELU;
-    RUAI_TRY(ruai_gemv_launch(c, Ly.up.w, xn, RUAI_F32, d, rows, hb, eu));
+    if (fold) {
+      GemvPrologue pr;
+      pr.norm_w = Ly.n2w.as<float>(); pr.sumsq = ss; pr.tiles = ss_tiles; pr.eps = m->eps;
+      RUAI_TRY(ruai_gemv_launch(c, Ly.up.w, x, RUAI_F32, d, rows, hb, eu, pr));
+    } else {
+      if (m->llama) RUAI_TRY(ruai_rms_norm(c, x, Ly.n2w.as<float>(), rows, d, m->eps, xn));
+      else RUAI_TRY(ruai_layer_norm(c, x, Ly.n2w.as<float>(), Ly.n2b.as<float>(), rows, d, 1e-5f, xn));
+      RUAI_TRY(ruai_gemv_launch(c, Ly.up.w, xn, RUAI_F32, d, rows, hb, eu));
+    }
     GemvEpilogue ed;
     ed.bias = Ly.down.bias.as<float>();
     if (!tp) {
       ed.resid = x;
+      ed.sumsq = ss;
       RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, rows, x, ed));
     } else {
       RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, rows, m->tp.local_partial(), ed));
@@ -516,19 +547,33 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
   }
   const float* hx = x;
   uint32_t out_rows = rows;
-  if (!all_positions && T > 1) {
+  const bool last_only = !all_positions && T > 1;
+  if (last_only) {
     RUAI_TRY(ruai_take_last_rows(c, x, B, T, d, m->xl.as<float>()));
     hx = m->xl.as<float>();
     out_rows = B;
   }
-  if (m->llama) RUAI_TRY(ruai_rms_norm(c, hx, m->final_w.as<float>(), out_rows, d, m->eps, xn));
-  else RUAI_TRY(ruai_layer_norm(c, hx, m->final_w.as<float>(), m->final_b.as<float>(), out_rows, d, 1e-5f, xn));
   GemvEpilogue eh;
-  RUAI_TRY(ruai_gemv_launch(c, m->head.w, xn, RUAI_F32, d, out_rows, m->logits.as<float>(), eh));
-  RUAI_TRY(ruai_add_scalar(c, m->d_len.as<int32_t>(), (int32_t)T));
-  if (want_argmax) {
-    if (!tp) RUAI_TRY(ruai_argmax(c, m->logits.as<float>(), m->Vl, B, m->Vl, m->d_ids.as<int32_t>(), 0));
-    else RUAI_TRY(ruai_tp_argmax(c, &m->tp, m->logits.as<float>(), m->Vl, B, m->rank * m->Vl, m->d_ids.as<int32_t>(), m->d_err.as<int>()));
+  const bool fused_pick = want_argmax && !tp && out_rows <= 16;
+  if (fused_pick) {
+    eh.argmax_out = m->d_ids.as<int32_t>(); eh.argmax_slots = m->arg_slots.as<int2>(); eh.argmax_counter = m->arg_counter.as<unsigned>();
+    eh.len_ptr = len; eh.len_add = (int32_t)T;
+  }
+  if (fold && !last_only) {
+    GemvPrologue pr;
+    pr.norm_w = m->final_w.as<float>(); pr.sumsq = ss; pr.tiles = ss_tiles; pr.eps = m->eps;
+    RUAI_TRY(ruai_gemv_launch(c, m->head.w, hx, RUAI_F32, d, out_rows, m->logits.as<float>(), eh, pr));
+  } else {
+    if (m->llama) RUAI_TRY(ruai_rms_norm(c, hx, m->final_w.as<float>(), out_rows, d, m->eps, xn));
+    else RUAI_TRY(ruai_layer_norm(c, hx, m->final_w.as<float>(), m->final_b.as<float>(), out_rows, d, 1e-5f, xn));
+    RUAI_TRY(ruai_gemv_launch(c, m->head.w, xn, RUAI_F32, d, out_rows, m->logits.as<float>(), eh));
+  }
+  if (!fused_pick) {
+    RUAI_TRY(ruai_add_scalar(c, len, (int32_t)T));
+    if (want_argmax) {
+      if (!tp) RUAI_TRY(ruai_argmax(c, m->logits.as<float>(), m->Vl, B, m->Vl, m->d_ids.as<int32_t>(), 0));
+      else RUAI_TRY(ruai_tp_argmax(c, &m->tp, m->logits.as<float>(), m->Vl, B, m->rank * m->Vl, m->d_ids.as<int32_t>(), m->d_err.as<int>()));
+    }
   }
   return RUAI_OK;
 }
@@ -616,7 +661,7 @@ RUAI_API int ruai_model_destroy(ruai_model* m) {
   }
   if (m->head.w) ruai_qweight_free(m->head.w);
   for (DevBuf* b : {&m->embed, &m->wpe, &m->final_w, &m->final_b, &m->rope_table, &m->d_ids, &m->d_len, &m->d_err, &m->x, &m->xn, &m->qkv, &m->att,
-                    &m->hbuf, &m->xl, &m->logits, &m->attn_scratch, &m->attn_counters})
+                    &m->hbuf, &m->xl, &m->logits, &m->attn_scratch, &m->attn_counters, &m->sumsq, &m->arg_slots, &m->arg_counter})
     b->release();
   delete m;
   return RUAI_OK;
@@ -745,6 +790,13 @@ RUAI_API int ruai_model_cache_len(const ruai_model* m, uint32_t* len, uint32_t* 
   if (len) *len = m->len;
   if (cap) *cap = m->cap;
   return RUAI_OK;
+}
+
+RUAI_API int ruai_model_cache_reserve(ruai_model* m, uint32_t B, uint32_t positions) {
+  if (!m) return ruai_fail(nullptr, RUAI_ERR_ARG, "model is NULL");
+  if (positions > m->max_pos) return model_fail(m, RUAI_ERR_SHAPE, "context %u exceeds the maximum %u", positions, m->max_pos);
+  DeviceGuard g(m->ctx->ordinal);
+  return ensure_cache(m, B, positions);
 }
 
 RUAI_API int ruai_model_cache_assume(ruai_model* m, uint32_t B, uint32_t len) {

@@ -317,6 +317,9 @@ class _Model:
         self.dev.check(self.dev.L.ruai_model_decode_step(self.h, ids_dev, B, out.ctypes.data_as(C.c_void_p) if fetch else None))
         return out
 
+    def cache_reserve(self, B, positions):
+        self.dev.check(self.dev.L.ruai_model_cache_reserve(self.h, B, positions))
+
     def cache_assume(self, B, length):
         self.dev.check(self.dev.L.ruai_model_cache_assume(self.h, B, length))
 
