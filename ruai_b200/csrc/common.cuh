@@ -30,6 +30,10 @@ struct ruai_ctx {
   size_t counters_n = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool use_pdl = true;  // programmatic dependent launch between consecutive kernels
+  bool use_bulk = true; // bulk-copy staged GEMV (gemv_bulk.cu) where the weight allows it
+  bool use_tc = true;   // tensor-core GEMV (gemv_tc.cu) for int4 group-32 weights and up to 4 rows
+  void* prof = nullptr;  // debug: device buffer for cycle stamps (set by ruai_debug_set_prof)
+  int* status = nullptr;  // device word: 0 ok, 3 = a bounded wait inside a kernel ran out
   unsigned long long launches = 0;
 };
 
@@ -165,7 +169,18 @@ struct GemvPrologue {
   float eps = 0.0f;
 };
 
-constexpr int kGemvTileCols = 256;  // columns per GEMV CTA, and per sumsq / argmax tile
+constexpr int kGemvTileCols = 256;      // columns per CTA of gemv.cu, and per sumsq / argmax tile it writes
+constexpr int kGemvBulkTileCols = 128;  // the same for gemv_bulk.cu
+// Number of sumsq / argmax tiles a GEMV over `w` writes (depends on which kernel serves it).
+uint32_t ruai_gemv_tiles(const ruai_ctx* ctx, const ruai_qweight* w);
+bool ruai_gemv_bulk_eligible(const ruai_qweight* w);
+int ruai_gemv_bulk_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
+                          const GemvEpilogue& epi, const GemvPrologue& pro);
+bool ruai_gemv_tc_eligible(const ruai_qweight* w, uint32_t m);
+int ruai_gemv_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
+                        const GemvEpilogue& epi, const GemvPrologue& pro);
+// Reads and clears the context's device status word (synchronizes the stream).
+int ruai_ctx_check_status(ruai_ctx* ctx);
 
 // y = x @ W for m rows; x is [m, k] (row stride x_ld) in x_dtype.
 int ruai_gemv_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,

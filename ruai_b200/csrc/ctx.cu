@@ -54,6 +54,14 @@ RUAI_API int ruai_ctx_create(int ordinal, void* stream_or_null, ruai_ctx** out) 
   cudaEventCreate(&c->ev1);
   const char* pdl = getenv("RUAI_B200_PDL");
   if (pdl && pdl[0] == '0') c->use_pdl = false;
+  const char* bulk = getenv("RUAI_B200_BULK");
+  if (bulk && bulk[0] == '0') c->use_bulk = false;
+  const char* tc = getenv("RUAI_B200_TC");
+  if (tc && tc[0] == '0') c->use_tc = false;
+  if (cudaMalloc(&c->status, sizeof(int)) != cudaSuccess || cudaMemset(c->status, 0, sizeof(int)) != cudaSuccess) {
+    delete c;
+    return ruai_fail(nullptr, RUAI_ERR_CUDA, "cannot allocate the status word");
+  }
   int rc = ruai_ctx_reserve(c, 8u << 20, 4096);
   if (rc != RUAI_OK) { g_ruai_global_err = c->err; delete c; return rc; }
   *out = c;
@@ -66,6 +74,7 @@ RUAI_API int ruai_ctx_destroy(ruai_ctx* c) {
   cudaStreamSynchronize(c->stream);
   cudaFree(c->partial);
   cudaFree(c->counters);
+  cudaFree(c->status);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->stream);
@@ -95,10 +104,19 @@ int ruai_ctx_reserve(ruai_ctx* c, size_t partial_bytes, size_t counters) {
   return RUAI_OK;
 }
 
+int ruai_ctx_check_status(ruai_ctx* c) {
+  int st = 0;
+  RUAI_CUDA(c, cudaMemcpyAsync(&st, c->status, sizeof st, cudaMemcpyDeviceToHost, c->stream));
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  if (st == 0) return RUAI_OK;
+  cudaMemsetAsync(c->status, 0, sizeof(int), c->stream);
+  return ruai_fail(c, RUAI_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (status %d); results of that launch are invalid", st);
+}
+
 RUAI_API int ruai_ctx_synchronize(ruai_ctx* c) {
   if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
-  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
-  return RUAI_OK;
+  DeviceGuard g(c->ordinal);
+  return ruai_ctx_check_status(c);
 }
 
 RUAI_API int ruai_malloc(ruai_ctx* c, size_t bytes, void** out) {
@@ -144,5 +162,11 @@ RUAI_API int ruai_timer_stop_ms(ruai_ctx* c, float* ms) {
   RUAI_CUDA(c, cudaEventRecord(c->ev1, c->stream));
   RUAI_CUDA(c, cudaEventSynchronize(c->ev1));
   RUAI_CUDA(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
+  return RUAI_OK;
+}
+
+// Debug hook (not declared in the public header): kernels that support it write cycle stamps here.
+RUAI_API int ruai_debug_set_prof(ruai_ctx* c, void* dev_buf) {
+  c->prof = dev_buf;
   return RUAI_OK;
 }

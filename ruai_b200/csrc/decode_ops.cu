@@ -11,6 +11,7 @@
 #include <algorithm>
 
 #include "decode_ops.cuh"
+#include "pipeline.cuh"
 
 namespace {
 
@@ -160,25 +161,58 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 // (functional.rs:197-204) on q and on the new key and appends the new key / value to the
 // cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
 template <int EPL, int REP>
-__global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
-  constexpr int kWarps = 4, kKeys = 4;
-  extern __shared__ float sm[];  // q [REP][hd] | new k [hd] | new v [hd] | merge [kWarps][REP][hd + 2]
+__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
+  constexpr int kWarps = kAttnThreads / 32;
+  extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs [kWarps][REP][32] | merge
+  __shared__ __align__(8) uint64_t kv_bar;
   __shared__ unsigned s_last;
   const uint32_t hd = p.hd, half = hd / 2;
-  float* qs = sm;
-  float* knew = sm + REP * hd;
+  float* ks = sm;
+  float* vs = ks + (size_t)kAttnChunkKeys * hd;
+  float* qs = vs + (size_t)kAttnChunkKeys * hd;
+  float* knew = qs + REP * hd;
   float* vnew = knew + hd;
-  float* mg = vnew + hd;
+  float* probs = vnew + hd;
+  float* mg = probs + kWarps * REP * 32;
   const uint32_t bk = blockIdx.x, b = bk / p.KV, kvh = bk % p.KV, t = blockIdx.y, split = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
+  float* vbase = p.vcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
+  if (threadIdx.x == 0) {
+    pipe::mbar_init(&kv_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  uint32_t past = 0, pos = 0, n_keys = 0, n_cached = 0, k0 = 0, k1 = 0;
+  auto plan = [&]() {
+    past = (uint32_t)*p.len;
+    pos = past + t;
+    n_keys = pos + 1;  // causal_mask_offset, functional.rs:238-247
+    n_cached = p.fuse ? n_keys - 1 : n_keys;
+    const uint32_t per = (n_cached + gridDim.z - 1) / gridDim.z;
+    k0 = min(n_cached, split * per);
+    k1 = min(n_cached, k0 + per);
+  };
+  // One bulk copy each brings a chunk of this CTA's keys and values (contiguous rows of the cache) into shared memory.
+  auto fetch_chunk = [&](uint32_t c0) {
+    const uint32_t nk = min((uint32_t)kAttnChunkKeys, k1 - c0);
+    const uint32_t bytes = nk * hd * 4u;
+    pipe::mbar_expect_tx(&kv_bar, 2u * bytes);
+    pipe::bulk_load(ks, kbase + (size_t)c0 * hd, bytes, &kv_bar);
+    pipe::bulk_load(vs, vbase + (size_t)c0 * hd, bytes, &kv_bar);
+  };
+  // In the fused single-token step the cached rows were written by earlier steps, and the position by the
+  // previous step's last kernel: both are safe to read while the predecessor (the q/k/v GEMV) still runs.
+  if (p.fuse) {
+    plan();
+    if (threadIdx.x == 0 && k1 > k0) fetch_chunk(k0);
+  }
   grid_dependency_wait();
   grid_launch_dependents();
-  const uint32_t past = (uint32_t)*p.len;
-  const uint32_t pos = past + t;
-  const uint32_t n_keys = pos + 1;  // causal_mask_offset, functional.rs:238-247
-  const uint32_t n_cached = p.fuse ? n_keys - 1 : n_keys;
-  const uint32_t per = (n_cached + gridDim.z - 1) / gridDim.z;
-  const uint32_t k0 = min(n_cached, split * per), k1 = min(n_cached, k0 + per);
+  if (!p.fuse) {
+    plan();
+    if (threadIdx.x == 0 && k1 > k0) fetch_chunk(k0);
+  }
   const bool owns_new = p.fuse && split == gridDim.z - 1;
   const float* row = p.q + (size_t)(b * p.T + t) * p.q_ld;
   const float* qrow = row + (size_t)kvh * REP * hd;
@@ -193,8 +227,6 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     }
     qs[i] = v;
   }
-  float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
-  float* vbase = p.vcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
   if (owns_new) {
     const float* kr = row + p.k_off + (size_t)kvh * hd;
     const float* vr = row + p.v_off + (size_t)kvh * hd;
@@ -222,75 +254,104 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i) o[r][i] = 0.0f;
   }
-  // one online-softmax update with up to kKeys keys whose rows are in registers
-  auto update = [&](const float (&kv)[kKeys][EPL], const float (&vv)[kKeys][EPL], int nk) {
+  float* ps = probs + (size_t)warp * REP * 32;  // this warp's probabilities of a 32-key block: [REP][32]
+  // A warp takes 32 keys at a time.  Scores: one key per lane, the lane walks its own key row (the 32 rows
+  // of a block are contiguous in the cache, so every byte of the lines it touches is used).  No reduction
+  // across lanes is needed for the dot products; the block maximum and sum cost ten shuffles per head.
+  // Weighted values: one output element per lane, the rows of V are read coalesced.
+  uint32_t phase = 0;
+  bool ok = true;
+  for (uint32_t c0 = k0; c0 < k1; c0 += kAttnChunkKeys) {
+    if (c0 != k0) {
+      __syncthreads();  // everyone is done with the previous chunk
+      if (threadIdx.x == 0) fetch_chunk(c0);
+    }
+    if (!pipe::mbar_wait(&kv_bar, phase & 1u)) { ok = false; break; }
+    ++phase;
+    const uint32_t c1 = min(k1, c0 + kAttnChunkKeys);
+    for (uint32_t blk = c0 + warp * 32; blk < c1; blk += kWarps * 32) {
+      const uint32_t key = blk + lane;
+      const bool valid = key < c1;
+      float sc[REP];
 #pragma unroll
-    for (int r = 0; r < REP; ++r) {
-      float s[kKeys];
+      for (int r = 0; r < REP; ++r) sc[r] = 0.0f;
+      // lane = key; the lane starts at its own 16-byte column so that the 32 lanes hit different banks
+      const uint32_t nq4 = hd / 4;
+      const float4* krow = reinterpret_cast<const float4*>(ks + (size_t)(valid ? key - c0 : 0) * hd);
+      for (uint32_t it = 0; it < nq4; ++it) {
+        uint32_t cidx = it + lane;
+        cidx = cidx >= nq4 ? cidx % nq4 : cidx;
+        const float4 kk = krow[cidx];
 #pragma unroll
-      for (int u = 0; u < kKeys; ++u) {
-        float a = 0.0f;
+        for (int r = 0; r < REP; ++r) {
+          const float4 qv = *reinterpret_cast<const float4*>(qs + r * hd + 4 * cidx);
+          sc[r] = fmaf(qv.x, kk.x, sc[r]);
+          sc[r] = fmaf(qv.y, kk.y, sc[r]);
+          sc[r] = fmaf(qv.z, kk.z, sc[r]);
+          sc[r] = fmaf(qv.w, kk.w, sc[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        const float sv = valid ? sc[r] * p.scale : -INFINITY;
+        float bm = sv;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
+        const float nm = fmaxf(mx[r], bm);   // the block has at least one valid key, so nm is finite
+        const float c = expf(mx[r] - nm);    // exp(-inf) = 0 on the first block
+        const float pr = valid ? expf(sv - nm) : 0.0f;
+        float bs = pr;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) bs += __shfl_xor_sync(0xFFFFFFFFu, bs, off);
+        l[r] = l[r] * c + bs;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[r][i] *= c;
+        mx[r] = nm;
+        ps[r * 32 + lane] = pr;
+      }
+      __syncwarp();
+      const uint32_t nk = min(32u, c1 - blk);
+      for (uint32_t kk0 = 0; kk0 < nk; ++kk0) {
+        float vv[EPL];
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
           const uint32_t e = lane + 32 * i;
-          if (e < hd) a = fmaf(qs[r * hd + e], kv[u][i], a);
+          vv[i] = e < hd ? vs[(size_t)(blk - c0 + kk0) * hd + e] : 0.0f;
         }
-        s[u] = a;
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+          const float pr = ps[r * 32 + kk0];
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) o[r][i] = fmaf(pr, vv[i], o[r][i]);
+        }
+      }
+      __syncwarp();
+    }
+  }
+  if (!ok && p.status && threadIdx.x == 0) atomicExch(p.status, 3);
+  if (owns_new && warp == 0) {  // the token's own key and value, from shared memory
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float a = 0.0f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const uint32_t e = lane + 32 * i;
+        if (e < hd) a = fmaf(qs[r * hd + e], knew[e], a);
       }
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
+      for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, off);
+      const float sv = a * p.scale;
+      const float nm = fmaxf(mx[r], sv);
+      const float c = expf(mx[r] - nm);
+      const float pr = expf(sv - nm);
+      l[r] = l[r] * c + pr;
 #pragma unroll
-        for (int u = 0; u < kKeys; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], off);
+      for (int i = 0; i < EPL; ++i) {
+        const uint32_t e = lane + 32 * i;
+        o[r][i] = o[r][i] * c + (e < hd ? pr * vnew[e] : 0.0f);
       }
-      float nm = mx[r];
-#pragma unroll
-      for (int u = 0; u < kKeys; ++u) {
-        s[u] = u < nk ? s[u] * p.scale : -INFINITY;
-        nm = fmaxf(nm, s[u]);
-      }
-      const float c = expf(mx[r] - nm);  // exp(-inf) = 0 on the first keys
-      float ls = l[r] * c;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) o[r][i] *= c;
-#pragma unroll
-      for (int u = 0; u < kKeys; ++u) {
-        const float pr = expf(s[u] - nm);
-        ls += pr;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) o[r][i] = fmaf(pr, vv[u][i], o[r][i]);
-      }
-      l[r] = ls;
       mx[r] = nm;
     }
-  };
-  for (uint32_t key = k0 + warp * kKeys; key < k1; key += kWarps * kKeys) {
-    float kv[kKeys][EPL], vv[kKeys][EPL];
-    const int nk = (int)min((uint32_t)kKeys, k1 - key);
-#pragma unroll
-    for (int u = 0; u < kKeys; ++u) {
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        const uint32_t e = lane + 32 * i;
-        const bool ok = u < nk && e < hd;
-        kv[u][i] = ok ? __ldcs(kbase + (size_t)(key + u) * hd + e) : 0.0f;
-        vv[u][i] = ok ? __ldcs(vbase + (size_t)(key + u) * hd + e) : 0.0f;
-      }
-    }
-    update(kv, vv, nk);
-  }
-  if (owns_new && warp == 0) {
-    float kv[kKeys][EPL], vv[kKeys][EPL];
-#pragma unroll
-    for (int u = 0; u < kKeys; ++u) {
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        const uint32_t e = lane + 32 * i;
-        const bool ok = u == 0 && e < hd;
-        kv[u][i] = ok ? knew[e] : 0.0f;
-        vv[u][i] = ok ? vnew[e] : 0.0f;
-      }
-    }
-    update(kv, vv, 1);
   }
   // ---- merge the warps ----
   const uint32_t stride = hd + 2;
@@ -439,14 +500,25 @@ __global__ void take_last_rows_kernel(const float* __restrict__ x, uint32_t T, u
   for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) y[(size_t)blockIdx.x * d + i] = src[i];
 }
 
+template <int EPL, int REP>
+cudaError_t launch_attn(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem) {
+  static bool attr_done[64] = {};
+  if (!attr_done[c->ordinal & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel<EPL, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_done[c->ordinal & 63] = true;
+  }
+  return ruai_launch(c, attention_kernel<EPL, REP>, grid, dim3(kAttnThreads), smem, true, p);
+}
+
 template <int EPL>
 cudaError_t launch_attn_rep(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem, uint32_t rep) {
   switch (rep) {
-    case 1: return ruai_launch(c, attention_kernel<EPL, 1>, grid, dim3(128), smem, true, p);
-    case 2: return ruai_launch(c, attention_kernel<EPL, 2>, grid, dim3(128), smem, true, p);
-    case 3: return ruai_launch(c, attention_kernel<EPL, 3>, grid, dim3(128), smem, true, p);
-    case 4: return ruai_launch(c, attention_kernel<EPL, 4>, grid, dim3(128), smem, true, p);
-    case 8: return ruai_launch(c, attention_kernel<EPL, 8>, grid, dim3(128), smem, true, p);
+    case 1: return launch_attn<EPL, 1>(c, p, grid, smem);
+    case 2: return launch_attn<EPL, 2>(c, p, grid, smem);
+    case 3: return launch_attn<EPL, 3>(c, p, grid, smem);
+    case 4: return launch_attn<EPL, 4>(c, p, grid, smem);
+    case 8: return launch_attn<EPL, 8>(c, p, grid, smem);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -485,9 +557,11 @@ int ruai_rope_kv(ruai_ctx* c, float* qkv, uint32_t qkv_ld, uint32_t k_off, uint3
 }
 
 int ruai_attention(ruai_ctx* c, const AttnParams& p, uint32_t B, uint32_t rep, uint32_t splits) {
+  if (p.hd % 4) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4", p.hd);
   const uint32_t epl = (p.hd + 31) / 32;
-  const size_t merge = std::max<size_t>(4 * (size_t)rep * (p.hd + 2), 128 * (size_t)rep + rep);
-  const size_t smem = ((size_t)rep * p.hd + 2 * (size_t)p.hd + merge) * sizeof(float);
+  constexpr size_t nw = kAttnThreads / 32;
+  const size_t merge = std::max<size_t>(nw * (size_t)rep * (p.hd + 2), 128 * (size_t)rep + rep);
+  const size_t smem = (2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + nw * (size_t)rep * 32 + merge) * sizeof(float);
   const dim3 grid(B * p.KV, p.T, splits);
   cudaError_t e;
   if (epl <= 1) e = launch_attn_rep<1>(c, p, grid, smem, rep);

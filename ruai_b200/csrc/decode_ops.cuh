@@ -2,6 +2,9 @@
 #pragma once
 #include "common.cuh"
 
+constexpr int kAttnThreads = 64;     // two warps per CTA, one 32-key block each per chunk
+constexpr int kAttnChunkKeys = 64;  // keys (and values) staged in shared memory at a time
+
 struct AttnParams {
   const float* q;       // [B*T, q_ld]; the rep query heads of KV head g at column g*rep*hd
   uint32_t q_ld;
@@ -19,6 +22,7 @@ struct AttnParams {
   uint32_t out_ld;
   float* scratch;       // split merge: [B*KV*T][splits][rep][hd+2]
   unsigned* counters;   // [B*KV*T], zero between launches
+  int* status;          // context status word (bounded waits)
 };
 
 int ruai_embed(ruai_ctx* c, const int32_t* ids, const float* embed, const float* wpe, const int32_t* len, uint32_t rows, uint32_t T, uint32_t d,

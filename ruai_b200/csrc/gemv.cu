@@ -374,6 +374,8 @@ cudaError_t launch_mt(ruai_ctx* c, const GemvParams& p, dim3 grid, int mt) {
 int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                      const GemvEpilogue& epi_in, const GemvPrologue& pro) {
   if (m == 0) return RUAI_OK;
+  if (c->use_bulk && c->use_tc && ruai_gemv_tc_eligible(w, m)) return ruai_gemv_tc_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
+  if (c->use_bulk && ruai_gemv_bulk_eligible(w)) return ruai_gemv_bulk_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   GemvEpilogue epi = epi_in;
   if (epi.act == ACT_SWIGLU && (w->n & 1)) return ruai_fail(c, RUAI_ERR_SHAPE, "SwiGLU epilogue needs an even column count, got %u", w->n);
   if (epi.out_ld == 0) epi.out_ld = epi.act == ACT_SWIGLU ? w->n / 2 : w->n;
@@ -409,6 +411,11 @@ int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dt
   cudaError_t e = w->bits == 8 ? launch_mt<8>(c, p, grid, mt) : launch_mt<4>(c, p, grid, mt);
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(e));
   return RUAI_OK;
+}
+
+uint32_t ruai_gemv_tiles(const ruai_ctx* c, const ruai_qweight* w) {
+  const uint32_t t = c->use_bulk && ruai_gemv_bulk_eligible(w) ? kGemvBulkTileCols : kGemvTileCols;
+  return (w->n + t - 1) / t;
 }
 
 // Backend::matmul_int8 / matmul_int4 (mod.rs:675-704) + Linear::forward's bias (layers.rs:184-189).

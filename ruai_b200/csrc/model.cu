@@ -415,12 +415,10 @@ int ensure_cache(ruai_model* m, uint32_t B, uint32_t need) {
 
 uint32_t attn_splits(const ruai_model* m, uint32_t B, uint32_t T) {
   if (T > 1) return 1;
-  // enough CTAs to fill the machine, but at least 64 keys per split at full capacity
-  const uint32_t base = B * m->KVl;
-  uint32_t s = (uint32_t)(2 * m->ctx->sm_count + base - 1) / base;
-  const uint32_t by_len = (m->cap + 63) / 64;
-  s = std::min(s, std::max(1u, by_len));
-  return std::max(1u, std::min(s, 64u));
+  // one chunk of 64 keys per CTA where the capacity allows it (a single round trip to memory per CTA)
+  const uint32_t by_len = (m->cap + kAttnChunkKeys - 1) / kAttnChunkKeys;
+  (void)B;
+  return std::max(1u, std::min(by_len, 64u));
 }
 
 int ensure_activations(ruai_model* m, uint32_t rows, uint32_t out_rows, uint32_t B, uint32_t T) {
@@ -435,8 +433,8 @@ int ensure_activations(ruai_model* m, uint32_t rows, uint32_t out_rows, uint32_t
     RUAI_TRY(m->att.alloc(c, (size_t)rows * m->Hl * m->hd * sizeof(float)));
     RUAI_TRY(m->hbuf.alloc(c, (size_t)rows * m->fl * sizeof(float)));
     RUAI_TRY(m->xl.alloc(c, (size_t)rows * m->d * sizeof(float)));
-    RUAI_TRY(m->sumsq.alloc(c, (size_t)rows * ((m->d + kGemvTileCols - 1) / kGemvTileCols) * sizeof(float)));
-    RUAI_TRY(m->arg_slots.alloc(c, (size_t)16 * ((m->Vl + kGemvTileCols - 1) / kGemvTileCols) * sizeof(int2)));
+    RUAI_TRY(m->sumsq.alloc(c, (size_t)rows * ((m->d + kGemvBulkTileCols - 1) / kGemvBulkTileCols) * sizeof(float)));
+    RUAI_TRY(m->arg_slots.alloc(c, (size_t)16 * ((m->Vl + kGemvBulkTileCols - 1) / kGemvBulkTileCols) * sizeof(int2)));
     if (!m->arg_counter.p) {
       RUAI_TRY(m->arg_counter.alloc(c, sizeof(unsigned)));
       RUAI_CUDA(c, cudaMemsetAsync(m->arg_counter.p, 0, sizeof(unsigned), c->stream));
@@ -484,7 +482,7 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
   // kernel) keep the standalone norm kernels.
   const bool fold = m->llama && !tp && (m->bits == 8 || m->group == 32);  // the chunk-layout kernel only
   float* ss = fold ? m->sumsq.as<float>() : nullptr;
-  const uint32_t d_tiles = (d + kGemvTileCols - 1) / kGemvTileCols;
+  const uint32_t d_tiles = ruai_gemv_tiles(c, m->layers[0].o.w);  // o_proj and down_proj both write [.., d]
   uint32_t ss_tiles = 1;
   RUAI_TRY(ruai_embed(c, m->d_ids.as<int32_t>(), m->embed.as<float>(), m->llama ? nullptr : m->wpe.as<float>(), len, rows, T, d, m->V, x,
                       m->d_err.as<int>(), ss));
@@ -509,7 +507,7 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
     ap.q = qkv; ap.q_ld = nqkv; ap.kcache = Ly.kc.as<float>(); ap.vcache = Ly.vc.as<float>(); ap.len = len;
     ap.fuse = fuse ? 1 : 0; ap.table = table; ap.k_off = nql; ap.v_off = nql + nkvl;
     ap.T = T; ap.KV = m->KVl; ap.hd = hd; ap.cap = m->cap; ap.scale = 1.0f / sqrtf((float)hd);
-    ap.out = att; ap.out_ld = nql; ap.scratch = m->attn_scratch.as<float>(); ap.counters = m->attn_counters.as<unsigned>();
+    ap.out = att; ap.out_ld = nql; ap.scratch = m->attn_scratch.as<float>(); ap.counters = m->attn_counters.as<unsigned>(); ap.status = c->status;
     RUAI_TRY(ruai_attention(c, ap, B, rep, splits));
     GemvEpilogue eo;
     eo.bias = Ly.o.bias.as<float>();
@@ -582,7 +580,7 @@ int check_device_status(ruai_model* m) {
   int32_t e = 0;
   RUAI_CUDA(m->ctx, cudaMemcpyAsync(&e, m->d_err.p, sizeof e, cudaMemcpyDeviceToHost, m->ctx->stream));
   RUAI_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
-  if (e == 0) return RUAI_OK;
+  if (e == 0) return ruai_ctx_check_status(m->ctx);
   cudaMemsetAsync(m->d_err.p, 0, sizeof(int32_t), m->ctx->stream);
   if (e == 1) return model_fail(m, RUAI_ERR_ARG, "token id out of range [0, %u)", m->V);
   return model_fail(m, RUAI_ERR_TIMEOUT, "tensor-parallel exchange timed out waiting for a peer (status %d)", e);
