@@ -33,6 +33,8 @@ struct ruai_ctx {
   bool use_bulk = true; // bulk-copy staged GEMV (gemv_bulk.cu) where the weight allows it
   bool use_tc = true;   // tensor-core GEMV (gemv_tc.cu) for int4 group-32 weights and up to 4 rows
   void* prof = nullptr;  // debug: device buffer for cycle stamps (set by ruai_debug_set_prof)
+  unsigned long long* trace = nullptr;  // debug: per-launch [first entry, first past the dependency wait, last exit] in ns
+  unsigned trace_slots = 0, trace_seq = 0;
   int* status = nullptr;  // device word: 0 ok, 3 = a bounded wait inside a kernel ran out
   unsigned long long launches = 0;
 };
@@ -107,6 +109,19 @@ inline cudaError_t ruai_launch(ruai_ctx* ctx, void (*kernel)(KArgs...), dim3 gri
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Debug timeline: slot[0] = earliest entry, slot[1] = earliest return from the dependency wait, slot[2] = latest exit.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_min(unsigned long long* slot, int i) { if (slot) atomicMin(slot + i, global_ns()); }
+__device__ __forceinline__ void trace_max(unsigned long long* slot, int i) { if (slot) atomicMax(slot + i, global_ns()); }
+inline unsigned long long* ruai_trace_slot(ruai_ctx* c) {
+  if (!c->trace || c->trace_seq >= c->trace_slots) return nullptr;
+  return c->trace + 4ull * (c->trace_seq++);
+}
+
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -167,6 +182,13 @@ struct GemvPrologue {
   const float* sumsq = nullptr;
   uint32_t tiles = 0;
   float eps = 0.0f;
+  // Weights of the kernel that will run next: every CTA asks the L2 to fetch its share of them
+  // (cp.async.bulk.prefetch.L2), so the next kernel starts on warm lines while this one computes.
+  const void* next_data = nullptr;
+  size_t next_data_bytes = 0;
+  const void* next_scale = nullptr;
+  size_t next_scale_bytes = 0;
+  unsigned long long* trace = nullptr;  // debug timeline slot of this launch
 };
 
 constexpr int kGemvTileCols = 256;      // columns per CTA of gemv.cu, and per sumsq / argmax tile it writes

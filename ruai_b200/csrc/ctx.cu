@@ -170,3 +170,10 @@ RUAI_API int ruai_debug_set_prof(ruai_ctx* c, void* dev_buf) {
   c->prof = dev_buf;
   return RUAI_OK;
 }
+
+RUAI_API int ruai_debug_trace(ruai_ctx* c, void* dev_buf, unsigned slots) {
+  c->trace = (unsigned long long*)dev_buf;
+  c->trace_slots = slots;
+  c->trace_seq = 0;
+  return RUAI_OK;
+}

@@ -151,19 +151,25 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 
 // scaled_dot_product_attention over the cache (functional.rs:264-296, llama.rs:248-277):
 // softmax(q k^T / sqrt(hd) + causal mask) v.  The `rep` query heads of one KV head are
-// handled together so the cached rows are read once (the reference's
-// [B, H_kv, rep*T, hd] view, llama.rs:264-268).  Keys are split over gridDim.z CTAs and
-// over the warps of a CTA; a warp takes kKeys keys per iteration (all their loads are
-// issued before any arithmetic) and keeps an online-softmax state (max, sum, weighted V).
-// States are merged at the end: within the CTA through shared memory, across CTAs by the
-// last one to arrive.
+// handled by one CTA so the cached rows are read once (the reference's [B, H_kv, rep*T, hd]
+// view, llama.rs:264-268).  Keys are split over gridDim.z CTAs; a CTA brings its keys and
+// values into shared memory with bulk copies, 64 at a time, requested before the
+// grid-dependency wait in the fused step.
+//   scores : warp (block of 32 keys, head): one key per lane, the lane walks its key row
+//            starting at its own 16-byte column (no bank conflicts, no cross-lane sums);
+//            block maximum and sum by shuffles.
+//   values : thread (head, element): sums p * V over the chunk's keys, rows read conflict-free.
+// Every thread keeps a running (max, sum, weighted value) for its outputs across chunks; the
+// splits are merged by the last CTA to arrive.
 // With p.fuse (single new token per sequence) the kernel also does apply_rope
 // (functional.rs:197-204) on q and on the new key and appends the new key / value to the
 // cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
-template <int EPL, int REP>
-__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
-  constexpr int kWarps = kAttnThreads / 32;
-  extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs [kWarps][REP][32] | merge
+constexpr int kAttnOutPerThread = 4;  // (rep * hd) / (64 * rep) for hd up to 256
+
+template <int REP>
+__global__ void __launch_bounds__(64 * REP) attention_kernel(const AttnParams p) {
+  constexpr int kThreads = 64 * REP, kBlocks = kAttnChunkKeys / 32;
+  extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs | stats | merge
   __shared__ __align__(8) uint64_t kv_bar;
   __shared__ unsigned s_last;
   const uint32_t hd = p.hd, half = hd / 2;
@@ -172,13 +178,19 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
   float* qs = vs + (size_t)kAttnChunkKeys * hd;
   float* knew = qs + REP * hd;
   float* vnew = knew + hd;
-  float* probs = vnew + hd;
-  float* mg = probs + kWarps * REP * 32;
+  float* probs = vnew + hd;                       // [kBlocks][REP][32]
+  float* bmax = probs + kBlocks * REP * 32;       // [kBlocks + 1][REP]: block maxima; the last row is the new key's score
+  float* bsum = bmax + (kBlocks + 1) * REP;       // [kBlocks][REP]
+  float* mg = bsum + kBlocks * REP;               // split merge: [64][REP] weights, [64][REP] sums, [REP]
   const uint32_t bk = blockIdx.x, b = bk / p.KV, kvh = bk % p.KV, t = blockIdx.y, split = blockIdx.z;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  long long* prof = (p.prof && blockIdx.x == 0 && blockIdx.z == 3 && threadIdx.x == 0) ? p.prof + 2048 : nullptr;
+  int pn = 0;
+#define ASTAMP() do { if (prof && pn < 60) prof[pn++] = clock64(); } while (0)
+  ASTAMP();
   float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
   float* vbase = p.vcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     pipe::mbar_init(&kv_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -193,8 +205,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     k0 = min(n_cached, split * per);
     k1 = min(n_cached, k0 + per);
   };
-  // One bulk copy each brings a chunk of this CTA's keys and values (contiguous rows of the cache) into shared memory.
-  auto fetch_chunk = [&](uint32_t c0) {
+  auto fetch_chunk = [&](uint32_t c0) {  // one thread
     const uint32_t nk = min((uint32_t)kAttnChunkKeys, k1 - c0);
     const uint32_t bytes = nk * hd * 4u;
     pipe::mbar_expect_tx(&kv_bar, 2u * bytes);
@@ -205,19 +216,23 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
   // previous step's last kernel: both are safe to read while the predecessor (the q/k/v GEMV) still runs.
   if (p.fuse) {
     plan();
-    if (threadIdx.x == 0 && k1 > k0) fetch_chunk(k0);
+    if (tid == 0 && k1 > k0) fetch_chunk(k0);
   }
+  ASTAMP();
+  if (tid == 0) trace_min(p.trace, 0);
   grid_dependency_wait();
+  ASTAMP();
+  if (tid == 0) trace_min(p.trace, 1);
   grid_launch_dependents();
   if (!p.fuse) {
     plan();
-    if (threadIdx.x == 0 && k1 > k0) fetch_chunk(k0);
+    if (tid == 0 && k1 > k0) fetch_chunk(k0);
   }
   const bool owns_new = p.fuse && split == gridDim.z - 1;
   const float* row = p.q + (size_t)(b * p.T + t) * p.q_ld;
   const float* qrow = row + (size_t)kvh * REP * hd;
   const bool rot = p.fuse && p.table != nullptr;
-  for (uint32_t i = threadIdx.x; i < REP * hd; i += blockDim.x) {
+  for (uint32_t i = tid; i < REP * hd; i += kThreads) {
     float v = qrow[i];
     if (rot) {
       const uint32_t r = i / hd, e = i % hd, f = e < half ? e : e - half;
@@ -230,7 +245,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
   if (owns_new) {
     const float* kr = row + p.k_off + (size_t)kvh * hd;
     const float* vr = row + p.v_off + (size_t)kvh * hd;
-    for (uint32_t e = threadIdx.x; e < hd; e += blockDim.x) {
+    for (uint32_t e = tid; e < hd; e += kThreads) {
       float kvv = kr[e];
       if (rot) {
         const uint32_t f = e < half ? e : e - half;
@@ -246,174 +261,173 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     }
   }
   __syncthreads();
-  float mx[REP], l[REP], o[REP][EPL];
+  ASTAMP();
+  // this thread's outputs: idx = tid + i * kThreads over [REP][hd]
+  const uint32_t total = REP * hd;
+  float run_m[kAttnOutPerThread], run_l[kAttnOutPerThread], run_o[kAttnOutPerThread];
 #pragma unroll
-  for (int r = 0; r < REP; ++r) {
-    mx[r] = -INFINITY;
-    l[r] = 0.0f;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) o[r][i] = 0.0f;
-  }
-  float* ps = probs + (size_t)warp * REP * 32;  // this warp's probabilities of a 32-key block: [REP][32]
-  // A warp takes 32 keys at a time.  Scores: one key per lane, the lane walks its own key row (the 32 rows
-  // of a block are contiguous in the cache, so every byte of the lines it touches is used).  No reduction
-  // across lanes is needed for the dot products; the block maximum and sum cost ten shuffles per head.
-  // Weighted values: one output element per lane, the rows of V are read coalesced.
+  for (int i = 0; i < kAttnOutPerThread; ++i) { run_m[i] = -INFINITY; run_l[i] = 0.0f; run_o[i] = 0.0f; }
+  const int wblk = warp / REP, wr = warp % REP;  // this warp's (key block, head) in the score phase
   uint32_t phase = 0;
   bool ok = true;
-  for (uint32_t c0 = k0; c0 < k1; c0 += kAttnChunkKeys) {
+  for (uint32_t c0 = k0; c0 < k1 || (c0 == k0 && owns_new); c0 += kAttnChunkKeys) {
+    const bool have_keys = c0 < k1;
     if (c0 != k0) {
       __syncthreads();  // everyone is done with the previous chunk
-      if (threadIdx.x == 0) fetch_chunk(c0);
+      if (tid == 0) fetch_chunk(c0);
     }
-    if (!pipe::mbar_wait(&kv_bar, phase & 1u)) { ok = false; break; }
-    ++phase;
-    const uint32_t c1 = min(k1, c0 + kAttnChunkKeys);
-    for (uint32_t blk = c0 + warp * 32; blk < c1; blk += kWarps * 32) {
-      const uint32_t key = blk + lane;
-      const bool valid = key < c1;
-      float sc[REP];
-#pragma unroll
-      for (int r = 0; r < REP; ++r) sc[r] = 0.0f;
-      // lane = key; the lane starts at its own 16-byte column so that the 32 lanes hit different banks
+    if (have_keys) {
+      if (!pipe::mbar_wait(&kv_bar, phase & 1u)) { ok = false; break; }
+      ++phase;
+    }
+    ASTAMP();
+    const uint32_t c1 = have_keys ? min(k1, c0 + kAttnChunkKeys) : c0;
+    const uint32_t nkeys = c1 - c0;
+    // ---- scores ----
+    {
+      const uint32_t key = wblk * 32 + lane;
+      const bool valid = key < nkeys;
+      float sc = 0.0f;
       const uint32_t nq4 = hd / 4;
-      const float4* krow = reinterpret_cast<const float4*>(ks + (size_t)(valid ? key - c0 : 0) * hd);
-      for (uint32_t it = 0; it < nq4; ++it) {
-        uint32_t cidx = it + lane;
-        cidx = cidx >= nq4 ? cidx % nq4 : cidx;
-        const float4 kk = krow[cidx];
-#pragma unroll
-        for (int r = 0; r < REP; ++r) {
-          const float4 qv = *reinterpret_cast<const float4*>(qs + r * hd + 4 * cidx);
-          sc[r] = fmaf(qv.x, kk.x, sc[r]);
-          sc[r] = fmaf(qv.y, kk.y, sc[r]);
-          sc[r] = fmaf(qv.z, kk.z, sc[r]);
-          sc[r] = fmaf(qv.w, kk.w, sc[r]);
-        }
+      const float4* krow = reinterpret_cast<const float4*>(ks + (size_t)(valid ? key : 0) * hd);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + wr * hd);
+      // four independent 16-byte columns per step so that the shared-memory reads overlap
+      uint32_t cc = lane % nq4;
+      auto nxt = [&](uint32_t c) { return c + 1 >= nq4 ? c + 1 - nq4 : c + 1; };
+      auto dot4 = [](const float4& a, const float4& b2, float acc) {
+        acc = fmaf(a.x, b2.x, acc); acc = fmaf(a.y, b2.y, acc); acc = fmaf(a.z, b2.z, acc); return fmaf(a.w, b2.w, acc);
+      };
+      float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+      uint32_t it = 0;
+      for (; it + 4 <= nq4; it += 4) {
+        const uint32_t c0i = cc, c1i = nxt(c0i), c2i = nxt(c1i), c3i = nxt(c2i);
+        const float4 ka = krow[c0i], kb = krow[c1i], kc = krow[c2i], kd = krow[c3i];
+        const float4 qa = q4[c0i], qb = q4[c1i], qc = q4[c2i], qd = q4[c3i];
+        s0 = dot4(qa, ka, s0); s1 = dot4(qb, kb, s1); s2 = dot4(qc, kc, s2); s3 = dot4(qd, kd, s3);
+        cc = nxt(c3i);
       }
-#pragma unroll
-      for (int r = 0; r < REP; ++r) {
-        const float sv = valid ? sc[r] * p.scale : -INFINITY;
-        float bm = sv;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
-        const float nm = fmaxf(mx[r], bm);   // the block has at least one valid key, so nm is finite
-        const float c = expf(mx[r] - nm);    // exp(-inf) = 0 on the first block
-        const float pr = valid ? expf(sv - nm) : 0.0f;
-        float bs = pr;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) bs += __shfl_xor_sync(0xFFFFFFFFu, bs, off);
-        l[r] = l[r] * c + bs;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) o[r][i] *= c;
-        mx[r] = nm;
-        ps[r * 32 + lane] = pr;
+      for (; it < nq4; ++it) {
+        s0 = dot4(q4[cc], krow[cc], s0);
+        cc = nxt(cc);
       }
-      __syncwarp();
-      const uint32_t nk = min(32u, c1 - blk);
-      for (uint32_t kk0 = 0; kk0 < nk; ++kk0) {
-        float vv[EPL];
+      sc = (s0 + s1) + (s2 + s3);
+      const float sv = valid ? sc * p.scale : -INFINITY;
+      float bm = sv;
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-          const uint32_t e = lane + 32 * i;
-          vv[i] = e < hd ? vs[(size_t)(blk - c0 + kk0) * hd + e] : 0.0f;
-        }
+      for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
+      const float pr = valid ? expf(sv - bm) : 0.0f;
+      float bs = pr;
 #pragma unroll
-        for (int r = 0; r < REP; ++r) {
-          const float pr = ps[r * 32 + kk0];
+      for (int off = 16; off > 0; off >>= 1) bs += __shfl_xor_sync(0xFFFFFFFFu, bs, off);
+      probs[(wblk * REP + wr) * 32 + lane] = pr;
+      if (lane == 0) { bmax[wblk * REP + wr] = bm; bsum[wblk * REP + wr] = bs; }
+      // the token's own key: one more score per head, computed by the first block's warps on the first chunk
+      if (owns_new && c0 == k0 && wblk == 0) {
+        float a = 0.0f;
+        for (uint32_t e = lane; e < hd; e += 32) a = fmaf(qs[wr * hd + e], knew[e], a);
 #pragma unroll
-          for (int i = 0; i < EPL; ++i) o[r][i] = fmaf(pr, vv[i], o[r][i]);
-        }
+        for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, off);
+        if (lane == 0) bmax[kBlocks * REP + wr] = a * p.scale;
       }
-      __syncwarp();
+    }
+    ASTAMP();
+    __syncthreads();
+    ASTAMP();
+    // ---- weighted values ----
+    const bool with_new = owns_new && c0 == k0;
+#pragma unroll
+    for (int i = 0; i < kAttnOutPerThread; ++i) {
+      const uint32_t idx = tid + i * kThreads;
+      if (idx < total) {
+        const uint32_t r = idx / hd, e = idx % hd;
+        float M = run_m[i];
+#pragma unroll
+        for (int bl = 0; bl < kBlocks; ++bl) M = fmaxf(M, bmax[bl * REP + r]);
+        const float snew = with_new ? bmax[kBlocks * REP + r] : -INFINITY;
+        M = fmaxf(M, snew);
+        const float cr = expf(run_m[i] - M);  // 0 on the first chunk
+        float L = run_l[i] * cr, O = run_o[i] * cr;
+#pragma unroll
+        for (int bl = 0; bl < kBlocks; ++bl) {
+          const float bm = bmax[bl * REP + r];
+          if (bm != -INFINITY) {
+            const float cb = expf(bm - M);
+            L = fmaf(bsum[bl * REP + r], cb, L);
+            const uint32_t nb = min(32u, nkeys - min(nkeys, (uint32_t)bl * 32u));
+            const float* pp = probs + (bl * REP + r) * 32;
+            const float* vp = vs + (size_t)bl * 32 * hd + e;
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+            uint32_t kk = 0;
+            for (; kk + 8 <= nb; kk += 8) {  // eight keys per step: sixteen independent shared-memory reads in flight
+              float pv[8], vv[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) { pv[u] = pp[kk + u]; vv[u] = vp[(size_t)(kk + u) * hd]; }
+              a0 = fmaf(pv[0], vv[0], a0); a1 = fmaf(pv[1], vv[1], a1); a2 = fmaf(pv[2], vv[2], a2); a3 = fmaf(pv[3], vv[3], a3);
+              a0 = fmaf(pv[4], vv[4], a0); a1 = fmaf(pv[5], vv[5], a1); a2 = fmaf(pv[6], vv[6], a2); a3 = fmaf(pv[7], vv[7], a3);
+            }
+            for (; kk < nb; ++kk) a0 = fmaf(pp[kk], vp[(size_t)kk * hd], a0);
+            a0 += a2; a1 += a3;
+            O = fmaf(a0 + a1, cb, O);
+          }
+        }
+        if (with_new) {
+          const float cn = expf(snew - M);
+          L += cn;
+          O = fmaf(cn, vnew[e], O);
+        }
+        run_m[i] = M; run_l[i] = L; run_o[i] = O;
+      }
     }
   }
-  if (!ok && p.status && threadIdx.x == 0) atomicExch(p.status, 3);
-  if (owns_new && warp == 0) {  // the token's own key and value, from shared memory
-#pragma unroll
-    for (int r = 0; r < REP; ++r) {
-      float a = 0.0f;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        const uint32_t e = lane + 32 * i;
-        if (e < hd) a = fmaf(qs[r * hd + e], knew[e], a);
-      }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, off);
-      const float sv = a * p.scale;
-      const float nm = fmaxf(mx[r], sv);
-      const float c = expf(mx[r] - nm);
-      const float pr = expf(sv - nm);
-      l[r] = l[r] * c + pr;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        const uint32_t e = lane + 32 * i;
-        o[r][i] = o[r][i] * c + (e < hd ? pr * vnew[e] : 0.0f);
-      }
-      mx[r] = nm;
-    }
-  }
-  // ---- merge the warps ----
+  if (!ok && p.status && tid == 0) atomicExch(p.status, 3);
+  ASTAMP();
+  // ---- this CTA's result: straight out, or into the split scratch ----
   const uint32_t stride = hd + 2;
-#pragma unroll
-  for (int r = 0; r < REP; ++r) {
-    float* dst = mg + ((size_t)warp * REP + r) * stride;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const uint32_t e = lane + 32 * i;
-      if (e < hd) dst[e] = o[r][i];
-    }
-    if (lane == 0) { dst[hd] = mx[r]; dst[hd + 1] = l[r]; }
-  }
-  __syncthreads();
-  const uint32_t total = REP * hd;
   float* sc = p.scratch + ((((size_t)bk * p.T + t) * gridDim.z + split) * REP) * stride;
-  for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
-    const uint32_t r = idx / hd, e = idx % hd;
-    float M = -INFINITY;
-    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, mg[((size_t)w * REP + r) * stride + hd]);
-    float L = 0.0f, O = 0.0f;
-    for (int w = 0; w < kWarps; ++w) {
-      const float* src = mg + ((size_t)w * REP + r) * stride;
-      const float c = src[hd] == -INFINITY ? 0.0f : expf(src[hd] - M);
-      L += src[hd + 1] * c;
-      O += src[e] * c;
-    }
-    if (gridDim.z == 1) {
-      p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = O / L;
-    } else {
-      sc[(size_t)r * stride + e] = O;
-      if (e == 0) { sc[(size_t)r * stride + hd] = M; sc[(size_t)r * stride + hd + 1] = L; }
+#pragma unroll
+  for (int i = 0; i < kAttnOutPerThread; ++i) {
+    const uint32_t idx = tid + i * kThreads;
+    if (idx < total) {
+      const uint32_t r = idx / hd, e = idx % hd;
+      if (gridDim.z == 1) {
+        p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = run_o[i] / run_l[i];
+      } else {
+        sc[(size_t)r * stride + e] = run_o[i];
+        if (e == 0) { sc[(size_t)r * stride + hd] = run_m[i]; sc[(size_t)r * stride + hd + 1] = run_l[i]; }
+      }
     }
   }
-  if (gridDim.z == 1) return;
+  if (gridDim.z == 1) { if (tid == 0) trace_max(p.trace, 2); return; }
+  ASTAMP();
   // ---- merge the key splits: last CTA to arrive ----
   __threadfence();
   __syncthreads();
   unsigned* counter = p.counters + (size_t)bk * p.T + t;
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     const unsigned a = atomicAdd(counter, 1u);
     s_last = a == gridDim.z - 1 ? 1u : 0u;
   }
   __syncthreads();
-  if (!s_last) return;
+  ASTAMP();
+  if (prof) prof[63] = pn;
+  if (!s_last) { if (tid == 0) trace_max(p.trace, 2); return; }
   __threadfence();
-  if (threadIdx.x == 0) *counter = 0;
+  if (tid == 0) *counter = 0;
   const float* base = p.scratch + (((size_t)bk * p.T + t) * gridDim.z) * REP * stride;
   // weights of the splits first (one parallel round of loads), then the weighted sums with
-  // eight independent loads in flight per thread; `mg` is free again and holds the weights
+  // eight independent loads in flight per thread
   const uint32_t ns = gridDim.z;  // <= 64
   float* wgt = mg;                // [ns][REP] max, then coefficient
   float* lsum = mg + 64 * REP;    // [ns][REP]
-  for (uint32_t i = threadIdx.x; i < ns * REP; i += blockDim.x) {
+  for (uint32_t i = tid; i < ns * REP; i += kThreads) {
     const float* src = base + (size_t)i * stride;  // i = s * REP + r
     wgt[i] = __ldcg(src + hd);
     lsum[i] = __ldcg(src + hd + 1);
   }
   __syncthreads();
   float* inv = lsum + 64 * REP;   // [REP] 1 / total
-  if (threadIdx.x < REP) {
-    const uint32_t r = threadIdx.x;
+  if (tid < REP) {
+    const uint32_t r = tid;
     float M = -INFINITY;
     for (uint32_t s2 = 0; s2 < ns; ++s2) M = fmaxf(M, wgt[s2 * REP + r]);
     float L = 0.0f;
@@ -426,7 +440,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     inv[r] = 1.0f / L;
   }
   __syncthreads();
-  for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
+  for (uint32_t idx = tid; idx < total; idx += kThreads) {
     const uint32_t r = idx / hd, e = idx % hd;
     float O = 0.0f;
     for (uint32_t s0 = 0; s0 < ns; s0 += 8) {
@@ -439,6 +453,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     }
     p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = O * inv[r];
   }
+  if (tid == 0) trace_max(p.trace, 2);
+#undef ASTAMP
 }
 
 // generation::argmax (generation.rs:6-8): the LAST index among equal maxima, in
@@ -500,27 +516,15 @@ __global__ void take_last_rows_kernel(const float* __restrict__ x, uint32_t T, u
   for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) y[(size_t)blockIdx.x * d + i] = src[i];
 }
 
-template <int EPL, int REP>
+template <int REP>
 cudaError_t launch_attn(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem) {
   static bool attr_done[64] = {};
   if (!attr_done[c->ordinal & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attention_kernel<EPL, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel<REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_done[c->ordinal & 63] = true;
   }
-  return ruai_launch(c, attention_kernel<EPL, REP>, grid, dim3(kAttnThreads), smem, true, p);
-}
-
-template <int EPL>
-cudaError_t launch_attn_rep(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem, uint32_t rep) {
-  switch (rep) {
-    case 1: return launch_attn<EPL, 1>(c, p, grid, smem);
-    case 2: return launch_attn<EPL, 2>(c, p, grid, smem);
-    case 3: return launch_attn<EPL, 3>(c, p, grid, smem);
-    case 4: return launch_attn<EPL, 4>(c, p, grid, smem);
-    case 8: return launch_attn<EPL, 8>(c, p, grid, smem);
-    default: return cudaErrorInvalidValue;
-  }
+  return ruai_launch(c, attention_kernel<REP>, grid, dim3(64 * REP), smem, true, p);
 }
 
 }  // namespace
@@ -556,21 +560,26 @@ int ruai_rope_kv(ruai_ctx* c, float* qkv, uint32_t qkv_ld, uint32_t k_off, uint3
   return RUAI_OK;
 }
 
-int ruai_attention(ruai_ctx* c, const AttnParams& p, uint32_t B, uint32_t rep, uint32_t splits) {
-  if (p.hd % 4) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4", p.hd);
-  const uint32_t epl = (p.hd + 31) / 32;
-  constexpr size_t nw = kAttnThreads / 32;
-  const size_t merge = std::max<size_t>(nw * (size_t)rep * (p.hd + 2), 128 * (size_t)rep + rep);
-  const size_t smem = (2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + nw * (size_t)rep * 32 + merge) * sizeof(float);
+int ruai_attention(ruai_ctx* c, const AttnParams& p_in, uint32_t B, uint32_t rep, uint32_t splits) {
+  AttnParams p = p_in;
+  p.trace = ruai_trace_slot(c);
+  p.prof = (long long*)c->prof;
+  if (p.hd % 4 || p.hd > 256) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4 and at most 256", p.hd);
+  constexpr size_t kb = kAttnChunkKeys / 32;
+  const size_t floats = 2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + kb * rep * 32 + (kb + 1) * rep + kb * rep +
+                        128 * (size_t)rep + rep;
+  const size_t smem = floats * sizeof(float);
   const dim3 grid(B * p.KV, p.T, splits);
   cudaError_t e;
-  if (epl <= 1) e = launch_attn_rep<1>(c, p, grid, smem, rep);
-  else if (epl <= 2) e = launch_attn_rep<2>(c, p, grid, smem, rep);
-  else if (epl <= 4) e = launch_attn_rep<4>(c, p, grid, smem, rep);
-  else if (epl <= 8) e = launch_attn_rep<8>(c, p, grid, smem, rep);
-  else return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u > 256", p.hd);
-  if (e != cudaSuccess) return ruai_fail(c, e == cudaErrorInvalidValue ? RUAI_ERR_UNSUPPORTED : RUAI_ERR_CUDA,
-                                         "attention launch (heads per KV head = %u): %s", rep, cudaGetErrorString(e));
+  switch (rep) {
+    case 1: e = launch_attn<1>(c, p, grid, smem); break;
+    case 2: e = launch_attn<2>(c, p, grid, smem); break;
+    case 3: e = launch_attn<3>(c, p, grid, smem); break;
+    case 4: e = launch_attn<4>(c, p, grid, smem); break;
+    case 8: e = launch_attn<8>(c, p, grid, smem); break;
+    default: return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "%u query heads per KV head (supported: 1, 2, 3, 4, 8)", rep);
+  }
+  if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
   return RUAI_OK;
 }
 

@@ -2,7 +2,6 @@
 #pragma once
 #include "common.cuh"
 
-constexpr int kAttnThreads = 64;     // two warps per CTA, one 32-key block each per chunk
 constexpr int kAttnChunkKeys = 64;  // keys (and values) staged in shared memory at a time
 
 struct AttnParams {
@@ -23,6 +22,8 @@ struct AttnParams {
   float* scratch;       // split merge: [B*KV*T][splits][rep][hd+2]
   unsigned* counters;   // [B*KV*T], zero between launches
   int* status;          // context status word (bounded waits)
+  unsigned long long* trace;  // debug timeline slot
+  long long* prof;            // debug cycle stamps of one CTA
 };
 
 int ruai_embed(ruai_ctx* c, const int32_t* ids, const float* embed, const float* wpe, const int32_t* len, uint32_t rows, uint32_t T, uint32_t d,

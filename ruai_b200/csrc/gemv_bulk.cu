@@ -164,7 +164,14 @@ __global__ void __launch_bounds__(kCols) gemv_bulk_kernel(const Params p) {
   // weights do not depend on the predecessor kernel: fill the ring before waiting for it
   if (tid == 0)
     for (uint32_t i = 0; i < nst && i < (uint32_t)kStages; ++i) issue(i);
+  if (tid == 0) {  // warm the L2 for the kernel after this one
+    const uint32_t cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y * gridDim.z;
+    l2_prefetch_share(p.pro.next_data, p.pro.next_data_bytes, cta, n_ctas);
+    l2_prefetch_share(p.pro.next_scale, p.pro.next_scale_bytes, cta, n_ctas);
+  }
+  if (tid == 0) trace_min(p.pro.trace, 0);
   grid_dependency_wait();
+  if (tid == 0) trace_min(p.pro.trace, 1);
   grid_launch_dependents();
   const bool normed = p.pro.norm_w != nullptr;
   if (normed && tid < MT) {
@@ -222,7 +229,7 @@ __global__ void __launch_bounds__(kCols) gemv_bulk_kernel(const Params p) {
       for (int r = 0; r < MT; ++r) st_cluster_f32(red + ((size_t)split * MT + r) * kCols + tid, 0, acc[r]);
     }
     cluster_sync_all();
-    if (split != 0) return;
+    if (split != 0) { if (tid == 0) trace_max(p.pro.trace, 2); return; }
     for (uint32_t s = 1; s < p.splits; ++s) {
 #pragma unroll
       for (int r = 0; r < MT; ++r) acc[r] += red[((size_t)s * MT + r) * kCols + tid];
@@ -232,6 +239,7 @@ __global__ void __launch_bounds__(kCols) gemv_bulk_kernel(const Params p) {
   // ---- epilogue ----
   const float col_scale = (BITS == 8 && active) ? p.scale[j] : 1.0f;
   gemv_epilogue<MT, kCols>(p.epi, acc, rows, m0, p.m, j, active, BITS == 8, col_scale, p.out, s_red, s_arg, &s_flag);
+  if (tid == 0) trace_max(p.pro.trace, 2);
 }
 
 template <int BITS, int MT>
@@ -307,6 +315,7 @@ int ruai_gemv_bulk_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int
   p.w = (const uint4*)w->data; p.scale = w->scale; p.x = x; p.x_dtype = x_dtype; p.x_ld = x_ld;
   p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_cta = cpc; p.splits = splits;
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
+  p.pro.trace = ruai_trace_slot(c);
   const dim3 grid(col_tiles, splits, row_tiles);
   cudaError_t e = w->bits == 8 ? launch_mt<8>(c, p, grid, mt) : launch_mt<4>(c, p, grid, mt);
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "bulk gemv launch failed: %s", cudaGetErrorString(e));

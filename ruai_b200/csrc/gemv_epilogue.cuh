@@ -18,7 +18,8 @@ __device__ __forceinline__ int32_t ordered_bits(float v) {  // total_cmp order a
 
 template <int MT, int COLS>
 __device__ __forceinline__ void gemv_epilogue(const GemvEpilogue& e, float (&acc)[MT], uint32_t rows, uint32_t m0, uint32_t m, uint32_t j, bool active,
-                                              bool scale_cols, float col_scale, void* out, float* s_red, int2* s_arg, unsigned* s_flag) {
+                                              bool scale_cols, float col_scale, void* out, float* s_red, int2* s_arg, unsigned* s_flag,
+                                              const float* resid_pre = nullptr) {
   const int tid = threadIdx.x;
   const float bias = (e.bias && active) ? e.bias[j] : 0.0f;
   const int lane = tid & 31, warp = tid >> 5;
@@ -42,7 +43,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvEpilogue& e, float (&acc
     if (active) {
       if (e.act == ACT_GELU) v = gelu_ref(v);
       const size_t o = row * e.out_ld + j;
-      if (e.resid) v = e.resid[o] + v;
+      if (e.resid) v = (resid_pre ? resid_pre[r] : e.resid[o]) + v;  // resid_pre: the same values, fetched early
       store_from_f32(out, e.out_dtype, o, v);
     }
     if (e.sumsq) {  // sum of squares of this tile's part of the stored row, in a fixed order

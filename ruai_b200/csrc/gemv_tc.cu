@@ -33,7 +33,6 @@ using namespace pipe;
 
 constexpr int kCols = kGemvBulkTileCols;  // 128 = MMA M = TMEM lanes = threads
 constexpr int kStageGroups = 4;           // scale groups (chunks) per ring stage
-constexpr int kAheadStages = 2;           // stages of packed weights held in registers ahead of use
 constexpr int kRoundGroups = 16;          // groups per conversion round of the activations
 constexpr int kN = 16;                    // MMA N: rows x limbs, padded
 constexpr int kLimbs = 3;
@@ -63,7 +62,9 @@ struct Smem {
 
 constexpr int kThreads = kCols + 32;  // four loading / converting / draining warps and one MMA-issuing warp
 
-template <int MT>
+// kAheadStages: stages of packed weights held in registers ahead of their use (2: more CTAs per SM; 4: more
+// bytes in flight per CTA, for launches with few CTAs per SM).
+template <int MT, int kAheadStages>
 __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) {
   static_assert(MT * kLimbs <= kN, "rows x limbs must fit the MMA N");
   using L = Smem<MT>;
@@ -130,16 +131,29 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
 #pragma unroll
     for (int a = 0; a < kAheadStages; ++a) load_stage(a, wq[a], sq[a]);
   }
-  grid_dependency_wait();
-  grid_launch_dependents();
-  const bool normed = p.pro.norm_w != nullptr;
-  if (normed && tid < MT) {
-    float ss = 0.0f;
-    if (tid < (int)rows)
-      for (uint32_t t = 0; t < p.pro.tiles; ++t) ss += p.pro.sumsq[(size_t)t * p.m + m0 + tid];
-    s_rstd[tid] = 1.0f / sqrtf(ss * (1.0f / (float)p.k) + p.pro.eps);
+  if (tid == 0) {  // warm the L2 for the kernel after this one
+    const uint32_t cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y * gridDim.z;
+    l2_prefetch_share(p.pro.next_data, p.pro.next_data_bytes, cta, n_ctas);
+    l2_prefetch_share(p.pro.next_scale, p.pro.next_scale_bytes, cta, n_ctas);
   }
-  if (normed) __syncthreads();
+  if (tid == 0) trace_min(p.pro.trace, 0);
+  grid_dependency_wait();
+  if (tid == 0) trace_min(p.pro.trace, 1);
+  grid_launch_dependents();
+  // RMSNorm: x * rstd * w with rstd a per-row scalar, so the digits are taken from x * w and rstd multiplies
+  // the finished sums; its inputs are fetched now and not needed before the end.
+  const bool normed = p.pro.norm_w != nullptr;
+  if (normed && warp == kCols / 32 && lane < MT) {
+    float ss = 0.0f;
+    if (lane < (int)rows)
+      for (uint32_t t = 0; t < p.pro.tiles; ++t) ss += p.pro.sumsq[(size_t)t * p.m + m0 + lane];
+    s_rstd[lane] = 1.0f / sqrtf(ss * (1.0f / (float)p.k) + p.pro.eps);
+  }
+  // the residual this CTA will add in its epilogue, fetched before the main loop
+  float resid_pre[MT];
+  const bool pre = p.epi.resid != nullptr && p.epi.act != ACT_SWIGLU && split == 0 && active;
+#pragma unroll
+  for (int r = 0; r < MT; ++r) resid_pre[r] = (pre && r < (int)rows) ? p.epi.resid[(size_t)(m0 + r) * p.epi.out_ld + j] : 0.0f;
 
   float acc[MT];
 #pragma unroll
@@ -179,7 +193,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
           for (int t = 0; t < 4; ++t) {
             if (kidx + t < p.k) {
               v[t] = load_as_f32(p.x, p.x_dtype, (size_t)(m0 + r) * p.x_ld + kidx + t);
-              if (normed) v[t] = v[t] * s_rstd[r] * p.pro.norm_w[kidx + t];
+              if (normed) v[t] = v[t] * p.pro.norm_w[kidx + t];
             }
           }
         }
@@ -325,7 +339,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
       for (int r = 0; r < MT; ++r) st_cluster_f32(red + ((size_t)split * MT + r) * kCols + tid, 0, acc[r]);
     }
     cluster_sync_all();
-    if (split != 0) return;
+    if (split != 0) { if (tid == 0) trace_max(p.pro.trace, 2); return; }
     if (tid < kCols) {
       for (uint32_t s = 1; s < p.splits; ++s) {
 #pragma unroll
@@ -333,17 +347,22 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
       }
     }
   }
-  gemv_epilogue<MT, kThreads>(p.epi, acc, rows, m0, p.m, j, active, false, 1.0f, p.out, s_red, s_arg, &s_flag);
+  if (normed) {
+#pragma unroll
+    for (int r = 0; r < MT; ++r) acc[r] *= s_rstd[r];
+  }
+  gemv_epilogue<MT, kThreads>(p.epi, acc, rows, m0, p.m, j, active, false, 1.0f, p.out, s_red, s_arg, &s_flag, pre ? resid_pre : nullptr);
+  if (tid == 0) trace_max(p.pro.trace, 2);
   STAMP();
   if (prof) prof[511] = pn;
 #undef STAMP
 }
 
-template <int MT>
+template <int MT, int AHEAD>
 cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
   static bool attr_done[64] = {};
   if (!attr_done[c->ordinal & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_tc_int4_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT>::bytes(8));
+    cudaError_t e = cudaFuncSetAttribute(gemv_tc_int4_kernel<MT, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT>::bytes(8));
     if (e != cudaSuccess) return e;
     attr_done[c->ordinal & 63] = true;
   }
@@ -369,7 +388,7 @@ cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
   cfg.attrs = attr;
   cfg.numAttrs = na;
   c->launches++;
-  return cudaLaunchKernelEx(&cfg, gemv_tc_int4_kernel<MT>, p);
+  return cudaLaunchKernelEx(&cfg, gemv_tc_int4_kernel<MT, AHEAD>, p);
 }
 
 }  // namespace gemv_tc
@@ -397,9 +416,14 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   p.w = (const uint4*)w->data; p.scale = w->scale; p.x = x; p.x_dtype = x_dtype; p.x_ld = x_ld;
   p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_cta = cpc; p.splits = splits;
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
+  p.pro.trace = ruai_trace_slot(c);
   p.prof = (long long*)c->prof;
   const dim3 grid(col_tiles, splits, 1);
-  cudaError_t e = mt == 1 ? launch_one<1>(c, p, grid) : mt == 2 ? launch_one<2>(c, p, grid) : launch_one<4>(c, p, grid);
+  // few CTAs per SM: spend the free registers on a deeper weight queue
+  const bool deep = col_tiles * splits <= 2u * (uint32_t)c->sm_count;
+  cudaError_t e = mt == 1 ? (deep ? launch_one<1, 4>(c, p, grid) : launch_one<1, 2>(c, p, grid))
+                : mt == 2 ? (deep ? launch_one<2, 4>(c, p, grid) : launch_one<2, 2>(c, p, grid))
+                          : launch_one<4, 2>(c, p, grid);
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "tensor-core gemv launch failed: %s", cudaGetErrorString(e));
   return RUAI_OK;
 }
