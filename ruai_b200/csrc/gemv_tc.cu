@@ -34,9 +34,10 @@ using namespace pipe;
 constexpr int kCols = kGemvBulkTileCols;  // 128 = MMA M = TMEM lanes = threads
 constexpr int kStageGroups = 4;           // scale groups (chunks) per ring stage
 constexpr int kRoundGroups = 16;          // groups per conversion round of the activations
-constexpr int kN = 16;                    // MMA N: rows x limbs, padded
 constexpr int kLimbs = 3;
-constexpr int kTmemCols = 2 * kStageGroups * kN;  // two stages of accumulators
+// MMA N (rows x limbs, padded to a multiple of 16) and the TMEM columns of two stages of accumulators
+constexpr int n_of(int mt) { return mt <= 4 ? 16 : mt <= 8 ? 32 : 48; }
+constexpr int tmem_cols_of(int mt) { return 2 * kStageGroups * n_of(mt) <= 128 ? 128 : 2 * kStageGroups * n_of(mt) <= 256 ? 256 : 512; }
 
 struct Params {
   const uint4* w;
@@ -53,6 +54,7 @@ struct Params {
 
 template <int MT>
 struct Smem {
+  static constexpr int kN = n_of(MT);
   static constexpr size_t off_a = 0;
   static constexpr size_t off_b = off_a + 2 * (size_t)kStageGroups * kCols * 32;
   static constexpr size_t off_meta = off_b + 2 * (size_t)kRoundGroups * kN * 32;
@@ -66,6 +68,8 @@ constexpr int kThreads = kCols + 32;  // four loading / converting / draining wa
 // bytes in flight per CTA, for launches with few CTAs per SM).
 template <int MT, int kAheadStages>
 __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) {
+  constexpr int kN = n_of(MT);
+  constexpr int kTmemCols = tmem_cols_of(MT);
   static_assert(MT * kLimbs <= kN, "rows x limbs must fit the MMA N");
   using L = Smem<MT>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -211,26 +215,31 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
       const uint32_t g0 = (s % kRoundStages) * kStageGroups;
       const uint32_t nch = min((uint32_t)kStageGroups, c_end - (c_begin + s * kStageGroups));
       constexpr int kQ = (MT * kLimbs + 3) / 4;  // 4-column loads per group
-      int32_t d[kStageGroups][kQ * 4];
+      constexpr int kBatch = MT <= 4 ? kStageGroups : 1;  // groups whose sums are in registers at once
 #pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) {
-        const uint32_t col = tmem_base + lane_base + ((s & 1) * kStageGroups + u) * kN;
+      for (int u0 = 0; u0 < kStageGroups; u0 += kBatch) {
+        int32_t d[kBatch][kQ * 4];
 #pragma unroll
-        for (int q4 = 0; q4 < kQ; ++q4) {
-          int32_t t4[4];
-          tmem_ld4(col + 4 * q4, t4);  // groups past the end hold stale sums; they are not used below
-          d[u][4 * q4 + 0] = t4[0]; d[u][4 * q4 + 1] = t4[1]; d[u][4 * q4 + 2] = t4[2]; d[u][4 * q4 + 3] = t4[3];
+        for (int ub = 0; ub < kBatch; ++ub) {
+          const uint32_t col = tmem_base + lane_base + ((s & 1) * kStageGroups + u0 + ub) * kN;
+#pragma unroll
+          for (int q4 = 0; q4 < kQ; ++q4) {
+            int32_t t4[4];
+            tmem_ld4(col + 4 * q4, t4);  // groups past the end hold stale sums; they are not used below
+            d[ub][4 * q4 + 0] = t4[0]; d[ub][4 * q4 + 1] = t4[1]; d[ub][4 * q4 + 2] = t4[2]; d[ub][4 * q4 + 3] = t4[3];
+          }
         }
-      }
-      tmem_ld_wait();
+        tmem_ld_wait();
 #pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) {
-        if ((uint32_t)u < nch) {
+        for (int ub = 0; ub < kBatch; ++ub) {
+          const int u = u0 + ub;
+          if ((uint32_t)u < nch) {
 #pragma unroll
-          for (int r = 0; r < MT; ++r) {
-            const uint32_t mi = (rb * kRoundGroups + g0 + u) * MT + r;
-            const int val = d[u][kLimbs * r] * 16384 + d[u][kLimbs * r + 1] * 128 + d[u][kLimbs * r + 2] - 8 * meta_sum[mi];
-            acc[r] = fmaf((float)val, sv[u] * meta_scale[mi], acc[r]);
+            for (int r = 0; r < MT; ++r) {
+              const uint32_t mi = (rb * kRoundGroups + g0 + u) * MT + r;
+              const int val = d[ub][kLimbs * r] * 16384 + d[ub][kLimbs * r + 1] * 128 + d[ub][kLimbs * r + 2] - 8 * meta_sum[mi];
+              acc[r] = fmaf((float)val, sv[u] * meta_scale[mi], acc[r]);
+            }
           }
         }
       }
@@ -394,7 +403,7 @@ cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
 }  // namespace gemv_tc
 
 bool ruai_gemv_tc_eligible(const ruai_qweight* w, uint32_t m) {
-  return w->layout == QL_CHUNK16 && w->bits == 4 && w->n % 4 == 0 && m >= 1 && m <= 4;
+  return w->layout == QL_CHUNK16 && w->bits == 4 && w->n % 4 == 0 && m >= 1 && m <= 16;
 }
 
 int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
@@ -405,11 +414,14 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   if (epi.out_ld == 0) epi.out_ld = epi.act == ACT_SWIGLU ? w->n / 2 : w->n;
   if (epi.sumsq && epi.act == ACT_SWIGLU) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "sum of squares with the SwiGLU epilogue");
   if (epi.argmax_out && epi.act == ACT_SWIGLU) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "argmax with the SwiGLU epilogue");
-  const int mt = m <= 1 ? 1 : m <= 2 ? 2 : 4;
+  // up to 8 rows per CTA; 9..16 rows run as two row tiles (the second pass over the weights mostly hits the L2)
+  const int mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8;
+  const uint32_t row_tiles = (m + mt - 1) / mt;
+  if (epi.argmax_out && row_tiles != 1) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "fused argmax needs a single row tile");
   const uint32_t col_tiles = (w->n + kCols - 1) / kCols;
   // split k over a cluster until there are about two CTAs per SM, keeping at least two ring stages per CTA
   uint32_t splits = 1;
-  while (splits < 8 && col_tiles * splits < 2u * (uint32_t)c->sm_count && w->chunks / (splits * 2) >= 2u * kStageGroups) splits *= 2;
+  while (splits < 8 && col_tiles * row_tiles * splits < 2u * (uint32_t)c->sm_count && w->chunks / (splits * 2) >= 2u * kStageGroups) splits *= 2;
   uint32_t cpc = (w->chunks + splits - 1) / splits;
   cpc = (cpc + kStageGroups - 1) / kStageGroups * kStageGroups;
   Params p;
@@ -418,12 +430,13 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
   p.pro.trace = ruai_trace_slot(c);
   p.prof = (long long*)c->prof;
-  const dim3 grid(col_tiles, splits, 1);
+  const dim3 grid(col_tiles, splits, row_tiles);
   // few CTAs per SM: spend the free registers on a deeper weight queue
-  const bool deep = col_tiles * splits <= 2u * (uint32_t)c->sm_count;
+  const bool deep = col_tiles * row_tiles * splits <= 2u * (uint32_t)c->sm_count;
   cudaError_t e = mt == 1 ? (deep ? launch_one<1, 4>(c, p, grid) : launch_one<1, 2>(c, p, grid))
                 : mt == 2 ? (deep ? launch_one<2, 4>(c, p, grid) : launch_one<2, 2>(c, p, grid))
-                          : launch_one<4, 2>(c, p, grid);
+                : mt == 4 ? launch_one<4, 2>(c, p, grid)
+                          : launch_one<8, 2>(c, p, grid);
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "tensor-core gemv launch failed: %s", cudaGetErrorString(e));
   return RUAI_OK;
 }
