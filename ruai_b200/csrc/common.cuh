@@ -201,6 +201,9 @@ int ruai_gemv_bulk_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, i
 bool ruai_gemv_tc_eligible(const ruai_qweight* w, uint32_t m);
 int ruai_gemv_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                         const GemvEpilogue& epi, const GemvPrologue& pro);
+bool ruai_gemm_tc_eligible(const ruai_qweight* w, uint32_t m);
+int ruai_gemm_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
+                        const GemvEpilogue& epi, const GemvPrologue& pro);
 // Reads and clears the context's device status word (synchronizes the stream).
 int ruai_ctx_check_status(ruai_ctx* ctx);
 

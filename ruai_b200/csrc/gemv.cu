@@ -374,6 +374,8 @@ cudaError_t launch_mt(ruai_ctx* c, const GemvParams& p, dim3 grid, int mt) {
 int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                      const GemvEpilogue& epi_in, const GemvPrologue& pro) {
   if (m == 0) return RUAI_OK;
+  if (c->use_bulk && c->use_tc && ruai_gemm_tc_eligible(w, m) && !epi_in.sumsq && !epi_in.argmax_out)
+    return ruai_gemm_tc_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   if (c->use_bulk && c->use_tc && ruai_gemv_tc_eligible(w, m)) return ruai_gemv_tc_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   if (c->use_bulk && ruai_gemv_bulk_eligible(w)) return ruai_gemv_bulk_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   GemvEpilogue epi = epi_in;

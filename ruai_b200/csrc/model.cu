@@ -487,7 +487,7 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
   // RMSNorm rides in the prologue of the GEMV that consumes it: the producer of x (embedding, o_proj, down_proj)
   // leaves per-tile sums of squares.  LayerNorm (GPT-2) and the sharded model (x is produced by the exchange
   // kernel) keep the standalone norm kernels.
-  const bool fold = m->llama && !tp && (m->bits == 8 || m->group == 32);  // the chunk-layout kernel only
+  const bool fold = m->llama && !tp && (m->bits == 8 || m->group == 32) && rows <= 16;  // decode-sized steps on the chunk-layout kernels
   float* ss = fold ? m->sumsq.as<float>() : nullptr;
   const uint32_t d_tiles = ruai_gemv_tiles(c, m->layers[0].o.w);  // o_proj and down_proj both write [.., d]
   uint32_t ss_tiles = 1;
