@@ -487,9 +487,10 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
   // RMSNorm rides in the prologue of the GEMV that consumes it: the producer of x (embedding, o_proj, down_proj)
   // leaves per-tile sums of squares.  LayerNorm (GPT-2) and the sharded model (x is produced by the exchange
   // kernel) keep the standalone norm kernels.
-  const bool fold = m->llama && !tp && (m->bits == 8 || m->group == 32) && rows <= 16;  // decode-sized steps on the chunk-layout kernels
+  // decode-sized steps on the chunk-layout kernels; sharded: only where the exchange kernel can supply the sum of squares
+  const bool fold = m->llama && (m->bits == 8 || m->group == 32) && rows <= 16 && (!tp || ruai_tp_allreduce_gives_sumsq(rows, d));
   float* ss = fold ? m->sumsq.as<float>() : nullptr;
-  const uint32_t d_tiles = ruai_gemv_tiles(c, m->layers[0].o.w);  // o_proj and down_proj both write [.., d]
+  const uint32_t d_tiles = tp ? 1u : ruai_gemv_tiles(c, m->layers[0].o.w);  // o_proj and down_proj both write [.., d]; sharded: the exchange writes one tile
   uint32_t ss_tiles = 1;
   RUAI_TRY(ruai_embed(c, m->d_ids.as<int32_t>(), m->embed.as<float>(), m->llama ? nullptr : m->wpe.as<float>(), len, rows, T, d, m->V, x,
                       m->d_err.as<int>(), ss));
@@ -527,7 +528,7 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, nql, rows, x, eo, po));
     } else {
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, nql, rows, m->tp.local_partial(), eo));
-      RUAI_TRY(ruai_tp_allreduce_add(c, &m->tp, x, rows, d, m->d_err.as<int>()));
+      RUAI_TRY(ruai_tp_allreduce_add(c, &m->tp, x, rows, d, m->d_err.as<int>(), ss));
     }
     ss_tiles = d_tiles;
     GemvEpilogue eu;
@@ -553,7 +554,7 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
       RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, rows, x, ed, pd));
     } else {
       RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, rows, m->tp.local_partial(), ed));
-      RUAI_TRY(ruai_tp_allreduce_add(c, &m->tp, x, rows, d, m->d_err.as<int>()));
+      RUAI_TRY(ruai_tp_allreduce_add(c, &m->tp, x, rows, d, m->d_err.as<int>(), ss));
     }
   }
   const float* hx = x;

@@ -62,8 +62,9 @@ __device__ bool bounded_wait(const unsigned* flag, unsigned want) {
 }
 
 __global__ void __launch_bounds__(256) allreduce_push_kernel(TpDev t, const float* __restrict__ partial, float* __restrict__ x, uint32_t count4,
-                                                             int* err) {
+                                                             int* err, float* __restrict__ sumsq) {
   __shared__ int s_ok;
+  __shared__ float s_sq[8];
   grid_dependency_wait();
   grid_launch_dependents();
   const unsigned seq = *(volatile unsigned*)&t.seq[0] + 1u;
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(TpDev t, const floa
     if (threadIdx.x == 0) atomicExch(err, 2);
   } else {
     float4* xv = reinterpret_cast<float4*>(x);
+    float sq = 0.0f;
     for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
       for (uint32_t p = 0; p < t.world; ++p) {  // rank order: identical bits everywhere
@@ -100,6 +102,18 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(TpDev t, const floa
       float4 r = xv[i];
       r.x += s.x; r.y += s.y; r.z += s.z; r.w += s.w;
       xv[i] = r;
+      sq = fmaf(r.x, r.x, sq); sq = fmaf(r.y, r.y, sq); sq = fmaf(r.z, r.z, sq); sq = fmaf(r.w, r.w, sq);
+    }
+    if (sumsq) {  // single-CTA, single-row launches only: the sum of squares the next RMSNorm needs, in a fixed order
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+      if ((threadIdx.x & 31) == 0) s_sq[threadIdx.x >> 5] = sq;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float tot = 0.0f;
+        for (int w = 0; w < 8; ++w) tot += s_sq[w];
+        sumsq[0] = tot;
+      }
     }
   }
   // the last CTA to finish advances the sequence number
@@ -237,11 +251,14 @@ int ruai_tp_check_ready(ruai_ctx* c, ruai_tp_state* t, uint32_t rows, uint32_t d
   return RUAI_OK;
 }
 
-int ruai_tp_allreduce_add(ruai_ctx* c, ruai_tp_state* t, float* x, uint32_t rows, uint32_t d, int* err) {
+bool ruai_tp_allreduce_gives_sumsq(uint32_t rows, uint32_t d) { return rows == 1 && d / 4 <= 1024; }
+
+int ruai_tp_allreduce_add(ruai_ctx* c, ruai_tp_state* t, float* x, uint32_t rows, uint32_t d, int* err, float* sumsq) {
   const uint32_t count4 = (uint32_t)((size_t)rows * d / 4);
   uint32_t ctas = (count4 + 1023) / 1024;  // 4 float4 per thread
   ctas = ctas < 1 ? 1 : (ctas > kTpMaxCtas ? kTpMaxCtas : ctas);
-  RUAI_CUDA(c, ruai_launch(c, allreduce_push_kernel, dim3(ctas), dim3(256), 0, true, make_dev(t), (const float*)t->partial, x, count4, err));
+  if (sumsq && !(ctas == 1 && rows == 1)) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the exchange gives the sum of squares only for one row in one CTA");
+  RUAI_CUDA(c, ruai_launch(c, allreduce_push_kernel, dim3(ctas), dim3(256), 0, true, make_dev(t), (const float*)t->partial, x, count4, err, sumsq));
   return RUAI_OK;
 }
 

@@ -24,6 +24,8 @@ int ruai_tp_export_handle(ruai_ctx* c, ruai_tp_state* t, void* handle_out);
 int ruai_tp_connect_handles(ruai_ctx* c, ruai_tp_state* t, const void* handles);
 int ruai_tp_check_ready(ruai_ctx* c, ruai_tp_state* t, uint32_t rows, uint32_t d);
 // x[rows, d] += sum over ranks of partial[rows, d], the same bits on every rank.
-int ruai_tp_allreduce_add(ruai_ctx* c, ruai_tp_state* t, float* x, uint32_t rows, uint32_t d, int* err);
+// With `sumsq` (one row, d <= 4096 only) it also leaves sum(x^2) of the new row there, as one tile.
+int ruai_tp_allreduce_add(ruai_ctx* c, ruai_tp_state* t, float* x, uint32_t rows, uint32_t d, int* err, float* sumsq = nullptr);
+bool ruai_tp_allreduce_gives_sumsq(uint32_t rows, uint32_t d);
 // Greedy argmax over a vocabulary split by columns: out[row] = global index of the maximum.
 int ruai_tp_argmax(ruai_ctx* c, ruai_tp_state* t, const float* logits, uint32_t n_local, uint32_t rows, uint32_t col_offset, int32_t* out, int* err);
