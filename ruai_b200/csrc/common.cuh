@@ -31,7 +31,8 @@ struct ruai_ctx {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool use_pdl = true;  // programmatic dependent launch between consecutive kernels
   bool use_bulk = true; // bulk-copy staged GEMV (gemv_bulk.cu) where the weight allows it
-  bool use_tc = true;   // tensor-core GEMV (gemv_tc.cu) for int4 group-32 weights and up to 4 rows
+  bool use_tc = true;   // tensor-core GEMV (gemv_tc.cu, gemv_tc8.cu) for chunk-layout weights and up to 16 rows
+  unsigned force_splits = 0;  // debug: overrides the split-K choice of the tensor-core GEMVs (0 = automatic)
   void* prof = nullptr;  // debug: device buffer for cycle stamps (set by ruai_debug_set_prof)
   unsigned long long* trace = nullptr;  // debug: per-launch [first entry, first past the dependency wait, last exit] in ns
   unsigned trace_slots = 0, trace_seq = 0;
@@ -201,6 +202,9 @@ int ruai_gemv_bulk_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, i
 bool ruai_gemv_tc_eligible(const ruai_qweight* w, uint32_t m);
 int ruai_gemv_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                         const GemvEpilogue& epi, const GemvPrologue& pro);
+bool ruai_gemv_tc8_eligible(const ruai_qweight* w, uint32_t m);
+int ruai_gemv_tc8_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
+                         const GemvEpilogue& epi, const GemvPrologue& pro);
 bool ruai_gemm_tc_eligible(const ruai_qweight* w, uint32_t m);
 int ruai_gemm_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                         const GemvEpilogue& epi, const GemvPrologue& pro);

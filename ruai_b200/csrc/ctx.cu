@@ -171,6 +171,11 @@ RUAI_API int ruai_debug_set_prof(ruai_ctx* c, void* dev_buf) {
   return RUAI_OK;
 }
 
+RUAI_API int ruai_debug_force_splits(ruai_ctx* c, unsigned splits) {
+  c->force_splits = splits;
+  return RUAI_OK;
+}
+
 RUAI_API int ruai_debug_trace(ruai_ctx* c, void* dev_buf, unsigned slots) {
   c->trace = (unsigned long long*)dev_buf;
   c->trace_slots = slots;

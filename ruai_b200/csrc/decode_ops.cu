@@ -164,11 +164,11 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 // With p.fuse (single new token per sequence) the kernel also does apply_rope
 // (functional.rs:197-204) on q and on the new key and appends the new key / value to the
 // cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
-constexpr int kAttnOutPerThread = 4;  // (rep * hd) / (64 * rep) for hd up to 256
+constexpr int kAttnOutPerThread = 8;  // (rep * hd) / (threads = 32 * blocks * rep) for hd up to 256
 
 template <int REP>
-__global__ void __launch_bounds__(64 * REP) attention_kernel(const AttnParams p) {
-  constexpr int kThreads = 64 * REP, kBlocks = kAttnChunkKeys / 32;
+__global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const AttnParams p) {
+  constexpr int kThreads = kAttnChunkKeys * REP, kBlocks = kAttnChunkKeys / 32;
   extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs | stats | merge
   __shared__ __align__(8) uint64_t kv_bar;
   __shared__ unsigned s_last;
@@ -524,7 +524,7 @@ cudaError_t launch_attn(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem
     if (e != cudaSuccess) return e;
     attr_done[c->ordinal & 63] = true;
   }
-  return ruai_launch(c, attention_kernel<REP>, grid, dim3(64 * REP), smem, true, p);
+  return ruai_launch(c, attention_kernel<REP>, grid, dim3(kAttnChunkKeys * REP), smem, true, p);
 }
 
 }  // namespace

@@ -373,6 +373,7 @@ cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
   if (!attr_done[c->ordinal & 63]) {
     cudaError_t e = cudaFuncSetAttribute(gemv_tc_int4_kernel<MT, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT>::bytes(8));
     if (e != cudaSuccess) return e;
+
     attr_done[c->ordinal & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -419,9 +420,19 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   const uint32_t row_tiles = (m + mt - 1) / mt;
   if (epi.argmax_out && row_tiles != 1) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "fused argmax needs a single row tile");
   const uint32_t col_tiles = (w->n + kCols - 1) / kCols;
-  // split k over a cluster until there are about two CTAs per SM, keeping at least two ring stages per CTA
+  // Split k over a cluster of up to 8 CTAs.  A launch is a link in a chain of
+  // dependent kernels, so what counts is its latency: waves x (fixed cost + stages per CTA x time per stage).
+  const uint32_t slots = 4u * (uint32_t)c->sm_count;
   uint32_t splits = 1;
-  while (splits < 8 && col_tiles * row_tiles * splits < 2u * (uint32_t)c->sm_count && w->chunks / (splits * 2) >= 2u * kStageGroups) splits *= 2;
+  double best = 1e30;
+  for (uint32_t s2 = 1; s2 <= 8; s2 *= 2) {  // 16-CTA clusters were tried: fewer clusters fit at once and the launch got slower
+    const uint32_t per = (w->chunks + s2 - 1) / s2;
+    if (s2 > 1 && per < (uint32_t)kStageGroups) break;
+    const uint32_t stages = (per + kStageGroups - 1) / kStageGroups;
+    const uint32_t waves = (col_tiles * row_tiles * s2 + slots - 1) / slots;
+    const double t = waves * (4.7 + 1.5 * stages + 0.15 * s2);
+    if (t < best) { best = t; splits = s2; }
+  }
   uint32_t cpc = (w->chunks + splits - 1) / splits;
   cpc = (cpc + kStageGroups - 1) / kStageGroups * kStageGroups;
   Params p;
