@@ -19,10 +19,15 @@
 // scale[g,j] * 2^(e-20).  The rounding of x to 21 significant bits relative to its group
 // maximum is the only approximation (relative error of a group sum about 2^-21).
 //
-// Data movement is that of gemv_bulk.cu: a ring of bulk asynchronous copies of the chunk
-// layout (2 KB of packed weights + 512 B of scales per group and 128-column tile), filled
-// before the grid-dependency wait; split-K over a cluster with the partial sums sent
-// through distributed shared memory; bounded waits everywhere.
+// Organisation of a CTA (128 columns of W, a slice of k): three kinds of warps that only meet at mbarriers,
+// so that the latency of one kind's work hides behind the others'.
+//   * four expanding warps (thread = column): the packed weights of their column come straight from global memory
+//     into registers, some stages ahead of their use and requested before the grid-dependency wait (weights do not
+//     depend on the predecessor); nibbles -> bytes into one of kBufs A operand buffers in shared memory;
+//   * one warp whose first lane issues the MMAs of a stage (one per scale group) and commits them;
+//   * four draining warps (thread = column): digits of the activations a round (16 groups) ahead, and per stage
+//     the sums out of tensor memory, scaled and accumulated in f32; they run the epilogue.
+// Split-K over a cluster with the partial sums sent through distributed shared memory; bounded waits everywhere.
 #include "common.cuh"
 #include "gemv_epilogue.cuh"
 #include "pipeline.cuh"
@@ -31,13 +36,17 @@ namespace gemv_tc {
 
 using namespace pipe;
 
-constexpr int kCols = kGemvBulkTileCols;  // 128 = MMA M = TMEM lanes = threads
-constexpr int kStageGroups = 4;           // scale groups (chunks) per ring stage
+constexpr int kCols = kGemvBulkTileCols;  // 128 = MMA M = TMEM lanes
+constexpr int kStageGroups = 4;           // scale groups (chunks) per stage
 constexpr int kRoundGroups = 16;          // groups per conversion round of the activations
+constexpr int kRoundStages = kRoundGroups / kStageGroups;
 constexpr int kLimbs = 3;
-// MMA N (rows x limbs, padded to a multiple of 16) and the TMEM columns of two stages of accumulators
-constexpr int n_of(int mt) { return mt <= 4 ? 16 : mt <= 8 ? 32 : 48; }
-constexpr int tmem_cols_of(int mt) { return 2 * kStageGroups * n_of(mt) <= 128 ? 128 : 2 * kStageGroups * n_of(mt) <= 256 ? 256 : 512; }
+constexpr int kThreads = 2 * kCols + 32;  // draining warps 0-3, issuing warp 4, expanding warps 5-8
+constexpr int kExpand0 = kCols + 32;      // first expanding thread
+// MMA N (rows x limbs, padded to a multiple of 16), stage buffers (A operand + accumulators), TMEM columns
+constexpr int n_of(int mt) { return mt <= 4 ? 16 : 32; }
+constexpr int bufs_of(int mt) { return mt <= 4 ? 4 : 2; }
+constexpr int tmem_cols_of(int mt) { return bufs_of(mt) * kStageGroups * n_of(mt); }  // 256
 
 struct Params {
   const uint4* w;
@@ -49,32 +58,33 @@ struct Params {
   int* status;
   GemvEpilogue epi;
   GemvPrologue pro;
-  long long* prof;  // debug: cycle stamps of one CTA (NULL in normal use)
 };
 
 template <int MT>
 struct Smem {
   static constexpr int kN = n_of(MT);
+  static constexpr int kBufs = bufs_of(MT);
   static constexpr size_t off_a = 0;
-  static constexpr size_t off_b = off_a + 2 * (size_t)kStageGroups * kCols * 32;
+  static constexpr size_t off_b = off_a + (size_t)kBufs * kStageGroups * kCols * 32;
   static constexpr size_t off_meta = off_b + 2 * (size_t)kRoundGroups * kN * 32;
   static constexpr size_t off_red = off_meta + 2 * (size_t)kRoundGroups * MT * 8;
   static size_t bytes(uint32_t splits) { return off_red + (size_t)splits * MT * kCols * 4 + 128; }
 };
 
-constexpr int kThreads = kCols + 32;  // four loading / converting / draining warps and one MMA-issuing warp
-
-// kAheadStages: stages of packed weights held in registers ahead of their use (2: more CTAs per SM; 4: more
-// bytes in flight per CTA, for launches with few CTAs per SM).
-template <int MT, int kAheadStages>
-__global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) {
+// kAhead: stages of packed weights an expanding thread holds in registers ahead of their use.
+template <int MT, int kAhead>
+__global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel(const Params p) {
   constexpr int kN = n_of(MT);
+  constexpr int kBufs = bufs_of(MT);
   constexpr int kTmemCols = tmem_cols_of(MT);
   static_assert(MT * kLimbs <= kN, "rows x limbs must fit the MMA N");
+  static_assert((kBufs & (kBufs - 1)) == 0 && kRoundStages % kBufs == 0, "stage buffers must divide a round");
   using L = Smem<MT>;
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t a_ready[2];      // A operand (and digits) of a stage written (4 warp arrivals)
-  __shared__ __align__(8) uint64_t mma_done[2];     // MMAs of a stage completed
+  __shared__ __align__(8) uint64_t a_ready[kBufs];   // A operand of a stage written (4 expanding warps)
+  __shared__ __align__(8) uint64_t mma_done[kBufs];  // MMAs of a stage completed: sums valid, A buffer free
+  __shared__ __align__(8) uint64_t acc_free[kBufs];  // sums of a stage read out of tensor memory (4 draining warps)
+  __shared__ __align__(8) uint64_t b_ready[2];       // digits of a round written (4 draining warps)
   __shared__ uint32_t s_tmem;
   __shared__ float s_rstd[MT];
   __shared__ float s_red[kThreads / 32];
@@ -83,29 +93,26 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
   __shared__ volatile int s_abort;
   unsigned char* abuf = smem + L::off_a;
   unsigned char* bop = smem + L::off_b;
-  float* meta_scale = reinterpret_cast<float*>(smem + L::off_meta);        // [2][kRoundGroups][MT]
+  float* meta_scale = reinterpret_cast<float*>(smem + L::off_meta);  // [2][kRoundGroups][MT]
   int* meta_sum = reinterpret_cast<int*>(smem + L::off_meta) + 2 * kRoundGroups * MT;
   float* red = reinterpret_cast<float*>(smem + L::off_red);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  long long* prof = (p.prof && blockIdx.x == 7 && blockIdx.y == 0 && (tid == 0 || tid == 64)) ? p.prof + (tid ? 512 : 0) : nullptr;
-  int pn = 0;
-#define STAMP() do { if (prof && pn < 500) prof[pn++] = clock64(); } while (0)
-  STAMP();
   const uint32_t j0 = blockIdx.x * kCols;
   const uint32_t j = j0 + tid;
   const bool active = tid < kCols && j < p.n;
-  const uint32_t cols = min((uint32_t)kCols, p.n - j0);
   const uint32_t split = p.splits > 1 ? cluster_ctarank() : 0u;
   const uint32_t m0 = blockIdx.z * MT;
   const uint32_t rows = min((uint32_t)MT, p.m - m0);
   const uint32_t c_begin = min(p.chunks, split * p.chunks_per_cta);
   const uint32_t c_end = min(p.chunks, c_begin + p.chunks_per_cta);
   const uint32_t nst = (c_end - c_begin + kStageGroups - 1) / kStageGroups;
-  constexpr uint32_t kRoundStages = kRoundGroups / kStageGroups;
+  const uint32_t nrounds = (nst + kRoundStages - 1) / kRoundStages;
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&a_ready[s], kCols / 32); mbar_init(&mma_done[s], 1); }
+    for (int s = 0; s < kBufs; ++s) { mbar_init(&a_ready[s], kCols / 32); mbar_init(&mma_done[s], 1); mbar_init(&acc_free[s], kCols / 32); }
+    mbar_init(&b_ready[0], kCols / 32);
+    mbar_init(&b_ready[1], kCols / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_abort = 0;
   }
@@ -117,78 +124,131 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem;
-  STAMP();
-  // packed weights and scales of this thread's column, kAheadStages stages ahead of their use.  They do not
-  // depend on the predecessor kernel: the first ones are requested before waiting for it.
-  uint4 wq[kAheadStages][kStageGroups];
-  float sq[kAheadStages][kStageGroups];
-  auto load_stage = [&](uint32_t i, uint4 (&wv)[kStageGroups], float (&sv)[kStageGroups]) {
-#pragma unroll
-    for (int u = 0; u < kStageGroups; ++u) {
-      const uint32_t c = c_begin + i * kStageGroups + u;
-      const bool in = tid < kCols && j < p.n && i < nst && c < c_end;
-      wv[u] = in ? __ldcs(&p.w[(size_t)c * p.n + j]) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-      sv[u] = in ? __ldcs(&p.scale[(size_t)c * p.n + j]) : 0.0f;
-    }
-  };
-  if (tid < kCols) {
-#pragma unroll
-    for (int a = 0; a < kAheadStages; ++a) load_stage(a, wq[a], sq[a]);
-  }
   if (tid == 0) {  // warm the L2 for the kernel after this one
     const uint32_t cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y * gridDim.z;
     l2_prefetch_share(p.pro.next_data, p.pro.next_data_bytes, cta, n_ctas);
     l2_prefetch_share(p.pro.next_scale, p.pro.next_scale_bytes, cta, n_ctas);
   }
-  if (tid == 0) trace_min(p.pro.trace, 0);
-  grid_dependency_wait();
-  if (tid == 0) trace_min(p.pro.trace, 1);
-  grid_launch_dependents();
-  // RMSNorm: x * rstd * w with rstd a per-row scalar, so the digits are taken from x * w and rstd multiplies
-  // the finished sums; its inputs are fetched now and not needed before the end.
   const bool normed = p.pro.norm_w != nullptr;
-  if (normed && warp == kCols / 32 && lane < MT) {
-    float ss = 0.0f;
-    if (lane < (int)rows)
-      for (uint32_t t = 0; t < p.pro.tiles; ++t) ss += p.pro.sumsq[(size_t)t * p.m + m0 + lane];
-    s_rstd[lane] = 1.0f / sqrtf(ss * (1.0f / (float)p.k) + p.pro.eps);
-  }
-  // the residual this CTA will add in its epilogue, fetched before the main loop
-  float resid_pre[MT];
-  const bool pre = p.epi.resid != nullptr && p.epi.act != ACT_SWIGLU && split == 0 && active;
-#pragma unroll
-  for (int r = 0; r < MT; ++r) resid_pre[r] = (pre && r < (int)rows) ? p.epi.resid[(size_t)(m0 + r) * p.epi.out_ld + j] : 0.0f;
-
   float acc[MT];
+  float resid_pre[MT];
 #pragma unroll
-  for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
+  for (int r = 0; r < MT; ++r) { acc[r] = 0.0f; resid_pre[r] = 0.0f; }
+  const bool pre = p.epi.resid != nullptr && p.epi.act != ACT_SWIGLU && split == 0 && active;
 
-  if (warp == kCols / 32) {
-    // ===== MMA issuer: one thread =====
+  if (warp > kCols / 32) {
+    // ===== expanding warps: packed weights -> A operand.  Nothing here depends on the predecessor kernel, so
+    // these warps do not wait for it: the first kBufs stages are in place before the activations exist. =====
+    const int te = tid - kExpand0;
+    const uint32_t je = j0 + te;
+    const bool in_col = je < p.n;
+    uint4 wq[kAhead][kStageGroups];
+    auto load_stage = [&](uint32_t i, uint4 (&wv)[kStageGroups]) {
+#pragma unroll
+      for (int u = 0; u < kStageGroups; ++u) {
+        const uint32_t c = c_begin + i * kStageGroups + u;
+        // beyond the slice or the matrix: stored value 8 is weight 0
+        wv[u] = (in_col && c < c_end) ? __ldcs(&p.w[(size_t)c * p.n + je]) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+      }
+    };
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) load_stage(a, wq[a]);
+    bool ok = true;
+    // the register queue is addressed statically (stage i sits in wq[i % kAhead]): moving it along would make every
+    // stage wait for the newest loads
+    for (uint32_t i0 = 0; i0 < nst && ok; i0 += kAhead) {
+#pragma unroll
+      for (int a = 0; a < kAhead; ++a) {
+        const uint32_t i = i0 + a;
+        if (i >= nst) break;
+        const uint32_t b = i & (kBufs - 1), q = i / kBufs;
+        if (q > 0 && (s_abort || !mbar_wait(&mma_done[b], (q - 1) & 1u))) { ok = false; break; }  // the MMAs that read this buffer last are done
+        // nibbles -> bytes: 32 rows of this thread's column become one row of two 16-byte k-halves of A
+#pragma unroll
+        for (int u = 0; u < kStageGroups; ++u) {
+          const uint4 wv = wq[a][u];
+          uint4 lo, hi;
+          lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
+          lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
+          lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
+          lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
+          unsigned char* dst = abuf + ((size_t)b * kStageGroups + u) * (kCols * 32) + (size_t)te * 16;
+          *reinterpret_cast<uint4*>(dst) = lo;
+          *reinterpret_cast<uint4*>(dst + kCols * 16) = hi;
+        }
+        load_stage(i + kAhead, wq[a]);  // the stage kAhead further on, into the registers just consumed
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_ready[b]);
+      }
+    }
+    if (!ok) s_abort = 1;
+  } else if (warp == kCols / 32) {
+    // ===== issuing warp =====
+    if (tid == kCols) trace_min(p.pro.trace, 0);
+    grid_dependency_wait();
+    if (tid == kCols) trace_min(p.pro.trace, 1);
+    grid_launch_dependents();
+    // RMSNorm: x * rstd * w with rstd a per-row scalar, so the digits are taken from x * w and rstd multiplies
+    // the finished sums
+    if (normed && lane < MT) {
+      float ss = 0.0f;
+      if (lane < (int)rows)
+        for (uint32_t t = 0; t < p.pro.tiles; ++t) ss += p.pro.sumsq[(size_t)t * p.m + m0 + lane];
+      s_rstd[lane] = 1.0f / sqrtf(ss * (1.0f / (float)p.k) + p.pro.eps);
+    }
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8(kN, false);
-      for (uint32_t i = 0; i < nst; ++i) {
-        if (s_abort || !mbar_wait(&a_ready[i & 1], (i >> 1) & 1u)) { s_abort = 1; break; }
+      // descriptors of the first operand slots; the loop only adds to their address fields
+      const uint64_t ad0 = umma_desc_kmajor(smem_u32(abuf), kCols * 16, 128);
+      const uint64_t bd0 = umma_desc_kmajor(smem_u32(bop), kN / 8 * 128, 128);
+      uint32_t left = c_end - c_begin;
+      for (uint32_t i = 0; i < nst; ++i, left -= kStageGroups) {
+        const uint32_t b = i & (kBufs - 1), q = i / kBufs;
+        bool ok = !s_abort;
+        if (ok && (i % kRoundStages) == 0) ok = mbar_wait(&b_ready[(i / kRoundStages) & 1u], (i / (2 * kRoundStages)) & 1u);  // digits of the round
+        if (ok && q > 0) ok = mbar_wait(&acc_free[b], (q - 1) & 1u);  // the sums these MMAs overwrite have been read
+        if (ok) ok = mbar_wait(&a_ready[b], q & 1u);
+        if (!ok) { s_abort = 1; break; }
         tc_fence_after_sync();
-        const uint32_t rb = (i / kRoundStages) & 1u, g0 = (i % kRoundStages) * kStageGroups;
-        const uint32_t nch = min((uint32_t)kStageGroups, c_end - (c_begin + i * kStageGroups));
-        for (uint32_t u = 0; u < nch; ++u) {
-          const uint64_t ad = umma_desc_kmajor(smem_u32(abuf + ((size_t)(i & 1) * kStageGroups + u) * (kCols * 32)), kCols * 16, 128);
-          const uint64_t bd = umma_desc_kmajor(smem_u32(bop + ((size_t)rb * kRoundGroups + g0 + u) * (kN * 32)), kN / 8 * 128, 128);
-          umma_i8(tmem_base + ((i & 1) * kStageGroups + u) * kN, ad, bd, idesc, 0u);
+        const uint32_t slot = b * kStageGroups;                            // A and accumulator slots of this stage
+        const uint32_t gb = (i & (2 * kRoundStages - 1)) * kStageGroups;   // first group in the two rounds of digits
+        const uint64_t ad = umma_desc_advance(ad0, slot * (kCols * 32));
+        const uint64_t bd = umma_desc_advance(bd0, gb * (kN * 32));
+        const uint32_t d = tmem_base + slot * kN;
+        if (left >= (uint32_t)kStageGroups) {
+#pragma unroll
+          for (uint32_t u = 0; u < (uint32_t)kStageGroups; ++u)
+            umma_i8(d + u * kN, umma_desc_advance(ad, u * (kCols * 32)), umma_desc_advance(bd, u * (kN * 32)), idesc, 0u);
+        } else {
+          for (uint32_t u = 0; u < left; ++u)
+            umma_i8(d + u * kN, umma_desc_advance(ad, u * (kCols * 32)), umma_desc_advance(bd, u * (kN * 32)), idesc, 0u);
         }
-        umma_commit(&mma_done[i & 1]);
+        umma_commit(&mma_done[b]);
       }
     }
   } else {
-    // ===== four warps: activations -> digits, nibbles -> bytes, scaled sums out of TMEM =====
+    // ===== draining warps: digits of the activations, scaled sums out of tensor memory =====
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float sv_prev[kStageGroups] = {0.f, 0.f, 0.f, 0.f};
-    // activations of one round (16 groups = 512 values per row): 4 consecutive values per thread, fetched a round ahead
-    float4 xnext[MT];
-    auto fetch_round = [&](uint32_t stage0) {
-      const uint32_t kidx = (c_begin + stage0 * kStageGroups) * 32 + 4 * tid;
-      const bool in = stage0 < nst && c_begin + stage0 * kStageGroups + tid / 8 < c_end;
+    // scales of this thread's column one round ahead of their use; they do not depend on the predecessor
+    float sq[kRoundStages][kStageGroups];
+    auto load_scales = [&](uint32_t i, float (&sv)[kStageGroups]) {
+#pragma unroll
+      for (int u = 0; u < kStageGroups; ++u) {
+        const uint32_t c = c_begin + i * kStageGroups + u;
+        sv[u] = (active && c < c_end) ? __ldcs(&p.scale[(size_t)c * p.n + j]) : 0.0f;
+      }
+    };
+#pragma unroll
+    for (int a = 0; a < kRoundStages; ++a) load_scales(a, sq[a]);
+    grid_dependency_wait();
+#pragma unroll
+    for (int r = 0; r < MT; ++r) resid_pre[r] = (pre && r < (int)rows) ? p.epi.resid[(size_t)(m0 + r) * p.epi.out_ld + j] : 0.0f;
+    // activations of one round (16 groups = 512 values per row): 4 consecutive values per thread
+    auto fetch_round = [&](uint32_t round, float4 (&dst)[MT]) {
+      const uint32_t g = c_begin + round * kRoundGroups + tid / 8;
+      const uint32_t kidx = (c_begin + round * kRoundGroups) * 32 + 4 * tid;
+      const bool in = round < nrounds && g < c_end;
 #pragma unroll
       for (int r = 0; r < MT; ++r) {
         float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -201,139 +261,118 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
             }
           }
         }
-        xnext[r] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[r] = make_float4(v[0], v[1], v[2], v[3]);
       }
     };
-    fetch_round(0);
-    STAMP();
+    // this warp's 4 groups of a round (8 lanes per group): block fixed point, three int8 digits into the B operand
+    auto convert = [&](uint32_t round, const float4 (&src)[MT]) {
+      const uint32_t rb = round & 1u;
+      const uint32_t gi = warp * 4 + (lane >> 3);
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        const float4 xv = src[r];
+        float gmax = fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w)));
+        gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 1));
+        gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 2));
+        gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 4));
+        // gmax < 2^e with e = biased exponent - 126; f = round(v * 2^(20-e)), x = f * 2^(e-20)
+        const uint32_t eb = __float_as_uint(gmax) >> 23;
+        const bool nz = eb >= 20u && eb < 255u;
+        const float up = nz ? __uint_as_float((273u - eb) << 23) : 0.0f;
+        const float xscale = nz ? __uint_as_float((eb - 19u) << 23) : 0.0f;
+        const float vv[4] = {xv.x, xv.y, xv.z, xv.w};
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+        int fs = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int f = __float2int_rn(vv[t] * up);
+          const int d2 = ((f + 64) & 127) - 64;
+          const int t1 = (f - d2) >> 7;
+          const int d1 = ((t1 + 64) & 127) - 64;
+          const int d0 = (t1 - d1) >> 7;
+          fs += f;
+          w0 |= (uint32_t)(d0 & 0xFF) << (8 * t);
+          w1 |= (uint32_t)(d1 & 0xFF) << (8 * t);
+          w2 |= (uint32_t)(d2 & 0xFF) << (8 * t);
+        }
+        fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 1);
+        fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 2);
+        fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 4);
+        unsigned char* bg = bop + ((size_t)rb * kRoundGroups + gi) * (kN * 32) + ((lane & 7) >> 2) * (kN / 8 * 128) + ((4 * (lane & 7)) & 15);
+        const uint32_t ww[kLimbs] = {w0, w1, w2};
+#pragma unroll
+        for (int t = 0; t < kLimbs; ++t) {
+          const uint32_t nrow = r * kLimbs + t;
+          *reinterpret_cast<uint32_t*>(bg + (nrow >> 3) * 128 + (nrow & 7) * 16) = ww[t];
+        }
+        if ((lane & 7) == 0) {
+          meta_scale[(rb * kRoundGroups + gi) * MT + r] = xscale;
+          meta_sum[(rb * kRoundGroups + gi) * MT + r] = fs;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&b_ready[rb]);
+    };
+    float4 xa[MT], xb[MT];
+    fetch_round(0, xa);
+    fetch_round(1, xb);
+    convert(0, xa);
+    if (nrounds > 1) convert(1, xb);
+    fetch_round(2, xa);
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the rounds' scales and sums are visible to the four warps
 
-    // scaled sums of stage s (its MMAs must have completed) into acc
-    auto drain = [&](uint32_t s, const float (&sv)[kStageGroups]) -> bool {
-      if (!mbar_wait(&mma_done[s & 1], (s >> 1) & 1u)) return false;
-      tc_fence_after_sync();
-      const uint32_t rb = (s / kRoundStages) & 1u;
-      const uint32_t g0 = (s % kRoundStages) * kStageGroups;
-      const uint32_t nch = min((uint32_t)kStageGroups, c_end - (c_begin + s * kStageGroups));
-      constexpr int kQ = (MT * kLimbs + 3) / 4;  // 4-column loads per group
-      constexpr int kBatch = MT <= 4 ? kStageGroups : 1;  // groups whose sums are in registers at once
+    bool ok = true;
+    // a warp whose wait ran out still walks the rounds, so that the four warps meet at every barrier below
+    for (uint32_t round = 0; round < nrounds; ++round) {
+      const uint32_t rb = round & 1u;
 #pragma unroll
-      for (int u0 = 0; u0 < kStageGroups; u0 += kBatch) {
-        int32_t d[kBatch][kQ * 4];
+      for (int a = 0; a < kRoundStages; ++a) {
+        const uint32_t i = round * kRoundStages + a;
+        if (i >= nst || !ok) break;
+        const uint32_t b = a & (kBufs - 1), q = i / kBufs;
+        if (s_abort || !mbar_wait(&mma_done[b], q & 1u)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t nch = min((uint32_t)kStageGroups, c_end - (c_begin + i * kStageGroups));
+        constexpr int kQ = (MT * kLimbs + 3) / 4;  // 4-column loads per group
+        int32_t d[kStageGroups][kQ * 4];
 #pragma unroll
-        for (int ub = 0; ub < kBatch; ++ub) {
-          const uint32_t col = tmem_base + lane_base + ((s & 1) * kStageGroups + u0 + ub) * kN;
+        for (int u = 0; u < kStageGroups; ++u) {
+          const uint32_t col = tmem_base + lane_base + (b * kStageGroups + u) * kN;
 #pragma unroll
           for (int q4 = 0; q4 < kQ; ++q4) {
             int32_t t4[4];
             tmem_ld4(col + 4 * q4, t4);  // groups past the end hold stale sums; they are not used below
-            d[ub][4 * q4 + 0] = t4[0]; d[ub][4 * q4 + 1] = t4[1]; d[ub][4 * q4 + 2] = t4[2]; d[ub][4 * q4 + 3] = t4[3];
+            d[u][4 * q4 + 0] = t4[0]; d[u][4 * q4 + 1] = t4[1]; d[u][4 * q4 + 2] = t4[2]; d[u][4 * q4 + 3] = t4[3];
           }
         }
         tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_free[b]);  // the next MMAs into this buffer may go
 #pragma unroll
-        for (int ub = 0; ub < kBatch; ++ub) {
-          const int u = u0 + ub;
+        for (int u = 0; u < kStageGroups; ++u) {
           if ((uint32_t)u < nch) {
 #pragma unroll
             for (int r = 0; r < MT; ++r) {
-              const uint32_t mi = (rb * kRoundGroups + g0 + u) * MT + r;
-              const int val = d[ub][kLimbs * r] * 16384 + d[ub][kLimbs * r + 1] * 128 + d[ub][kLimbs * r + 2] - 8 * meta_sum[mi];
-              acc[r] = fmaf((float)val, sv[u] * meta_scale[mi], acc[r]);
+              const uint32_t mi = (rb * kRoundGroups + a * kStageGroups + u) * MT + r;
+              const int val = d[u][kLimbs * r] * 16384 + d[u][kLimbs * r + 1] * 128 + d[u][kLimbs * r + 2] - 8 * meta_sum[mi];
+              acc[r] = fmaf((float)val, sq[a][u] * meta_scale[mi], acc[r]);
             }
           }
         }
+        load_scales(i + kRoundStages, sq[a]);
       }
-      tc_fence_before_sync();
-      return true;
-    };
-
-    bool ok = true;
-    for (uint32_t i = 0; i < nst && ok; ++i) {
-      if (s_abort) { ok = false; break; }
-      const uint32_t rb = (i / kRoundStages) & 1u;
-      if (i % kRoundStages == 0) {
-        // ---- this warp's 4 groups of the round (8 lanes per group): block fixed point, three int8 digits ----
-        const uint32_t gi = warp * 4 + (lane >> 3);
-#pragma unroll
-        for (int r = 0; r < MT; ++r) {
-          const float4 xv = xnext[r];
-          float gmax = fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w)));
-          gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 1));
-          gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 2));
-          gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 4));
-          // gmax < 2^e with e = biased exponent - 126; f = round(v * 2^(20-e)), x = f * 2^(e-20)
-          const uint32_t eb = __float_as_uint(gmax) >> 23;
-          const bool nz = eb >= 20u && eb < 255u;
-          const float up = nz ? __uint_as_float((273u - eb) << 23) : 0.0f;
-          const float xscale = nz ? __uint_as_float((eb - 19u) << 23) : 0.0f;
-          const float vv[4] = {xv.x, xv.y, xv.z, xv.w};
-          uint32_t w0 = 0, w1 = 0, w2 = 0;
-          int fs = 0;
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int f = __float2int_rn(vv[t] * up);
-            const int d2 = ((f + 64) & 127) - 64;
-            const int t1 = (f - d2) >> 7;
-            const int d1 = ((t1 + 64) & 127) - 64;
-            const int d0 = (t1 - d1) >> 7;
-            fs += f;
-            w0 |= (uint32_t)(d0 & 0xFF) << (8 * t);
-            w1 |= (uint32_t)(d1 & 0xFF) << (8 * t);
-            w2 |= (uint32_t)(d2 & 0xFF) << (8 * t);
-          }
-          fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 1);
-          fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 2);
-          fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 4);
-          unsigned char* bg = bop + ((size_t)rb * kRoundGroups + gi) * (kN * 32) + ((lane & 7) >> 2) * (kN / 8 * 128) + ((4 * (lane & 7)) & 15);
-          const uint32_t ww[kLimbs] = {w0, w1, w2};
-#pragma unroll
-          for (int t = 0; t < kLimbs; ++t) {
-            const uint32_t nrow = r * kLimbs + t;
-            *reinterpret_cast<uint32_t*>(bg + (nrow >> 3) * 128 + (nrow & 7) * 16) = ww[t];
-          }
-          if ((lane & 7) == 0) {
-            meta_scale[(rb * kRoundGroups + gi) * MT + r] = xscale;
-            meta_sum[(rb * kRoundGroups + gi) * MT + r] = fs;
-          }
+      if (round + 2 < nrounds) {
+        // every MMA of this round is complete and (after the barrier) every warp has used its scales and sums:
+        // the round after next takes its place
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok) {
+          convert(round + 2, xa);
+          fetch_round(round + 3, xa);
         }
-        fetch_round(i + kRoundStages);
       }
-      STAMP();
-      float sv_cur[kStageGroups];
-      // nibbles -> bytes: 32 rows of this thread's column become one row of two 16-byte k-halves of A
-#pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) {
-        const uint4 wv = wq[0][u];
-        sv_cur[u] = sq[0][u];
-        uint4 lo, hi;
-        lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
-        lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
-        lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
-        lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
-        unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + u) * (kCols * 32) + (size_t)tid * 16;
-        *reinterpret_cast<uint4*>(a) = lo;
-        *reinterpret_cast<uint4*>(a + kCols * 16) = hi;
-      }
-      // shift the register queue and request the stage kAheadStages further on
-#pragma unroll
-      for (int a = 0; a + 1 < kAheadStages; ++a) {
-#pragma unroll
-        for (int u = 0; u < kStageGroups; ++u) { wq[a][u] = wq[a + 1][u]; sq[a][u] = sq[a + 1][u]; }
-      }
-      load_stage(i + kAheadStages, wq[kAheadStages - 1], sq[kAheadStages - 1]);
-      STAMP();
-      // this warp's part of the A operand (and of the digits) is in place and its reads of the raw slot are done
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&a_ready[i & 1]);
-      STAMP();
-      if (i > 0) ok = drain(i - 1, sv_prev);
-      STAMP();
-#pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) sv_prev[u] = sv_cur[u];
     }
-    if (ok && nst > 0) ok = drain(nst - 1, sv_prev);
     if (!ok) s_abort = 1;
   }
   tc_fence_before_sync();
@@ -362,9 +401,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int4_kernel(const Params p) 
   }
   gemv_epilogue<MT, kThreads>(p.epi, acc, rows, m0, p.m, j, active, false, 1.0f, p.out, s_red, s_arg, &s_flag, pre ? resid_pre : nullptr);
   if (tid == 0) trace_max(p.pro.trace, 2);
-  STAMP();
-  if (prof) prof[511] = pn;
-#undef STAMP
 }
 
 template <int MT, int AHEAD>
@@ -422,7 +458,7 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   const uint32_t col_tiles = (w->n + kCols - 1) / kCols;
   // Split k over a cluster of up to 8 CTAs.  A launch is a link in a chain of
   // dependent kernels, so what counts is its latency: waves x (fixed cost + stages per CTA x time per stage).
-  const uint32_t slots = 4u * (uint32_t)c->sm_count;
+  const uint32_t slots = 2u * (uint32_t)c->sm_count;
   uint32_t splits = 1;
   double best = 1e30;
   for (uint32_t s2 = 1; s2 <= 8; s2 *= 2) {  // 16-CTA clusters were tried: fewer clusters fit at once and the launch got slower
@@ -440,10 +476,14 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_cta = cpc; p.splits = splits;
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
   p.pro.trace = ruai_trace_slot(c);
-  p.prof = (long long*)c->prof;
+  if ((c->force_splits & 255u) && (c->force_splits & 255u) <= 8) {
+    p.splits = splits = c->force_splits & 255u;
+    cpc = (w->chunks + splits - 1) / splits;
+    p.chunks_per_cta = cpc = (cpc + kStageGroups - 1) / kStageGroups * kStageGroups;
+  }
   const dim3 grid(col_tiles, splits, row_tiles);
   // few CTAs per SM: spend the free registers on a deeper weight queue
-  const bool deep = col_tiles * row_tiles * splits <= 2u * (uint32_t)c->sm_count;
+  const bool deep = !(c->force_splits & 256u);
   cudaError_t e = mt == 1 ? (deep ? launch_one<1, 4>(c, p, grid) : launch_one<1, 2>(c, p, grid))
                 : mt == 2 ? (deep ? launch_one<2, 4>(c, p, grid) : launch_one<2, 2>(c, p, grid))
                 : mt == 4 ? launch_one<4, 2>(c, p, grid)

@@ -153,20 +153,23 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
     // ===== MMA issuer =====
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8(kN, true);
+      const uint64_t ad0 = umma_desc_kmajor(smem_u32(ring), kCols * 16, 128);
+      const uint64_t bd0 = umma_desc_kmajor(smem_u32(bop), kN / 8 * 128, 128);
       bool ok = mbar_wait(&b_ready, 0);
       STAMP();
-      for (uint32_t i = 0; i < nst && ok; ++i) {
-        if (s_abort || !mbar_wait(&full[i % kStages], (i / kStages) & 1u)) { ok = false; break; }
+      uint32_t left = c_end - c_begin, slot = 0, par = 0;
+      uint64_t bd = bd0;
+      for (uint32_t i = 0; i < nst && ok; ++i, left -= kStageChunks) {
+        if (!mbar_wait(&full[slot], par)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t c0 = i * kStageChunks;  // chunk index within the slice
-        const uint32_t nch = min((uint32_t)kStageChunks, c_end - c_begin - c0);
-        for (uint32_t u = 0; u < nch; u += 2) {
-          const uint64_t ad = umma_desc_kmajor(smem_u32(ring + (size_t)((i % kStages) * kStageChunks + u) * kCols), kCols * 16, 128);
-          const uint64_t bd = umma_desc_kmajor(smem_u32(bop + (size_t)((c0 + u) / 2) * (kN * 32)), kN / 8 * 128, 128);
-          umma_i8(tmem_base, ad, bd, idesc, (i | u) != 0u ? 1u : 0u);
-        }
-        umma_commit(&empty[i % kStages]);
+        const uint64_t ad = umma_desc_advance(ad0, slot * (kStageChunks * kCols * 16));
+        // one MMA per two chunk rows (K = 32); an odd last chunk is paired with digits that are zero
+        umma_i8(tmem_base, ad, bd, idesc, i != 0u ? 1u : 0u);
+        if (left > 2) umma_i8(tmem_base, umma_desc_advance(ad, 2 * kCols * 16), umma_desc_advance(bd, kN * 32), idesc, 1u);
+        bd = umma_desc_advance(bd, 2 * kN * 32);
+        umma_commit(&empty[slot]);
         STAMP();
+        if (++slot == (uint32_t)kStages) { slot = 0; par ^= 1u; }
       }
       if (ok) umma_commit(&all_done);
       else s_abort = 1;

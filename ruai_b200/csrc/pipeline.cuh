@@ -102,6 +102,12 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
 }
+// The same descriptor with the operand `byte_off` bytes (a multiple of 16) further on: only the address field changes, so
+// an issuing loop advances a descriptor with one 32-bit add (the sum must stay inside the 256 KB shared window, as it does
+// for operands of one CTA).
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t byte_off) {
+  return desc + (uint64_t)(byte_off >> 4);
+}
 // Instruction descriptor of kind::i8: D = s32, A unsigned or signed 8-bit, B signed 8-bit, both K-major, M = 128.
 __host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t n, bool a_signed) {
   return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
