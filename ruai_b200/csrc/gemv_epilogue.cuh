@@ -90,14 +90,21 @@ __device__ __forceinline__ void gemv_epilogue(const GemvEpilogue& e, float (&acc
     __syncthreads();
     if (*s_flag) {
       __threadfence();
-      if (tid < (int)m) {
-        const volatile int* sl = (const volatile int*)e.argmax_slots;
+      // one warp per row: the lanes share the tiles, then the best of the 32 by shuffles
+      const volatile int* sl = (const volatile int*)e.argmax_slots;
+      for (uint32_t row = warp; row < m; row += COLS / 32) {
         int bv = INT32_MIN, bj = -1;
-        for (uint32_t t = 0; t < gridDim.x; ++t) {
-          const int v = sl[2 * ((size_t)t * m + tid)], jj = sl[2 * ((size_t)t * m + tid) + 1];
+        for (uint32_t t = lane; t < gridDim.x; t += 32) {
+          const int v = sl[2 * ((size_t)t * m + row)], jj = sl[2 * ((size_t)t * m + row) + 1];
           if (v > bv || (v == bv && jj > bj)) { bv = v; bj = jj; }
         }
-        e.argmax_out[tid] = bj;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          const int ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+          const int oj = __shfl_xor_sync(0xFFFFFFFFu, bj, off);
+          if (ov > bv || (ov == bv && oj > bj)) { bv = ov; bj = oj; }
+        }
+        if (lane == 0) e.argmax_out[row] = bj;
       }
       if (tid == 0) {
         *e.argmax_counter = 0;

@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
       for (int u = 0; u < kStageGroups; ++u) {
         const uint32_t c = c_begin + i * kStageGroups + u;
         // beyond the slice or the matrix: stored value 8 is weight 0
-        wv[u] = (in_col && c < c_end) ? __ldcs(&p.w[(size_t)c * p.n + je]) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+        wv[u] = (in_col && c < c_end) ? ldg_stream_u4(&p.w[(size_t)c * p.n + je]) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
       }
     };
 #pragma unroll
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
 #pragma unroll
       for (int u = 0; u < kStageGroups; ++u) {
         const uint32_t c = c_begin + i * kStageGroups + u;
-        sv[u] = (active && c < c_end) ? __ldcs(&p.scale[(size_t)c * p.n + j]) : 0.0f;
+        sv[u] = (active && c < c_end) ? ldg_stream_f32(&p.scale[(size_t)c * p.n + j]) : 0.0f;
       }
     };
 #pragma unroll
@@ -245,10 +245,23 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
 #pragma unroll
     for (int r = 0; r < MT; ++r) resid_pre[r] = (pre && r < (int)rows) ? p.epi.resid[(size_t)(m0 + r) * p.epi.out_ld + j] : 0.0f;
     // activations of one round (16 groups = 512 values per row): 4 consecutive values per thread
-    auto fetch_round = [&](uint32_t round, float4 (&dst)[MT]) {
+    // 16-byte loads when the layout allows; the RMSNorm weights of the same columns ride along and multiply at conversion
+    const bool vec = p.x_dtype == RUAI_F32 && (p.x_ld & 3u) == 0 && (p.k & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 &&
+                     (!normed || (reinterpret_cast<uintptr_t>(p.pro.norm_w) & 15u) == 0);
+    auto fetch_round = [&](uint32_t round, float4 (&dst)[MT], float4& nw) {
       const uint32_t g = c_begin + round * kRoundGroups + tid / 8;
       const uint32_t kidx = (c_begin + round * kRoundGroups) * 32 + 4 * tid;
       const bool in = round < nrounds && g < c_end;
+      nw = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (vec) {
+        const bool ld = in && kidx < p.k;
+        if (ld && normed) nw = ldg_f4(reinterpret_cast<const float4*>(p.pro.norm_w + kidx));
+#pragma unroll
+        for (int r = 0; r < MT; ++r)
+          dst[r] = (ld && r < (int)rows) ? ldg_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)(m0 + r) * p.x_ld + kidx))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+      }
 #pragma unroll
       for (int r = 0; r < MT; ++r) {
         float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -265,12 +278,12 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
       }
     };
     // this warp's 4 groups of a round (8 lanes per group): block fixed point, three int8 digits into the B operand
-    auto convert = [&](uint32_t round, const float4 (&src)[MT]) {
+    auto convert = [&](uint32_t round, const float4 (&src)[MT], const float4& nw) {
       const uint32_t rb = round & 1u;
       const uint32_t gi = warp * 4 + (lane >> 3);
 #pragma unroll
       for (int r = 0; r < MT; ++r) {
-        const float4 xv = src[r];
+        const float4 xv = make_float4(src[r].x * nw.x, src[r].y * nw.y, src[r].z * nw.z, src[r].w * nw.w);
         float gmax = fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w)));
         gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 1));
         gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 2));
@@ -314,12 +327,12 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
       __syncwarp();
       if (lane == 0) mbar_arrive(&b_ready[rb]);
     };
-    float4 xa[MT], xb[MT];
-    fetch_round(0, xa);
-    fetch_round(1, xb);
-    convert(0, xa);
-    if (nrounds > 1) convert(1, xb);
-    fetch_round(2, xa);
+    float4 xa[MT], xb[MT], na, nb;
+    fetch_round(0, xa, na);
+    fetch_round(1, xb, nb);
+    convert(0, xa, na);
+    if (nrounds > 1) convert(1, xb, nb);
+    fetch_round(2, xa, na);
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the rounds' scales and sums are visible to the four warps
 
     bool ok = true;
@@ -368,8 +381,8 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
         // the round after next takes its place
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ok) {
-          convert(round + 2, xa);
-          fetch_round(round + 3, xa);
+          convert(round + 2, xa, na);
+          fetch_round(round + 3, xa, na);
         }
       }
     }
