@@ -164,12 +164,11 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 // With p.fuse (single new token per sequence) the kernel also does apply_rope
 // (functional.rs:197-204) on q and on the new key and appends the new key / value to the
 // cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
-constexpr int kAttnOutPerThread = 8;  // (rep * hd) / (threads = 32 * blocks * rep) for hd up to 256
 
 template <int REP>
 __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const AttnParams p) {
   constexpr int kThreads = kAttnChunkKeys * REP, kBlocks = kAttnChunkKeys / 32;
-  extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs | stats | merge
+  extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs | stats | parts | merge
   __shared__ __align__(8) uint64_t kv_bar;
   __shared__ unsigned s_last;
   const uint32_t hd = p.hd, half = hd / 2;
@@ -181,13 +180,10 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
   float* probs = vnew + hd;                       // [kBlocks][REP][32]
   float* bmax = probs + kBlocks * REP * 32;       // [kBlocks + 1][REP]: block maxima; the last row is the new key's score
   float* bsum = bmax + (kBlocks + 1) * REP;       // [kBlocks][REP]
-  float* mg = bsum + kBlocks * REP;               // split merge: [64][REP] weights, [64][REP] sums, [REP]
+  float* part = bsum + kBlocks * REP;             // [REP parts][REP heads][64 keys] partial scores
+  float* mg = part + REP * REP * kAttnChunkKeys;  // split merge: [64][REP] weights, [64][REP] sums, [REP]
   const uint32_t bk = blockIdx.x, b = bk / p.KV, kvh = bk % p.KV, t = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  long long* prof = (p.prof && blockIdx.x == 0 && blockIdx.z == 3 && threadIdx.x == 0) ? p.prof + 2048 : nullptr;
-  int pn = 0;
-#define ASTAMP() do { if (prof && pn < 60) prof[pn++] = clock64(); } while (0)
-  ASTAMP();
   float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
   float* vbase = p.vcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
   if (tid == 0) {
@@ -218,10 +214,8 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
     plan();
     if (tid == 0 && k1 > k0) fetch_chunk(k0);
   }
-  ASTAMP();
   if (tid == 0) trace_min(p.trace, 0);
   grid_dependency_wait();
-  ASTAMP();
   if (tid == 0) trace_min(p.trace, 1);
   grid_launch_dependents();
   if (!p.fuse) {
@@ -261,13 +255,20 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
     }
   }
   __syncthreads();
-  ASTAMP();
-  // this thread's outputs: idx = tid + i * kThreads over [REP][hd]
-  const uint32_t total = REP * hd;
-  float run_m[kAttnOutPerThread], run_l[kAttnOutPerThread], run_o[kAttnOutPerThread];
-#pragma unroll
-  for (int i = 0; i < kAttnOutPerThread; ++i) { run_m[i] = -INFINITY; run_l[i] = 0.0f; run_o[i] = 0.0f; }
-  const int wblk = warp / REP, wr = warp % REP;  // this warp's (key block, head) in the score phase
+  // ---- thread roles ----
+  // partial scores: warp (key block, part of the head dimension), lane = key, all REP heads at once
+  // softmax stats : warp (key block, head), lane = key
+  // values        : thread (key group, head, 4 consecutive elements)
+  const uint32_t nq4 = hd / 4;
+  const int wblk = warp / REP, wr = warp % REP;
+  const uint32_t cper = (nq4 + REP - 1) / REP;
+  const uint32_t c_lo = min(nq4, (uint32_t)wr * cper), c_hi = min(nq4, c_lo + cper), ncols = c_hi - c_lo;
+  const uint32_t vthreads = REP * nq4;                 // threads that cover one full set of outputs
+  const uint32_t G = max(1u, (uint32_t)kThreads / vthreads);  // key groups in the value phase
+  const uint32_t vg = tid / vthreads, vrem = tid % vthreads, vr = vrem / nq4, vc = vrem % nq4;
+  const bool vact = (uint32_t)tid < G * vthreads;
+  float run_m = -INFINITY, run_l = 0.0f;
+  float4 run_o = make_float4(0.f, 0.f, 0.f, 0.f);
   uint32_t phase = 0;
   bool ok = true;
   for (uint32_t c0 = k0; c0 < k1 || (c0 == k0 && owns_new); c0 += kAttnChunkKeys) {
@@ -280,37 +281,50 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
       if (!pipe::mbar_wait(&kv_bar, phase & 1u)) { ok = false; break; }
       ++phase;
     }
-    ASTAMP();
     const uint32_t c1 = have_keys ? min(k1, c0 + kAttnChunkKeys) : c0;
     const uint32_t nkeys = c1 - c0;
-    // ---- scores ----
+    // ---- partial scores: this lane's key against this warp's columns of every head ----
+    {
+      const uint32_t key = wblk * 32 + lane;
+      const float4* krow = reinterpret_cast<const float4*>(ks + (size_t)(key < nkeys ? key : 0) * hd);
+      const float4* q4 = reinterpret_cast<const float4*>(qs);
+      float acc[REP][2];
+#pragma unroll
+      for (int r = 0; r < REP; ++r) { acc[r][0] = 0.0f; acc[r][1] = 0.0f; }
+      auto dot4 = [](const float4& a, const float4& b2, float s) {
+        s = fmaf(a.x, b2.x, s); s = fmaf(a.y, b2.y, s); s = fmaf(a.z, b2.z, s); return fmaf(a.w, b2.w, s);
+      };
+      if (ncols > 0) {
+        // each lane starts at its own column: the eight lanes of a quarter warp read eight different 16-byte columns
+        uint32_t cc = c_lo + lane % ncols;
+        uint32_t it = 0;
+        for (; it + 2 <= ncols; it += 2) {
+          const uint32_t ca = cc, cb = ca + 1 == c_hi ? c_lo : ca + 1;
+          const float4 ka = krow[ca], kb = krow[cb];
+#pragma unroll
+          for (int r = 0; r < REP; ++r) {
+            acc[r][0] = dot4(q4[r * nq4 + ca], ka, acc[r][0]);
+            acc[r][1] = dot4(q4[r * nq4 + cb], kb, acc[r][1]);
+          }
+          cc = cb + 1 == c_hi ? c_lo : cb + 1;
+        }
+        if (it < ncols) {
+          const float4 ka = krow[cc];
+#pragma unroll
+          for (int r = 0; r < REP; ++r) acc[r][0] = dot4(q4[r * nq4 + cc], ka, acc[r][0]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r) part[(wr * REP + r) * kAttnChunkKeys + key] = acc[r][0] + acc[r][1];
+    }
+    __syncthreads();
+    // ---- scores of (key block, head): sum of the parts, block maximum and sum by shuffles ----
     {
       const uint32_t key = wblk * 32 + lane;
       const bool valid = key < nkeys;
       float sc = 0.0f;
-      const uint32_t nq4 = hd / 4;
-      const float4* krow = reinterpret_cast<const float4*>(ks + (size_t)(valid ? key : 0) * hd);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + wr * hd);
-      // four independent 16-byte columns per step so that the shared-memory reads overlap
-      uint32_t cc = lane % nq4;
-      auto nxt = [&](uint32_t c) { return c + 1 >= nq4 ? c + 1 - nq4 : c + 1; };
-      auto dot4 = [](const float4& a, const float4& b2, float acc) {
-        acc = fmaf(a.x, b2.x, acc); acc = fmaf(a.y, b2.y, acc); acc = fmaf(a.z, b2.z, acc); return fmaf(a.w, b2.w, acc);
-      };
-      float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-      uint32_t it = 0;
-      for (; it + 4 <= nq4; it += 4) {
-        const uint32_t c0i = cc, c1i = nxt(c0i), c2i = nxt(c1i), c3i = nxt(c2i);
-        const float4 ka = krow[c0i], kb = krow[c1i], kc = krow[c2i], kd = krow[c3i];
-        const float4 qa = q4[c0i], qb = q4[c1i], qc = q4[c2i], qd = q4[c3i];
-        s0 = dot4(qa, ka, s0); s1 = dot4(qb, kb, s1); s2 = dot4(qc, kc, s2); s3 = dot4(qd, kd, s3);
-        cc = nxt(c3i);
-      }
-      for (; it < nq4; ++it) {
-        s0 = dot4(q4[cc], krow[cc], s0);
-        cc = nxt(cc);
-      }
-      sc = (s0 + s1) + (s2 + s3);
+#pragma unroll
+      for (int pt = 0; pt < REP; ++pt) sc += part[(pt * REP + wr) * kAttnChunkKeys + key];
       const float sv = valid ? sc * p.scale : -INFINITY;
       float bm = sv;
 #pragma unroll
@@ -330,75 +344,83 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
         if (lane == 0) bmax[kBlocks * REP + wr] = a * p.scale;
       }
     }
-    ASTAMP();
     __syncthreads();
-    ASTAMP();
-    // ---- weighted values ----
-    const bool with_new = owns_new && c0 == k0;
+    // ---- weighted values: this thread's four elements over its group's keys ----
+    if (vact) {
+      const bool with_new = owns_new && c0 == k0;
+      float M = run_m;
 #pragma unroll
-    for (int i = 0; i < kAttnOutPerThread; ++i) {
-      const uint32_t idx = tid + i * kThreads;
-      if (idx < total) {
-        const uint32_t r = idx / hd, e = idx % hd;
-        float M = run_m[i];
+      for (int bl = 0; bl < kBlocks; ++bl) M = fmaxf(M, bmax[bl * REP + vr]);
+      const float snew = with_new ? bmax[kBlocks * REP + vr] : -INFINITY;
+      M = fmaxf(M, snew);
+      const float cr = expf(run_m - M);  // 0 on the first chunk
+      float L = run_l * cr;
+      float4 O = make_float4(run_o.x * cr, run_o.y * cr, run_o.z * cr, run_o.w * cr);
 #pragma unroll
-        for (int bl = 0; bl < kBlocks; ++bl) M = fmaxf(M, bmax[bl * REP + r]);
-        const float snew = with_new ? bmax[kBlocks * REP + r] : -INFINITY;
-        M = fmaxf(M, snew);
-        const float cr = expf(run_m[i] - M);  // 0 on the first chunk
-        float L = run_l[i] * cr, O = run_o[i] * cr;
-#pragma unroll
-        for (int bl = 0; bl < kBlocks; ++bl) {
-          const float bm = bmax[bl * REP + r];
-          if (bm != -INFINITY) {
-            const float cb = expf(bm - M);
-            L = fmaf(bsum[bl * REP + r], cb, L);
-            const uint32_t nb = min(32u, nkeys - min(nkeys, (uint32_t)bl * 32u));
-            const float* pp = probs + (bl * REP + r) * 32;
-            const float* vp = vs + (size_t)bl * 32 * hd + e;
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-            uint32_t kk = 0;
-            for (; kk + 8 <= nb; kk += 8) {  // eight keys per step: sixteen independent shared-memory reads in flight
-              float pv[8], vv[8];
-#pragma unroll
-              for (int u = 0; u < 8; ++u) { pv[u] = pp[kk + u]; vv[u] = vp[(size_t)(kk + u) * hd]; }
-              a0 = fmaf(pv[0], vv[0], a0); a1 = fmaf(pv[1], vv[1], a1); a2 = fmaf(pv[2], vv[2], a2); a3 = fmaf(pv[3], vv[3], a3);
-              a0 = fmaf(pv[4], vv[4], a0); a1 = fmaf(pv[5], vv[5], a1); a2 = fmaf(pv[6], vv[6], a2); a3 = fmaf(pv[7], vv[7], a3);
-            }
-            for (; kk < nb; ++kk) a0 = fmaf(pp[kk], vp[(size_t)kk * hd], a0);
-            a0 += a2; a1 += a3;
-            O = fmaf(a0 + a1, cb, O);
+      for (int bl = 0; bl < kBlocks; ++bl) {
+        const float bm = bmax[bl * REP + vr];
+        if (bm != -INFINITY) {
+          const float cb = expf(bm - M);
+          L = fmaf(bsum[bl * REP + vr], cb, L);
+          const uint32_t nb = min(32u, nkeys - min(nkeys, (uint32_t)bl * 32u));
+          const float* pp = probs + (bl * REP + vr) * 32;
+          const float4* vp = reinterpret_cast<const float4*>(vs + (size_t)bl * 32 * hd) + vc;
+          float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+          uint32_t kk = vg;
+          for (; kk + G < nb; kk += 2 * G) {  // two keys per step: independent reads and sums
+            const float p0 = pp[kk], p1 = pp[kk + G];
+            const float4 v0 = vp[(size_t)kk * nq4], v1 = vp[(size_t)(kk + G) * nq4];
+            a0.x = fmaf(p0, v0.x, a0.x); a0.y = fmaf(p0, v0.y, a0.y); a0.z = fmaf(p0, v0.z, a0.z); a0.w = fmaf(p0, v0.w, a0.w);
+            a1.x = fmaf(p1, v1.x, a1.x); a1.y = fmaf(p1, v1.y, a1.y); a1.z = fmaf(p1, v1.z, a1.z); a1.w = fmaf(p1, v1.w, a1.w);
           }
+          if (kk < nb) {
+            const float p0 = pp[kk];
+            const float4 v0 = vp[(size_t)kk * nq4];
+            a0.x = fmaf(p0, v0.x, a0.x); a0.y = fmaf(p0, v0.y, a0.y); a0.z = fmaf(p0, v0.z, a0.z); a0.w = fmaf(p0, v0.w, a0.w);
+          }
+          O.x = fmaf(a0.x + a1.x, cb, O.x); O.y = fmaf(a0.y + a1.y, cb, O.y); O.z = fmaf(a0.z + a1.z, cb, O.z); O.w = fmaf(a0.w + a1.w, cb, O.w);
         }
-        if (with_new) {
-          const float cn = expf(snew - M);
-          L += cn;
-          O = fmaf(cn, vnew[e], O);
-        }
-        run_m[i] = M; run_l[i] = L; run_o[i] = O;
       }
+      if (with_new) {
+        const float cn = expf(snew - M);
+        L += cn;
+        if (vg == 0) {
+          const float4 vn = reinterpret_cast<const float4*>(vnew)[vc];
+          O.x = fmaf(cn, vn.x, O.x); O.y = fmaf(cn, vn.y, O.y); O.z = fmaf(cn, vn.z, O.z); O.w = fmaf(cn, vn.w, O.w);
+        }
+      }
+      run_m = M; run_l = L; run_o = O;
     }
   }
   if (!ok && p.status && tid == 0) atomicExch(p.status, 3);
-  ASTAMP();
-  // ---- this CTA's result: straight out, or into the split scratch ----
-  const uint32_t stride = hd + 2;
-  float* sc = p.scratch + ((((size_t)bk * p.T + t) * gridDim.z + split) * REP) * stride;
-#pragma unroll
-  for (int i = 0; i < kAttnOutPerThread; ++i) {
-    const uint32_t idx = tid + i * kThreads;
-    if (idx < total) {
-      const uint32_t r = idx / hd, e = idx % hd;
-      if (gridDim.z == 1) {
-        p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = run_o[i] / run_l[i];
-      } else {
-        sc[(size_t)r * stride + e] = run_o[i];
-        if (e == 0) { sc[(size_t)r * stride + hd] = run_m[i]; sc[(size_t)r * stride + hd + 1] = run_l[i]; }
+  // ---- the key groups' sums come together in group 0 (through the K staging area, no longer needed) ----
+  if (G > 1) {
+    __syncthreads();
+    float4* comb = reinterpret_cast<float4*>(ks);
+    if (vact && vg > 0) comb[(vg - 1) * vthreads + vrem] = run_o;
+    __syncthreads();
+    if (vact && vg == 0) {
+      for (uint32_t g2 = 1; g2 < G; ++g2) {
+        const float4 o2 = comb[(g2 - 1) * vthreads + vrem];
+        run_o.x += o2.x; run_o.y += o2.y; run_o.z += o2.z; run_o.w += o2.w;
       }
     }
   }
+  // ---- this CTA's result: straight out, or into the split scratch ----
+  const uint32_t stride = hd + 4;  // a row of sums, then its maximum and total; 16-byte aligned rows
+  const bool writer = vact && vg == 0;
+  float* sc = p.scratch + ((((size_t)bk * p.T + t) * gridDim.z + split) * REP) * stride;
+  if (writer) {
+    if (gridDim.z == 1) {
+      float* o = p.out + (size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + vr) * hd + 4 * vc;
+      const float inv = 1.0f / run_l;
+      o[0] = run_o.x * inv; o[1] = run_o.y * inv; o[2] = run_o.z * inv; o[3] = run_o.w * inv;
+    } else {
+      *reinterpret_cast<float4*>(sc + (size_t)vr * stride + 4 * vc) = run_o;
+      if (vc == 0) { sc[(size_t)vr * stride + hd] = run_m; sc[(size_t)vr * stride + hd + 1] = run_l; }
+    }
+  }
   if (gridDim.z == 1) { if (tid == 0) trace_max(p.trace, 2); return; }
-  ASTAMP();
   // ---- merge the key splits: last CTA to arrive ----
   __threadfence();
   __syncthreads();
@@ -408,17 +430,20 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
     s_last = a == gridDim.z - 1 ? 1u : 0u;
   }
   __syncthreads();
-  ASTAMP();
-  if (prof) prof[63] = pn;
   if (!s_last) { if (tid == 0) trace_max(p.trace, 2); return; }
   __threadfence();
   if (tid == 0) *counter = 0;
   const float* base = p.scratch + (((size_t)bk * p.T + t) * gridDim.z) * REP * stride;
-  // weights of the splits first (one parallel round of loads), then the weighted sums with
-  // eight independent loads in flight per thread
   const uint32_t ns = gridDim.z;  // <= 64
   float* wgt = mg;                // [ns][REP] max, then coefficient
   float* lsum = mg + 64 * REP;    // [ns][REP]
+  // the splits' sums for this thread's elements are requested first; the weights are worked out while they travel
+  float4 part_o[8];
+  if (writer) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      part_o[u] = (uint32_t)u < ns ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)u * REP + vr) * stride + 4 * vc)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   for (uint32_t i = tid; i < ns * REP; i += kThreads) {
     const float* src = base + (size_t)i * stride;  // i = s * REP + r
     wgt[i] = __ldcg(src + hd);
@@ -440,21 +465,27 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
     inv[r] = 1.0f / L;
   }
   __syncthreads();
-  for (uint32_t idx = tid; idx < total; idx += kThreads) {
-    const uint32_t r = idx / hd, e = idx % hd;
-    float O = 0.0f;
+  if (writer) {
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t s0 = 0; s0 < ns; s0 += 8) {
-      float v[8];
+      if (s0 > 0) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = s0 + u < ns ? __ldcg(base + ((size_t)(s0 + u) * REP + r) * stride + e) : 0.0f;
+        for (int u = 0; u < 8; ++u)
+          part_o[u] = s0 + u < ns ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * REP + vr) * stride + 4 * vc)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (s0 + u < ns) O = fmaf(v[u], wgt[(s0 + u) * REP + r], O);
+      for (int u = 0; u < 8; ++u) {
+        if (s0 + u < ns) {
+          const float w = wgt[(s0 + u) * REP + vr];
+          O.x = fmaf(part_o[u].x, w, O.x); O.y = fmaf(part_o[u].y, w, O.y); O.z = fmaf(part_o[u].z, w, O.z); O.w = fmaf(part_o[u].w, w, O.w);
+        }
+      }
     }
-    p.out[(size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + r) * hd + e] = O * inv[r];
+    float* o = p.out + (size_t)(b * p.T + t) * p.out_ld + ((size_t)kvh * REP + vr) * hd + 4 * vc;
+    const float iv = inv[vr];
+    o[0] = O.x * iv; o[1] = O.y * iv; o[2] = O.z * iv; o[3] = O.w * iv;
   }
   if (tid == 0) trace_max(p.trace, 2);
-#undef ASTAMP
 }
 
 // generation::argmax (generation.rs:6-8): the LAST index among equal maxima, in
@@ -567,7 +598,7 @@ int ruai_attention(ruai_ctx* c, const AttnParams& p_in, uint32_t B, uint32_t rep
   if (p.hd % 4 || p.hd > 256) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4 and at most 256", p.hd);
   constexpr size_t kb = kAttnChunkKeys / 32;
   const size_t floats = 2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + kb * rep * 32 + (kb + 1) * rep + kb * rep +
-                        128 * (size_t)rep + rep;
+                        (size_t)rep * rep * kAttnChunkKeys + 128 * (size_t)rep + rep;
   const size_t smem = floats * sizeof(float);
   const dim3 grid(B * p.KV, p.T, splits);
   cudaError_t e;

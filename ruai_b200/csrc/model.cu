@@ -450,7 +450,7 @@ int ensure_activations(ruai_model* m, uint32_t rows, uint32_t out_rows, uint32_t
   }
   const uint32_t splits = attn_splits(m, B, T);
   const uint32_t rep = m->Hl / m->KVl;
-  const size_t need = (size_t)B * m->KVl * T * splits * rep * (m->hd + 2) * sizeof(float);
+  const size_t need = (size_t)B * m->KVl * T * splits * rep * (m->hd + 4) * sizeof(float);
   const size_t cnt = (size_t)B * m->KVl * T * sizeof(unsigned);
   if (need > m->attn_scratch.bytes || cnt > m->attn_counters.bytes) {
     RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
