@@ -165,9 +165,11 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 // (functional.rs:197-204) on q and on the new key and appends the new key / value to the
 // cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
 
+constexpr int kAttnSub = 2;  // warps per (32 keys, query head): more warps than the work needs, to hide each other's latencies
+
 template <int REP>
-__global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const AttnParams p) {
-  constexpr int kThreads = kAttnChunkKeys * REP, kBlocks = kAttnChunkKeys / 32;
+__global__ void __launch_bounds__(kAttnChunkKeys * REP * kAttnSub) attention_kernel(const AttnParams p) {
+  constexpr int kThreads = kAttnChunkKeys * REP * kAttnSub, kBlocks = kAttnChunkKeys / 32, kParts = REP * kAttnSub;
   extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs | stats | parts | merge
   __shared__ __align__(8) uint64_t kv_bar;
   __shared__ unsigned s_last;
@@ -180,8 +182,8 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
   float* probs = vnew + hd;                       // [kBlocks][REP][32]
   float* bmax = probs + kBlocks * REP * 32;       // [kBlocks + 1][REP]: block maxima; the last row is the new key's score
   float* bsum = bmax + (kBlocks + 1) * REP;       // [kBlocks][REP]
-  float* part = bsum + kBlocks * REP;             // [REP parts][REP heads][64 keys] partial scores
-  float* mg = part + REP * REP * kAttnChunkKeys;  // split merge: [64][REP] weights, [64][REP] sums, [REP]
+  float* part = bsum + kBlocks * REP;             // [kParts][REP heads][64 keys] partial scores
+  float* mg = part + kParts * REP * kAttnChunkKeys;  // split merge: [64][REP] weights, [64][REP] sums, [REP]
   const uint32_t bk = blockIdx.x, b = bk / p.KV, kvh = bk % p.KV, t = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* kbase = p.kcache + ((size_t)b * p.KV + kvh) * p.cap * hd;
@@ -260,9 +262,9 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
   // softmax stats : warp (key block, head), lane = key
   // values        : thread (key group, head, 4 consecutive elements)
   const uint32_t nq4 = hd / 4;
-  const int wblk = warp / REP, wr = warp % REP;
-  const uint32_t cper = (nq4 + REP - 1) / REP;
-  const uint32_t c_lo = min(nq4, (uint32_t)wr * cper), c_hi = min(nq4, c_lo + cper), ncols = c_hi - c_lo;
+  const int wblk = warp / kParts, wpart = warp % kParts, wr = wpart;  // wr: the head, for the warps with wpart < REP
+  const uint32_t cper = (nq4 + kParts - 1) / kParts;
+  const uint32_t c_lo = min(nq4, (uint32_t)wpart * cper), c_hi = min(nq4, c_lo + cper), ncols = c_hi - c_lo;
   const uint32_t vthreads = REP * nq4;                 // threads that cover one full set of outputs
   const uint32_t G = max(1u, (uint32_t)kThreads / vthreads);  // key groups in the value phase
   const uint32_t vg = tid / vthreads, vrem = tid % vthreads, vr = vrem / nq4, vc = vrem % nq4;
@@ -315,16 +317,16 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
         }
       }
 #pragma unroll
-      for (int r = 0; r < REP; ++r) part[(wr * REP + r) * kAttnChunkKeys + key] = acc[r][0] + acc[r][1];
+      for (int r = 0; r < REP; ++r) part[(wpart * REP + r) * kAttnChunkKeys + key] = acc[r][0] + acc[r][1];
     }
     __syncthreads();
     // ---- scores of (key block, head): sum of the parts, block maximum and sum by shuffles ----
-    {
+    if (wpart < REP) {
       const uint32_t key = wblk * 32 + lane;
       const bool valid = key < nkeys;
       float sc = 0.0f;
 #pragma unroll
-      for (int pt = 0; pt < REP; ++pt) sc += part[(pt * REP + wr) * kAttnChunkKeys + key];
+      for (int pt = 0; pt < kParts; ++pt) sc += part[(pt * REP + wr) * kAttnChunkKeys + key];
       const float sv = valid ? sc * p.scale : -INFINITY;
       float bm = sv;
 #pragma unroll
@@ -451,18 +453,20 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP) attention_kernel(const A
   }
   __syncthreads();
   float* inv = lsum + 64 * REP;   // [REP] 1 / total
-  if (tid < REP) {
-    const uint32_t r = tid;
-    float M = -INFINITY;
-    for (uint32_t s2 = 0; s2 < ns; ++s2) M = fmaxf(M, wgt[s2 * REP + r]);
+  if (warp < REP) {  // one warp per head: the lanes share the splits (ns <= 64)
+    const uint32_t r = warp;
+    const float m0 = (uint32_t)lane < ns ? wgt[lane * REP + r] : -INFINITY;
+    const float m1 = (uint32_t)lane + 32 < ns ? wgt[(lane + 32) * REP + r] : -INFINITY;
+    float M = fmaxf(m0, m1);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, off));
+    const float c0 = m0 == -INFINITY ? 0.0f : expf(m0 - M), c1 = m1 == -INFINITY ? 0.0f : expf(m1 - M);
     float L = 0.0f;
-    for (uint32_t s2 = 0; s2 < ns; ++s2) {
-      const float ms = wgt[s2 * REP + r];
-      const float c = ms == -INFINITY ? 0.0f : expf(ms - M);
-      L += lsum[s2 * REP + r] * c;
-      wgt[s2 * REP + r] = c;
-    }
-    inv[r] = 1.0f / L;
+    if ((uint32_t)lane < ns) { L = lsum[lane * REP + r] * c0; wgt[lane * REP + r] = c0; }
+    if ((uint32_t)lane + 32 < ns) { L = fmaf(lsum[(lane + 32) * REP + r], c1, L); wgt[(lane + 32) * REP + r] = c1; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xFFFFFFFFu, L, off);
+    if (lane == 0) inv[r] = 1.0f / L;
   }
   __syncthreads();
   if (writer) {
@@ -555,7 +559,7 @@ cudaError_t launch_attn(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem
     if (e != cudaSuccess) return e;
     attr_done[c->ordinal & 63] = true;
   }
-  return ruai_launch(c, attention_kernel<REP>, grid, dim3(kAttnChunkKeys * REP), smem, true, p);
+  return ruai_launch(c, attention_kernel<REP>, grid, dim3(kAttnChunkKeys * REP * kAttnSub), smem, true, p);
 }
 
 }  // namespace
@@ -598,7 +602,7 @@ int ruai_attention(ruai_ctx* c, const AttnParams& p_in, uint32_t B, uint32_t rep
   if (p.hd % 4 || p.hd > 256) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4 and at most 256", p.hd);
   constexpr size_t kb = kAttnChunkKeys / 32;
   const size_t floats = 2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + kb * rep * 32 + (kb + 1) * rep + kb * rep +
-                        (size_t)rep * rep * kAttnChunkKeys + 128 * (size_t)rep + rep;
+                        (size_t)kAttnSub * rep * rep * kAttnChunkKeys + 128 * (size_t)rep + rep;
   const size_t smem = floats * sizeof(float);
   const dim3 grid(B * p.KV, p.T, splits);
   cudaError_t e;
