@@ -290,7 +290,13 @@ def main():
                 traffic = tr["dram_bytes_per_algorithmic_byte"] * lin_bytes / lin_launches
     except Exception:
         pass
-    roofline = {"bound": "hbm", "kernel": f"gemv_kernel<{bits}, rows<={B}> (fused dequant GEMV, every Linear of the model)",
+    if B > 16:
+        kname = "gemm_tc_kernel (tcgen05 kind::f16 dequant GEMM, every Linear of the model)"
+    elif bits == 4:
+        kname = f"gemv_tc_int4_kernel<rows<={min(B, 8)}> (tcgen05 kind::i8 fused dequant GEMV; the int8 head runs gemv_tc_int8_kernel)"
+    else:
+        kname = f"gemv_tc_int8_kernel<rows<={min(B, 8)}> (tcgen05 kind::i8 fused dequant GEMV, every Linear of the model)"
+    roofline = {"bound": "hbm", "kernel": kname,
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                 "traffic": traffic, "bytes_per_launch": lin_bytes / lin_launches, "us_per_launch": 1000.0 * lin_ms / lin_launches,
                 "launches_timed": lin_launches * iters, "per_gpu": True,

@@ -33,7 +33,6 @@ struct ruai_ctx {
   bool use_bulk = true; // bulk-copy staged GEMV (gemv_bulk.cu) where the weight allows it
   bool use_tc = true;   // tensor-core GEMV (gemv_tc.cu, gemv_tc8.cu) for chunk-layout weights and up to 16 rows
   unsigned force_splits = 0;  // debug: overrides the split-K choice of the tensor-core GEMVs (0 = automatic)
-  void* prof = nullptr;  // debug: device buffer for cycle stamps (set by ruai_debug_set_prof)
   unsigned long long* trace = nullptr;  // debug: per-launch [first entry, first past the dependency wait, last exit] in ns
   unsigned trace_slots = 0, trace_seq = 0;
   int* status = nullptr;  // device word: 0 ok, 3 = a bounded wait inside a kernel ran out

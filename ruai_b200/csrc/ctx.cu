@@ -165,12 +165,7 @@ RUAI_API int ruai_timer_stop_ms(ruai_ctx* c, float* ms) {
   return RUAI_OK;
 }
 
-// Debug hook (not declared in the public header): kernels that support it write cycle stamps here.
-RUAI_API int ruai_debug_set_prof(ruai_ctx* c, void* dev_buf) {
-  c->prof = dev_buf;
-  return RUAI_OK;
-}
-
+// Debug hooks (not declared in the public header).
 RUAI_API int ruai_debug_force_splits(ruai_ctx* c, unsigned splits) {
   c->force_splits = splits;
   return RUAI_OK;

@@ -598,7 +598,6 @@ int ruai_rope_kv(ruai_ctx* c, float* qkv, uint32_t qkv_ld, uint32_t k_off, uint3
 int ruai_attention(ruai_ctx* c, const AttnParams& p_in, uint32_t B, uint32_t rep, uint32_t splits) {
   AttnParams p = p_in;
   p.trace = ruai_trace_slot(c);
-  p.prof = (long long*)c->prof;
   if (p.hd % 4 || p.hd > 256) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4 and at most 256", p.hd);
   constexpr size_t kb = kAttnChunkKeys / 32;
   const size_t floats = 2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + kb * rep * 32 + (kb + 1) * rep + kb * rep +

@@ -23,7 +23,6 @@ struct AttnParams {
   unsigned* counters;   // [B*KV*T], zero between launches
   int* status;          // context status word (bounded waits)
   unsigned long long* trace;  // debug timeline slot
-  long long* prof;            // debug cycle stamps of one CTA
 };
 
 int ruai_embed(ruai_ctx* c, const int32_t* ids, const float* embed, const float* wpe, const int32_t* len, uint32_t rows, uint32_t T, uint32_t d,

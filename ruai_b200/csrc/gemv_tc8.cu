@@ -41,7 +41,6 @@ struct Params {
   uint32_t x_ld, m, k, n, chunks, chunks_per_cta, splits;
   void* out;
   int* status;
-  long long* prof;
   GemvEpilogue epi;
   GemvPrologue pro;
 };
@@ -78,10 +77,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   float* red = reinterpret_cast<float*>(smem + L::off_red(slice_k));
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  long long* prof = (p.prof && blockIdx.x == 7 && blockIdx.y == 0 && (tid == 0 || tid == 128)) ? p.prof + (tid ? 512 : 0) : nullptr;
-  int pn = 0;
-#define STAMP() do { if (prof && pn < 500) prof[pn++] = clock64(); } while (0)
-  STAMP();
   const uint32_t j0 = blockIdx.x * kCols;
   const uint32_t j = j0 + tid;
   const bool active = tid < kCols && j < p.n;
@@ -118,7 +113,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem;
-  STAMP();
   // weights do not depend on the predecessor kernel: fill the ring before waiting for it
   if (tid == kCols + 32) {
     for (uint32_t i = 0; i < nst && i < (uint32_t)kStages; ++i) issue(i);
@@ -132,7 +126,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   grid_dependency_wait();
   if (tid == 0) trace_min(p.pro.trace, 1);
   grid_launch_dependents();
-  STAMP();
   const bool normed = p.pro.norm_w != nullptr;
   if (normed && warp == kCols / 32 && lane < MT) {
     float ss = 0.0f;
@@ -156,7 +149,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
       const uint64_t ad0 = umma_desc_kmajor(smem_u32(ring), kCols * 16, 128);
       const uint64_t bd0 = umma_desc_kmajor(smem_u32(bop), kN / 8 * 128, 128);
       bool ok = mbar_wait(&b_ready, 0);
-      STAMP();
       uint32_t left = c_end - c_begin, slot = 0, par = 0;
       uint64_t bd = bd0;
       for (uint32_t i = 0; i < nst && ok; ++i, left -= kStageChunks) {
@@ -168,7 +160,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
         if (left > 2) umma_i8(tmem_base, umma_desc_advance(ad, 2 * kCols * 16), umma_desc_advance(bd, kN * 32), idesc, 1u);
         bd = umma_desc_advance(bd, 2 * kN * 32);
         umma_commit(&empty[slot]);
-        STAMP();
         if (++slot == (uint32_t)kStages) { slot = 0; par ^= 1u; }
       }
       if (ok) umma_commit(&all_done);
@@ -249,9 +240,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
         for (int i = 0; i < R; ++i) mx = max4(mx, v[r][i]);
         row_max(r, mx);
       }
-      STAMP();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      STAMP();
 #pragma unroll
       for (int r = 0; r < MT; ++r) {
         const float up = row_scale(r);
@@ -334,15 +323,12 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
           }
       }
     }
-    STAMP();
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(&b_ready);
-    STAMP();
     // ---- the sums, once every MMA has completed ----
     if (!mbar_wait(&all_done, 0)) s_abort = 1;
     else if (nst > 0) {
-      STAMP();
       tc_fence_after_sync();
       const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
 #pragma unroll
@@ -359,10 +345,8 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
       tc_fence_before_sync();
     }
   }
-  STAMP();
   tc_fence_before_sync();
   __syncthreads();
-  STAMP();
   if (s_abort && tid == 0) atomicExch(p.status, 3);
   if (warp == 0) tmem_dealloc(tmem_base, 32);
 
@@ -372,9 +356,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
 #pragma unroll
       for (int r = 0; r < MT; ++r) st_cluster_f32(red + ((size_t)split * MT + r) * kCols + tid, 0, acc[r]);
     }
-    STAMP();
     cluster_sync_all();
-    STAMP();
     if (split != 0) { if (tid == 0) trace_max(p.pro.trace, 2); return; }
     if (tid < kCols) {
       for (uint32_t s = 1; s < p.splits; ++s) {
@@ -389,9 +371,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   }
   const float col_scale = active ? p.scale[j] : 1.0f;
   gemv_epilogue<MT, kThreads>(p.epi, acc, rows, m0, p.m, j, active, true, col_scale, p.out, s_red, s_arg, &s_flag, pre ? resid_pre : nullptr);
-  STAMP();
-  if (prof) prof[511] = pn;
-#undef STAMP
   if (tid == 0) trace_max(p.pro.trace, 2);
 }
 
@@ -471,7 +450,6 @@ int ruai_gemv_tc8_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int 
   p.m = m; p.k = w->k; p.n = w->n; p.chunks = w->chunks; p.chunks_per_cta = cpc; p.splits = splits;
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
   p.pro.trace = ruai_trace_slot(c);
-  p.prof = (long long*)c->prof;
   const dim3 grid(col_tiles, splits, row_tiles);
   cudaError_t e = mt == 1 ? launch_one<1>(c, p, grid, slice_k) : mt == 2 ? launch_one<2>(c, p, grid, slice_k)
                 : mt == 4 ? launch_one<4>(c, p, grid, slice_k) : launch_one<8>(c, p, grid, slice_k);
