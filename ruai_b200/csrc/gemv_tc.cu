@@ -73,7 +73,7 @@ struct Smem {
 
 // kAhead: stages of packed weights an expanding thread holds in registers ahead of their use.
 template <int MT, int kAhead>
-__global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_tc_int4_kernel(const Params p) {
   constexpr int kN = n_of(MT);
   constexpr int kBufs = bufs_of(MT);
   constexpr int kTmemCols = tmem_cols_of(MT);
@@ -347,30 +347,37 @@ __global__ void __launch_bounds__(kThreads, MT <= 2 ? 2 : 1) gemv_tc_int4_kernel
         if (s_abort || !mbar_wait(&mma_done[b], q & 1u)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t nch = min((uint32_t)kStageGroups, c_end - (c_begin + i * kStageGroups));
-        constexpr int kQ = (MT * kLimbs + 3) / 4;  // 4-column loads per group
-        int32_t d[kStageGroups][kQ * 4];
+        constexpr int kQ = (MT * kLimbs + 3) / 4;            // 4-column loads per group
+        constexpr int kBatch = MT <= 2 ? kStageGroups : 1;  // groups whose sums are in registers at once
 #pragma unroll
-        for (int u = 0; u < kStageGroups; ++u) {
-          const uint32_t col = tmem_base + lane_base + (b * kStageGroups + u) * kN;
+        for (int u0 = 0; u0 < kStageGroups; u0 += kBatch) {
+          int32_t d[kBatch][kQ * 4];
 #pragma unroll
-          for (int q4 = 0; q4 < kQ; ++q4) {
-            int32_t t4[4];
-            tmem_ld4(col + 4 * q4, t4);  // groups past the end hold stale sums; they are not used below
-            d[u][4 * q4 + 0] = t4[0]; d[u][4 * q4 + 1] = t4[1]; d[u][4 * q4 + 2] = t4[2]; d[u][4 * q4 + 3] = t4[3];
+          for (int ub = 0; ub < kBatch; ++ub) {
+            const uint32_t col = tmem_base + lane_base + (b * kStageGroups + u0 + ub) * kN;
+#pragma unroll
+            for (int q4 = 0; q4 < kQ; ++q4) {
+              int32_t t4[4];
+              tmem_ld4(col + 4 * q4, t4);  // groups past the end hold stale sums; they are not used below
+              d[ub][4 * q4 + 0] = t4[0]; d[ub][4 * q4 + 1] = t4[1]; d[ub][4 * q4 + 2] = t4[2]; d[ub][4 * q4 + 3] = t4[3];
+            }
           }
-        }
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_free[b]);  // the next MMAs into this buffer may go
+          tmem_ld_wait();
+          if (u0 + kBatch >= kStageGroups) {  // the last sums of the stage are out: the next MMAs into this buffer may go
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_free[b]);
+          }
 #pragma unroll
-        for (int u = 0; u < kStageGroups; ++u) {
-          if ((uint32_t)u < nch) {
+          for (int ub = 0; ub < kBatch; ++ub) {
+            const int u = u0 + ub;
+            if ((uint32_t)u < nch) {
 #pragma unroll
-            for (int r = 0; r < MT; ++r) {
-              const uint32_t mi = (rb * kRoundGroups + a * kStageGroups + u) * MT + r;
-              const int val = d[u][kLimbs * r] * 16384 + d[u][kLimbs * r + 1] * 128 + d[u][kLimbs * r + 2] - 8 * meta_sum[mi];
-              acc[r] = fmaf((float)val, sq[a][u] * meta_scale[mi], acc[r]);
+              for (int r = 0; r < MT; ++r) {
+                const uint32_t mi = (rb * kRoundGroups + a * kStageGroups + u) * MT + r;
+                const int val = d[ub][kLimbs * r] * 16384 + d[ub][kLimbs * r + 1] * 128 + d[ub][kLimbs * r + 2] - 8 * meta_sum[mi];
+                acc[r] = fmaf((float)val, sq[a][u] * meta_scale[mi], acc[r]);
+              }
             }
           }
         }
