@@ -71,6 +71,26 @@ struct Smem {
   static size_t bytes(uint32_t splits) { return off_red + (size_t)splits * MT * kCols * 4 + 128; }
 };
 
+// Activations of one round for layouts the 16-byte path cannot take (any dtype, any alignment): one value at a time.
+template <int MT>
+static __device__ __noinline__ void fetch_round_scalar(float4* dst, const void* x, int x_dtype, uint32_t x_ld, uint32_t m0, uint32_t rows, uint32_t kidx,
+                                                       uint32_t k, bool in, const float* norm_w) {
+#pragma unroll 1
+  for (int r = 0; r < MT; ++r) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (in && r < (int)rows) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        if (kidx + t < k) {
+          v[t] = load_as_f32(x, x_dtype, (size_t)(m0 + r) * x_ld + kidx + t);
+          if (norm_w) v[t] = v[t] * norm_w[kidx + t];
+        }
+      }
+    }
+    dst[r] = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
 // kAhead: stages of packed weights an expanding thread holds in registers ahead of their use.
 template <int MT, int kAhead>
 __global__ void __launch_bounds__(kThreads, 2) gemv_tc_int4_kernel(const Params p) {
@@ -262,20 +282,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc_int4_kernel(const Params 
                                          : make_float4(0.f, 0.f, 0.f, 0.f);
         return;
       }
-#pragma unroll
-      for (int r = 0; r < MT; ++r) {
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (in && r < (int)rows) {
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            if (kidx + t < p.k) {
-              v[t] = load_as_f32(p.x, p.x_dtype, (size_t)(m0 + r) * p.x_ld + kidx + t);
-              if (normed) v[t] = v[t] * p.pro.norm_w[kidx + t];
-            }
-          }
-        }
-        dst[r] = make_float4(v[0], v[1], v[2], v[3]);
-      }
+      fetch_round_scalar<MT>(dst, p.x, p.x_dtype, p.x_ld, m0, rows, kidx, p.k, in, normed ? p.pro.norm_w : nullptr);
     };
     // this warp's 4 groups of a round (8 lanes per group): block fixed point, three int8 digits into the B operand
     auto convert = [&](uint32_t round, const float4 (&src)[MT], const float4& nw) {

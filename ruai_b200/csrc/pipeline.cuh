@@ -29,6 +29,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     if (ok) return true;
   }
+#pragma unroll 1
   for (unsigned i = 0; i < kWaitLimit; ++i) {
     uint32_t ok;
     asm volatile(
@@ -52,7 +53,7 @@ __device__ __forceinline__ void l2_prefetch(const void* ptr, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
 }
 // This CTA's share of a region, in pieces of at most 32 KB; one thread calls it.
-__device__ __forceinline__ void l2_prefetch_share(const void* base, size_t bytes, uint32_t cta, uint32_t n_ctas) {
+static __device__ __noinline__ void l2_prefetch_share(const void* base, size_t bytes, uint32_t cta, uint32_t n_ctas) {
   if (!base || !bytes) return;
   size_t per = (bytes + n_ctas - 1) / n_ctas;
   per = (per + 127) & ~(size_t)127;
