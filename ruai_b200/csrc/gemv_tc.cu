@@ -483,17 +483,20 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   const uint32_t row_tiles = (m + mt - 1) / mt;
   if (epi.argmax_out && row_tiles != 1) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "fused argmax needs a single row tile");
   const uint32_t col_tiles = (w->n + kCols - 1) / kCols;
-  // Split k over a cluster of up to 8 CTAs.  A launch is a link in a chain of
-  // dependent kernels, so what counts is its latency: waves x (fixed cost + stages per CTA x time per stage).
+  // Split k over a cluster of up to 8 CTAs.  A launch is a link in a chain of dependent kernels, so what counts is its
+  // latency.  Measured on the 8B shapes, in microseconds: about 5.5 per wave of CTAs that is fixed, 0.45 per stage
+  // (more with more rows) and 0.15 per CTA of the cluster for the reduction.
   const uint32_t slots = 2u * (uint32_t)c->sm_count;
+  const double per_stage = 0.45 * (mt == 1 ? 1.0 : mt == 2 ? 1.4 : mt == 4 ? 2.0 : 3.2);
   uint32_t splits = 1;
   double best = 1e30;
   for (uint32_t s2 = 1; s2 <= 8; s2 *= 2) {  // 16-CTA clusters were tried: fewer clusters fit at once and the launch got slower
     const uint32_t per = (w->chunks + s2 - 1) / s2;
     if (s2 > 1 && per < (uint32_t)kStageGroups) break;
     const uint32_t stages = (per + kStageGroups - 1) / kStageGroups;
-    const uint32_t waves = (col_tiles * row_tiles * s2 + slots - 1) / slots;
-    const double t = waves * (4.7 + 1.5 * stages + 0.15 * s2);
+    const uint32_t ctas = col_tiles * row_tiles * s2;
+    const uint32_t waves = (ctas + slots - 1) / slots;
+    const double t = waves * (5.5 + per_stage * stages) + 0.15 * s2;
     if (t < best) { best = t; splits = s2; }
   }
   uint32_t cpc = (w->chunks + splits - 1) / splits;
