@@ -165,11 +165,11 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
 // (functional.rs:197-204) on q and on the new key and appends the new key / value to the
 // cache (KvBuf::append, transformer.rs:27-53): the last key split owns the new position.
 
-constexpr int kAttnSub = 2;  // warps per (32 keys, query head): more warps than the work needs, to hide each other's latencies
-
-template <int REP>
-__global__ void __launch_bounds__(kAttnChunkKeys * REP * kAttnSub) attention_kernel(const AttnParams p) {
-  constexpr int kThreads = kAttnChunkKeys * REP * kAttnSub, kBlocks = kAttnChunkKeys / 32, kParts = REP * kAttnSub;
+// SUB: warps per (32 keys, query head).  2 (more warps than the work needs, to hide each other's latencies) for grids of
+// about one CTA per SM; 1 for large grids, where two or three smaller CTAs per SM hide them instead.
+template <int REP, int SUB>
+__global__ void __launch_bounds__(kAttnChunkKeys * REP * SUB) attention_kernel(const AttnParams p) {
+  constexpr int kThreads = kAttnChunkKeys * REP * SUB, kBlocks = kAttnChunkKeys / 32, kParts = REP * SUB;
   extern __shared__ __align__(128) float sm[];  // K chunk | V chunk | q [REP][hd] | new k | new v | probs | stats | parts | merge
   __shared__ __align__(8) uint64_t kv_bar;
   __shared__ unsigned s_last;
@@ -551,15 +551,22 @@ __global__ void take_last_rows_kernel(const float* __restrict__ x, uint32_t T, u
   for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) y[(size_t)blockIdx.x * d + i] = src[i];
 }
 
-template <int REP>
-cudaError_t launch_attn(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem) {
+template <int REP, int SUB>
+cudaError_t launch_attn_sub(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem) {
   static bool attr_done[64] = {};
   if (!attr_done[c->ordinal & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attention_kernel<REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel<REP, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_done[c->ordinal & 63] = true;
   }
-  return ruai_launch(c, attention_kernel<REP>, grid, dim3(kAttnChunkKeys * REP * kAttnSub), smem, true, p);
+  return ruai_launch(c, attention_kernel<REP, SUB>, grid, dim3(kAttnChunkKeys * REP * SUB), smem, true, p);
+}
+template <int REP>
+cudaError_t launch_attn(ruai_ctx* c, const AttnParams& p, dim3 grid, size_t smem_per_sub) {
+  // smem_per_sub: bytes without the partial scores; those take REP * REP * SUB * 64 floats more
+  const bool big = (size_t)grid.x * grid.y * grid.z > 2u * (size_t)c->sm_count;
+  const size_t parts = (size_t)REP * REP * kAttnChunkKeys * sizeof(float);
+  return big ? launch_attn_sub<REP, 1>(c, p, grid, smem_per_sub + parts) : launch_attn_sub<REP, 2>(c, p, grid, smem_per_sub + 2 * parts);
 }
 
 }  // namespace
@@ -601,7 +608,7 @@ int ruai_attention(ruai_ctx* c, const AttnParams& p_in, uint32_t B, uint32_t rep
   if (p.hd % 4 || p.hd > 256) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "head_dim %u must be a multiple of 4 and at most 256", p.hd);
   constexpr size_t kb = kAttnChunkKeys / 32;
   const size_t floats = 2 * (size_t)kAttnChunkKeys * p.hd + (size_t)rep * p.hd + 2 * (size_t)p.hd + kb * rep * 32 + (kb + 1) * rep + kb * rep +
-                        (size_t)kAttnSub * rep * rep * kAttnChunkKeys + 128 * (size_t)rep + rep;
+                        128 * (size_t)rep + rep;  // + the partial scores, added per variant at the launch
   const size_t smem = floats * sizeof(float);
   const dim3 grid(B * p.KV, p.T, splits);
   cudaError_t e;
