@@ -182,12 +182,6 @@ struct GemvPrologue {
   const float* sumsq = nullptr;
   uint32_t tiles = 0;
   float eps = 0.0f;
-  // Weights of the kernel that will run next: every CTA asks the L2 to fetch its share of them
-  // (cp.async.bulk.prefetch.L2), so the next kernel starts on warm lines while this one computes.
-  const void* next_data = nullptr;
-  size_t next_data_bytes = 0;
-  const void* next_scale = nullptr;
-  size_t next_scale_bytes = 0;
   unsigned long long* trace = nullptr;  // debug timeline slot of this launch
 };
 

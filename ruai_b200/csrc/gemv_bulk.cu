@@ -164,11 +164,6 @@ __global__ void __launch_bounds__(kCols) gemv_bulk_kernel(const Params p) {
   // weights do not depend on the predecessor kernel: fill the ring before waiting for it
   if (tid == 0)
     for (uint32_t i = 0; i < nst && i < (uint32_t)kStages; ++i) issue(i);
-  if (tid == 0) {  // warm the L2 for the kernel after this one
-    const uint32_t cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y * gridDim.z;
-    l2_prefetch_share(p.pro.next_data, p.pro.next_data_bytes, cta, n_ctas);
-    l2_prefetch_share(p.pro.next_scale, p.pro.next_scale_bytes, cta, n_ctas);
-  }
   if (tid == 0) trace_min(p.pro.trace, 0);
   grid_dependency_wait();
   if (tid == 0) trace_min(p.pro.trace, 1);

@@ -144,11 +144,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc_int4_kernel(const Params 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem;
-  if (tid == 0) {  // warm the L2 for the kernel after this one
-    const uint32_t cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y * gridDim.z;
-    l2_prefetch_share(p.pro.next_data, p.pro.next_data_bytes, cta, n_ctas);
-    l2_prefetch_share(p.pro.next_scale, p.pro.next_scale_bytes, cta, n_ctas);
-  }
   const bool normed = p.pro.norm_w != nullptr;
   float acc[MT];
   float resid_pre[MT];

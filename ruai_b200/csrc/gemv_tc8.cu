@@ -14,8 +14,8 @@
 // (|D_t| < 2^25 for k <= 4096 per CTA); the epilogue forms ((D3*128 + D2)*128 + D1)*128 + D0 in f32 and
 // multiplies by 2^(e-27) * scale[j].  An element much smaller than the row maximum keeps fewer
 // significant bits, but its absolute error stays below 2^-28 of the largest product, which is
-// inside the rounding of an f32 accumulation.  Split-K over a cluster, bounded waits, epilogues
-// and the weight prefetch are those of gemv_tc.cu.
+// inside the rounding of an f32 accumulation.  Split-K over a cluster, bounded waits and epilogues
+// are those of gemv_tc.cu.
 #include "common.cuh"
 #include "gemv_epilogue.cuh"
 #include "pipeline.cuh"
@@ -116,11 +116,6 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   // weights do not depend on the predecessor kernel: fill the ring before waiting for it
   if (tid == kCols + 32) {
     for (uint32_t i = 0; i < nst && i < (uint32_t)kStages; ++i) issue(i);
-  }
-  if (tid == 0) {  // warm the L2 for the kernel after this one
-    const uint32_t cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y * gridDim.z;
-    l2_prefetch_share(p.pro.next_data, p.pro.next_data_bytes, cta, n_ctas);
-    l2_prefetch_share(p.pro.next_scale, p.pro.next_scale_bytes, cta, n_ctas);
   }
   if (tid == 0) trace_min(p.pro.trace, 0);
   grid_dependency_wait();

@@ -469,13 +469,6 @@ int ensure_activations(ruai_model* m, uint32_t rows, uint32_t out_rows, uint32_t
 // Issues every kernel of one forward over rows = B*T new tokens whose ids are in d_ids and
 // whose first position is *d_len.  Logits for the last position of each sequence (or all
 // positions) land in m->logits.  With want_argmax the greedy next ids are written to d_ids[0..B).
-// Points a GEMV's prologue at the weights of the GEMV that follows it.
-void set_next(GemvPrologue& pr, const ruai_qweight* next) {
-  if (!next) return;
-  pr.next_data = next->data; pr.next_data_bytes = next->data_bytes;
-  pr.next_scale = next->scale; pr.next_scale_bytes = next->scale_bytes;
-}
-
 int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool want_argmax) {
   ruai_ctx* c = m->ctx;
   const uint32_t rows = B * T, d = m->d, hd = m->hd;
@@ -501,7 +494,6 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
     if (fold) {
       GemvPrologue pr;
       pr.norm_w = Ly.n1w.as<float>(); pr.sumsq = ss; pr.tiles = ss_tiles; pr.eps = m->eps;
-      set_next(pr, Ly.o.w);
       RUAI_TRY(ruai_gemv_launch(c, Ly.qkv.w, x, RUAI_F32, d, rows, qkv, e, pr));
     } else {
       if (m->llama) RUAI_TRY(ruai_rms_norm(c, x, Ly.n1w.as<float>(), rows, d, m->eps, xn));
@@ -524,7 +516,6 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
       eo.resid = x;
       eo.sumsq = ss;
       GemvPrologue po;
-      set_next(po, Ly.up.w);
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, nql, rows, x, eo, po));
     } else {
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, nql, rows, m->tp.local_partial(), eo));
@@ -537,7 +528,6 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
     if (fold) {
       GemvPrologue pr;
       pr.norm_w = Ly.n2w.as<float>(); pr.sumsq = ss; pr.tiles = ss_tiles; pr.eps = m->eps;
-      set_next(pr, Ly.down.w);
       RUAI_TRY(ruai_gemv_launch(c, Ly.up.w, x, RUAI_F32, d, rows, hb, eu, pr));
     } else {
       if (m->llama) RUAI_TRY(ruai_rms_norm(c, x, Ly.n2w.as<float>(), rows, d, m->eps, xn));
@@ -550,7 +540,6 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
       ed.resid = x;
       ed.sumsq = ss;
       GemvPrologue pd;
-      set_next(pd, l + 1 < m->L ? m->layers[l + 1].qkv.w : m->head.w);
       RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, rows, x, ed, pd));
     } else {
       RUAI_TRY(ruai_gemv_launch(c, Ly.down.w, hb, RUAI_F32, m->fl, rows, m->tp.local_partial(), ed));
@@ -889,8 +878,6 @@ RUAI_API int ruai_model_time_linears(ruai_model* m, uint32_t B, uint32_t iters, 
       e2.act = m->llama ? ACT_SWIGLU : ACT_GELU;
       GemvPrologue p0, p1, p2, p3;
       const size_t li = (size_t)(&Ly - m->layers.data());
-      set_next(p0, Ly.o.w); set_next(p1, Ly.up.w); set_next(p2, Ly.down.w);
-      set_next(p3, li + 1 < m->layers.size() ? m->layers[li + 1].qkv.w : m->head.w);
       RUAI_TRY(ruai_gemv_launch(c, Ly.qkv.w, xn, RUAI_F32, m->d, B, qkv, e0, p0));
       RUAI_TRY(ruai_gemv_launch(c, Ly.o.w, att, RUAI_F32, m->Hl * m->hd, B, xl, e1, p1));
       RUAI_TRY(ruai_gemv_launch(c, Ly.up.w, xn, RUAI_F32, m->d, B, hb, e2, p2));

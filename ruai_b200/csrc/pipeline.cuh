@@ -48,24 +48,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                "r"(smem_u32(bar))
                : "memory");
 }
-// Asks the L2 to fetch [ptr, ptr + bytes) (16-byte aligned, multiple of 16); nothing waits for it.
-__device__ __forceinline__ void l2_prefetch(const void* ptr, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-}
-// This CTA's share of a region, in pieces of at most 32 KB; one thread calls it.
-static __device__ __noinline__ void l2_prefetch_share(const void* base, size_t bytes, uint32_t cta, uint32_t n_ctas) {
-  if (!base || !bytes) return;
-  size_t per = (bytes + n_ctas - 1) / n_ctas;
-  per = (per + 127) & ~(size_t)127;
-  size_t b0 = (size_t)cta * per;
-  if (b0 >= bytes) return;
-  size_t b1 = b0 + per < bytes ? b0 + per : bytes;
-  b1 &= ~(size_t)15;
-  for (size_t o = b0; o < b1; o += 32768) {
-    const size_t n = b1 - o < 32768 ? b1 - o : 32768;
-    l2_prefetch((const char*)base + o, (uint32_t)n);
-  }
-}
 // Global loads that stay where they are written: a prefetch into registers is only worth something if the compiler does
 // not move the load down to its first use.  `stream`: evict-first (data read once).
 __device__ __forceinline__ uint4 ldg_stream_u4(const uint4* p) {
