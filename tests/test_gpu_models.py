@@ -117,6 +117,24 @@ def test_causal_and_batched(dev):
     assert np.abs(both[0] - la[0]).max() < 1e-5 and np.abs(both[1] - lb[0]).max() < 1e-5
 
 
+@pytest.mark.parametrize("H,KV,hd,B", [(4, 2, 96, 1), (6, 6, 24, 3), (8, 1, 40, 2), (4, 2, 96, 40)])
+def test_attention_geometries(dev, H, KV, hd, B):
+    """Head dimensions that are not powers of two, 1 / 2 / 8 query heads per KV head, and enough sequences to take the
+    small-CTA variant of the attention kernel: prefill of 70 tokens (two chunks of keys, causal) and then single-token
+    steps over several key splits, against the checker."""
+    cfg = dict(V=53, d=H * hd, ffn=64, L=2, H=H, KV=KV, hd=hd, max_pos=256)
+    om, gm = build(dev, llama_cfg(**cfg), 11, 8)
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, cfg["V"], (B, 70)).astype(np.int32)
+    close(om.forward_cached(prompt), gm.forward_cached(prompt), "prefill")
+    tok = rng.integers(0, cfg["V"], (B, 1)).astype(np.int32)
+    for step in range(70):
+        want, got = om.forward_cached(tok), gm.forward_cached(tok)
+        if step % 23 == 0 or step == 69:
+            close(want, got, f"step {step}")
+        tok = np.argmax(want, axis=1).astype(np.int32).reshape(B, 1)
+
+
 def test_errors_mirror_the_reference_asserts(dev):
     _, gm = build(dev, llama_cfg(**dict(TINY_LLAMA, max_pos=8)), 5, 8)
     with pytest.raises(nn.RuaiError, match="exceeds max_position_embeddings"):
