@@ -1,5 +1,5 @@
 // Fused dequantize + GEMV on the tensor cores (tcgen05, accumulators in tensor memory) for
-// int4 group-32 weights and up to four rows of activations: the decode hot path.
+// int4 group-32 weights and up to sixteen rows of activations (eight per CTA): the decode hot path.
 //
 // Why tensor cores for a memory-bound kernel: at full HBM speed one SM has to consume about
 // 46 int4 weights per clock.  On the CUDA cores every weight costs a byte permute, a
