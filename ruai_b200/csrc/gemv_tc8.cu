@@ -26,12 +26,17 @@ using namespace pipe;
 
 constexpr int kCols = kGemvBulkTileCols;  // 128
 constexpr int kStageChunks = 4;           // chunk rows (16 k each) per ring stage: two MMAs of K = 32
-constexpr int kStages = 6;                // ring stages (8 KB each)
+// ring stages (8 KB each): 10 for long slices of k with few rows (the digit buffer leaves room), 6 otherwise
+constexpr int kStagesShort = 6, kStagesLong = 10;
 constexpr int kLimbs = 4;
 constexpr int kThreads = kCols + 64;
 constexpr int kMaxSliceK = 4096;          // k per CTA (bounds the digit buffer and the s32 sums)
 
 constexpr int n_of(int mt) { return mt <= 4 ? 16 : 32; }
+// Rows of the digit operand that are stored.  With at most 8 rows in use (two rows of activations x four digits) only
+// the first 8-row group is kept and the descriptor's stride between 8-row groups is 0: the MMA reads it twice and leaves
+// a copy of columns 0-7 in columns 8-15 of the accumulator, which nobody reads.  Halves the digit buffer.
+constexpr int nb_of(int mt) { return mt <= 2 ? 8 : n_of(mt); }
 
 struct Params {
   const uint4* w;
@@ -45,20 +50,23 @@ struct Params {
   GemvPrologue pro;
 };
 
-template <int MT>
+template <int MT, int STAGES>
 struct Smem {
-  static constexpr int kN = n_of(MT);
+  static constexpr int kNB = nb_of(MT);
+  static constexpr int kStages = STAGES;
   static constexpr size_t off_ring = 0;
   static constexpr size_t off_b = off_ring + (size_t)kStages * kStageChunks * kCols * 16;
-  __host__ __device__ static size_t off_red(uint32_t slice_k) { return off_b + (size_t)(slice_k / 32) * kN * 32; }
+  __host__ __device__ static size_t off_red(uint32_t slice_k) { return off_b + (size_t)(slice_k / 32) * kNB * 32; }
   __host__ __device__ static size_t bytes(uint32_t slice_k, uint32_t splits) { return off_red(slice_k) + (size_t)splits * MT * kCols * 4 + 128; }
 };
 
-template <int MT>
+template <int MT, int STAGES>
 __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, uint32_t slice_k) {
   constexpr int kN = n_of(MT);
-  static_assert(MT * kLimbs <= kN, "rows x limbs must fit the MMA N");
-  using L = Smem<MT>;
+  constexpr int kNB = nb_of(MT);
+  constexpr int kStages = STAGES;
+  static_assert(MT * kLimbs <= kNB, "rows x limbs must fit the stored rows of the digit operand");
+  using L = Smem<MT, STAGES>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t full[kStages];   // ring stage landed
   __shared__ __align__(8) uint64_t empty[kStages];  // MMAs that read the stage completed
@@ -107,7 +115,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   __syncwarp();
   if (warp == 0) tmem_alloc(&s_tmem, 32);
   // the digit buffer starts as zeros (rows beyond rows x limbs, and k beyond the slice, stay zero)
-  for (uint32_t i = tid; i < (slice_k / 32) * kN * 32 / 16; i += kThreads) reinterpret_cast<uint4*>(bop)[i] = make_uint4(0, 0, 0, 0);
+  for (uint32_t i = tid; i < (slice_k / 32) * kNB * 32 / 16; i += kThreads) reinterpret_cast<uint4*>(bop)[i] = make_uint4(0, 0, 0, 0);
   // (an odd slice makes the last MMA read one chunk row that was never loaded: its digits are zero, so it adds nothing)
   tc_fence_before_sync();
   __syncthreads();
@@ -142,7 +150,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8(kN, true);
       const uint64_t ad0 = umma_desc_kmajor(smem_u32(ring), kCols * 16, 128);
-      const uint64_t bd0 = umma_desc_kmajor(smem_u32(bop), kN / 8 * 128, 128);
+      const uint64_t bd0 = umma_desc_kmajor(smem_u32(bop), kNB / 8 * 128, kNB == kN ? 128 : 0);
       bool ok = mbar_wait(&b_ready, 0);
       uint32_t left = c_end - c_begin, slot = 0, par = 0;
       uint64_t bd = bd0;
@@ -152,8 +160,8 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
         const uint64_t ad = umma_desc_advance(ad0, slot * (kStageChunks * kCols * 16));
         // one MMA per two chunk rows (K = 32); an odd last chunk is paired with digits that are zero
         umma_i8(tmem_base, ad, bd, idesc, i != 0u ? 1u : 0u);
-        if (left > 2) umma_i8(tmem_base, umma_desc_advance(ad, 2 * kCols * 16), umma_desc_advance(bd, kN * 32), idesc, 1u);
-        bd = umma_desc_advance(bd, 2 * kN * 32);
+        if (left > 2) umma_i8(tmem_base, umma_desc_advance(ad, 2 * kCols * 16), umma_desc_advance(bd, kNB * 32), idesc, 1u);
+        bd = umma_desc_advance(bd, 2 * kNB * 32);
         umma_commit(&empty[slot]);
         if (++slot == (uint32_t)kStages) { slot = 0; par ^= 1u; }
       }
@@ -204,7 +212,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
     auto put4 = [&](int r, uint32_t idx, const float4& v, float up) {
       int f[4] = {__float2int_rn(v.x * up), __float2int_rn(v.y * up), __float2int_rn(v.z * up), __float2int_rn(v.w * up)};
       const uint32_t rel = idx << 2, g = rel >> 5, l = rel & 31u;
-      unsigned char* bg = bop + (size_t)g * (kN * 32) + (l >> 4) * (kN / 8 * 128) + (l & 15u);
+      unsigned char* bg = bop + (size_t)g * (kNB * 32) + (l >> 4) * (kNB / 8 * 128) + (l & 15u);
 #pragma unroll
       for (int t = kLimbs - 1; t >= 0; --t) {  // least significant digit first; operand rows: most significant first
         uint32_t pack = 0;
@@ -307,7 +315,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
             if (normed) v *= p.pro.norm_w[kk];
             int f = __float2int_rn(v * up);
             const uint32_t rel = kk - kbeg, g = rel >> 5, l = rel & 31;
-            unsigned char* bg = bop + (size_t)g * (kN * 32) + (l >> 4) * (kN / 8 * 128) + (l & 15);
+            unsigned char* bg = bop + (size_t)g * (kNB * 32) + (l >> 4) * (kNB / 8 * 128) + (l & 15);
 #pragma unroll
             for (int t = kLimbs - 1; t >= 0; --t) {
               const int dgt = t > 0 ? ((f + 64) & 127) - 64 : f;
@@ -369,18 +377,18 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
   if (tid == 0) trace_max(p.pro.trace, 2);
 }
 
-template <int MT>
+template <int MT, int STAGES>
 cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid, uint32_t slice_k) {
   static bool attr_done[64] = {};
   if (!attr_done[c->ordinal & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_tc_int8_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT>::bytes(kMaxSliceK, 8));
+    cudaError_t e = cudaFuncSetAttribute(gemv_tc_int8_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT, STAGES>::bytes(kMaxSliceK, 8));
     if (e != cudaSuccess) return e;
     attr_done[c->ordinal & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = Smem<MT>::bytes(slice_k, p.splits);
+  cfg.dynamicSmemBytes = Smem<MT, STAGES>::bytes(slice_k, p.splits);
   cfg.stream = c->stream;
   cudaLaunchAttribute attr[2];
   int na = 0;
@@ -399,7 +407,7 @@ cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid, uint32_t slice_k
   cfg.attrs = attr;
   cfg.numAttrs = na;
   c->launches++;
-  return cudaLaunchKernelEx(&cfg, gemv_tc_int8_kernel<MT>, p, slice_k);
+  return cudaLaunchKernelEx(&cfg, gemv_tc_int8_kernel<MT, STAGES>, p, slice_k);
 }
 
 }  // namespace gemv_tc8
@@ -446,8 +454,10 @@ int ruai_gemv_tc8_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int 
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
   p.pro.trace = ruai_trace_slot(c);
   const dim3 grid(col_tiles, splits, row_tiles);
-  cudaError_t e = mt == 1 ? launch_one<1>(c, p, grid, slice_k) : mt == 2 ? launch_one<2>(c, p, grid, slice_k)
-                : mt == 4 ? launch_one<4>(c, p, grid, slice_k) : launch_one<8>(c, p, grid, slice_k);
+  const bool deep = mt <= 2 && slice_k >= 2048;  // a long slice of k and a small digit buffer: the deeper ring pays
+  cudaError_t e = mt == 1 ? (deep ? launch_one<1, kStagesLong>(c, p, grid, slice_k) : launch_one<1, kStagesShort>(c, p, grid, slice_k))
+                : mt == 2 ? (deep ? launch_one<2, kStagesLong>(c, p, grid, slice_k) : launch_one<2, kStagesShort>(c, p, grid, slice_k))
+                : mt == 4 ? launch_one<4, kStagesShort>(c, p, grid, slice_k) : launch_one<8, kStagesShort>(c, p, grid, slice_k);
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "int8 tensor-core gemv launch failed: %s", cudaGetErrorString(e));
   return RUAI_OK;
 }
