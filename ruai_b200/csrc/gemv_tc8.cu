@@ -26,17 +26,18 @@ using namespace pipe;
 
 constexpr int kCols = kGemvBulkTileCols;  // 128
 constexpr int kStageChunks = 4;           // chunk rows (16 k each) per ring stage: two MMAs of K = 32
-// ring stages (8 KB each): 10 for long slices of k with few rows (the digit buffer leaves room), 6 otherwise
-constexpr int kStagesShort = 6, kStagesLong = 10;
 constexpr int kLimbs = 4;
 constexpr int kThreads = kCols + 64;
 constexpr int kMaxSliceK = 4096;          // k per CTA (bounds the digit buffer and the s32 sums)
 
+// ring stages (8 KB each): 10 for long slices of k with few rows (the digit buffer leaves room), 6 otherwise
+constexpr int kStagesShort = 6, kStagesLong = 10;
 constexpr int n_of(int mt) { return mt <= 4 ? 16 : 32; }
-// Rows of the digit operand that are stored.  With at most 8 rows in use (two rows of activations x four digits) only
-// the first 8-row group is kept and the descriptor's stride between 8-row groups is 0: the MMA reads it twice and leaves
-// a copy of columns 0-7 in columns 8-15 of the accumulator, which nobody reads.  Halves the digit buffer.
-constexpr int nb_of(int mt) { return mt <= 2 ? 8 : n_of(mt); }
+// Rows of the digit operand that are stored.  In the long-slice variant, with at most 8 rows in use (two rows of
+// activations x four digits), only the first 8-row group is kept and the descriptor's stride between 8-row groups is
+// 0: the MMA reads it twice and leaves a copy of columns 0-7 in columns 8-15 of the accumulator, which nobody reads.
+// That halves the digit buffer and makes room for the longer ring.
+constexpr int nb_of(int mt, int stages) { return mt <= 2 && stages == kStagesLong ? 8 : n_of(mt); }
 
 struct Params {
   const uint4* w;
@@ -52,7 +53,7 @@ struct Params {
 
 template <int MT, int STAGES>
 struct Smem {
-  static constexpr int kNB = nb_of(MT);
+  static constexpr int kNB = nb_of(MT, STAGES);
   static constexpr int kStages = STAGES;
   static constexpr size_t off_ring = 0;
   static constexpr size_t off_b = off_ring + (size_t)kStages * kStageChunks * kCols * 16;
@@ -63,7 +64,7 @@ struct Smem {
 template <int MT, int STAGES>
 __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, uint32_t slice_k) {
   constexpr int kN = n_of(MT);
-  constexpr int kNB = nb_of(MT);
+  constexpr int kNB = nb_of(MT, STAGES);
   constexpr int kStages = STAGES;
   static_assert(MT * kLimbs <= kNB, "rows x limbs must fit the stored rows of the digit operand");
   using L = Smem<MT, STAGES>;
@@ -454,7 +455,7 @@ int ruai_gemv_tc8_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int 
   p.out = out; p.status = c->status; p.epi = epi; p.pro = pro;
   p.pro.trace = ruai_trace_slot(c);
   const dim3 grid(col_tiles, splits, row_tiles);
-  const bool deep = mt <= 2 && slice_k >= 2048;  // a long slice of k and a small digit buffer: the deeper ring pays
+  const bool deep = mt <= 2 && slice_k >= 4096;  // a long slice of k and a small digit buffer: the deeper ring pays
   cudaError_t e = mt == 1 ? (deep ? launch_one<1, kStagesLong>(c, p, grid, slice_k) : launch_one<1, kStagesShort>(c, p, grid, slice_k))
                 : mt == 2 ? (deep ? launch_one<2, kStagesLong>(c, p, grid, slice_k) : launch_one<2, kStagesShort>(c, p, grid, slice_k))
                 : mt == 4 ? launch_one<4, kStagesShort>(c, p, grid, slice_k) : launch_one<8, kStagesShort>(c, p, grid, slice_k);
