@@ -280,7 +280,9 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP * SUB) attention_kernel(c
       if (tid == 0) fetch_chunk(c0);
     }
     if (have_keys) {
-      if (!pipe::mbar_wait(&kv_bar, phase & 1u)) { ok = false; break; }
+      // the whole CTA leaves together if the copy did not arrive for any of its threads: the barriers below are for all
+      const bool got = pipe::mbar_wait(&kv_bar, phase & 1u);
+      if (__syncthreads_or(!got)) { ok = false; break; }
       ++phase;
     }
     const uint32_t c1 = have_keys ? min(k1, c0 + kAttnChunkKeys) : c0;
