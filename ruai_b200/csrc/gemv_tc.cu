@@ -45,8 +45,11 @@ constexpr int kThreads = 2 * kCols + 32;  // draining warps 0-3, issuing warp 4,
 constexpr int kExpand0 = kCols + 32;      // first expanding thread
 // MMA N (rows x limbs, padded to a multiple of 16), stage buffers (A operand + accumulators), TMEM columns
 constexpr int n_of(int mt) { return mt <= 4 ? 16 : 32; }
-constexpr int bufs_of(int mt) { return mt <= 4 ? 4 : 2; }
-constexpr int tmem_cols_of(int mt) { return bufs_of(mt) * kStageGroups * n_of(mt); }  // 256
+// The variant with a 2-stage register queue and up to two rows is the small one: two stage buffers, 128 TMEM columns,
+// about 52 KB of shared memory and 72 registers, so that three CTAs fit an SM; it serves launches of few stages per CTA.
+constexpr bool small_of(int mt, int ahead) { return mt <= 2 && ahead == 2; }
+constexpr int bufs_of(int mt, int ahead) { return mt <= 4 && !small_of(mt, ahead) ? 4 : 2; }
+constexpr int tmem_cols_of(int mt, int ahead) { return bufs_of(mt, ahead) * kStageGroups * n_of(mt); }  // 256 or 128
 
 struct Params {
   const uint4* w;
@@ -60,10 +63,10 @@ struct Params {
   GemvPrologue pro;
 };
 
-template <int MT>
+template <int MT, int AHEAD>
 struct Smem {
   static constexpr int kN = n_of(MT);
-  static constexpr int kBufs = bufs_of(MT);
+  static constexpr int kBufs = bufs_of(MT, AHEAD);
   static constexpr size_t off_a = 0;
   static constexpr size_t off_b = off_a + (size_t)kBufs * kStageGroups * kCols * 32;
   static constexpr size_t off_meta = off_b + 2 * (size_t)kRoundGroups * kN * 32;
@@ -93,13 +96,13 @@ static __device__ __noinline__ void fetch_round_scalar(float4* dst, const void* 
 
 // kAhead: stages of packed weights an expanding thread holds in registers ahead of their use.
 template <int MT, int kAhead>
-__global__ void __launch_bounds__(kThreads, 2) gemv_tc_int4_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_tc_int4_kernel(const Params p) {
   constexpr int kN = n_of(MT);
-  constexpr int kBufs = bufs_of(MT);
-  constexpr int kTmemCols = tmem_cols_of(MT);
+  constexpr int kBufs = bufs_of(MT, kAhead);
+  constexpr int kTmemCols = tmem_cols_of(MT, kAhead);
   static_assert(MT * kLimbs <= kN, "rows x limbs must fit the MMA N");
   static_assert((kBufs & (kBufs - 1)) == 0 && kRoundStages % kBufs == 0, "stage buffers must divide a round");
-  using L = Smem<MT>;
+  using L = Smem<MT, kAhead>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t a_ready[kBufs];   // A operand of a stage written (4 expanding warps)
   __shared__ __align__(8) uint64_t mma_done[kBufs];  // MMAs of a stage completed: sums valid, A buffer free
@@ -429,7 +432,7 @@ template <int MT, int AHEAD>
 cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
   static bool attr_done[64] = {};
   if (!attr_done[c->ordinal & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_tc_int4_kernel<MT, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT>::bytes(8));
+    cudaError_t e = cudaFuncSetAttribute(gemv_tc_int4_kernel<MT, AHEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<MT, AHEAD>::bytes(8));
     if (e != cudaSuccess) return e;
 
     attr_done[c->ordinal & 63] = true;
@@ -437,7 +440,7 @@ cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = Smem<MT>::bytes(p.splits);
+  cfg.dynamicSmemBytes = Smem<MT, AHEAD>::bytes(p.splits);
   cfg.stream = c->stream;
   cudaLaunchAttribute attr[2];
   int na = 0;
@@ -481,21 +484,25 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   // Split k over a cluster of up to 8 CTAs.  A launch is a link in a chain of dependent kernels, so what counts is its
   // latency.  Measured on the 8B shapes, in microseconds: about 5.5 per wave of CTAs that is fixed, 0.45 per stage
   // (more with more rows) and 0.15 per CTA of the cluster for the reduction.
-  const uint32_t slots = 2u * (uint32_t)c->sm_count;
   const double per_stage = 0.45 * (mt == 1 ? 1.0 : mt == 2 ? 1.4 : mt == 4 ? 2.0 : 3.2);
   uint32_t splits = 1;
+  bool small = false;  // the three-CTAs-per-SM variant
   double best = 1e30;
-  for (uint32_t s2 = 1; s2 <= 8; s2 *= 2) {  // 16-CTA clusters were tried: fewer clusters fit at once and the launch got slower
-    const uint32_t per = (w->chunks + s2 - 1) / s2;
-    if (s2 > 1 && per < (uint32_t)kStageGroups) break;
-    const uint32_t stages = (per + kStageGroups - 1) / kStageGroups;
-    const uint32_t ctas = col_tiles * row_tiles * s2;
-    const uint32_t waves = (ctas + slots - 1) / slots;
-    // clusters of 8 that nearly fill the machine do not always find their places at once (measured on o_proj: 256 CTAs,
-    // 5.7 or 9.8 us from launch to launch; as 128 CTAs in clusters of 4 always 6.5)
-    const double crowd = (s2 == 8 && 4u * ctas > 3u * slots) ? 2.0 : 0.0;
-    const double t = waves * (5.5 + per_stage * stages) + 0.15 * s2 + crowd;
-    if (t < best) { best = t; splits = s2; }
+  for (int variant = 0; variant < (mt <= 2 ? 2 : 1); ++variant) {
+    const uint32_t slots = (variant ? 3u : 2u) * (uint32_t)c->sm_count;
+    for (uint32_t s2 = 1; s2 <= 8; s2 *= 2) {  // 16-CTA clusters were tried: fewer clusters fit at once and the launch got slower
+      const uint32_t per = (w->chunks + s2 - 1) / s2;
+      if (s2 > 1 && per < (uint32_t)kStageGroups) break;
+      const uint32_t stages = (per + kStageGroups - 1) / kStageGroups;
+      if (variant && stages > 8) continue;  // the small variant's short queues are for short slices
+      const uint32_t ctas = col_tiles * row_tiles * s2;
+      const uint32_t waves = (ctas + slots - 1) / slots;
+      // clusters of 8 that nearly fill the machine do not always find their places at once (measured on o_proj: 256 CTAs,
+      // 5.7 or 9.8 us from launch to launch; as 128 CTAs in clusters of 4 always 6.5)
+      const double crowd = (s2 == 8 && 4u * ctas > 3u * slots) ? 2.0 : 0.0;
+      const double t = waves * (5.5 + per_stage * stages) + 0.15 * s2 + crowd + (variant ? 0.2 : 0.0);
+      if (t < best) { best = t; splits = s2; small = variant != 0; }
+    }
   }
   uint32_t cpc = (w->chunks + splits - 1) / splits;
   cpc = (cpc + kStageGroups - 1) / kStageGroups * kStageGroups;
@@ -512,8 +519,8 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   const dim3 grid(col_tiles, splits, row_tiles);
   // few CTAs per SM: spend the free registers on a deeper weight queue
   const bool deep = !(c->force_splits & 256u);
-  cudaError_t e = mt == 1 ? (deep ? launch_one<1, 4>(c, p, grid) : launch_one<1, 2>(c, p, grid))
-                : mt == 2 ? (deep ? launch_one<2, 4>(c, p, grid) : launch_one<2, 2>(c, p, grid))
+  cudaError_t e = mt == 1 ? (deep && !small ? launch_one<1, 4>(c, p, grid) : launch_one<1, 2>(c, p, grid))
+                : mt == 2 ? (deep && !small ? launch_one<2, 4>(c, p, grid) : launch_one<2, 2>(c, p, grid))
                 : mt == 4 ? launch_one<4, 2>(c, p, grid)
                           : launch_one<8, 2>(c, p, grid);
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "tensor-core gemv launch failed: %s", cudaGetErrorString(e));
