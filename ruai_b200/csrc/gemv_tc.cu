@@ -499,7 +499,7 @@ int ruai_gemv_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
       const uint32_t waves = (ctas + slots - 1) / slots;
       // clusters of 8 that nearly fill the machine do not always find their places at once (measured on o_proj: 256 CTAs,
       // 5.7 or 9.8 us from launch to launch; as 128 CTAs in clusters of 4 always 6.5)
-      const double crowd = (s2 == 8 && 4u * ctas > 3u * slots) ? 2.0 : 0.0;
+      const double crowd = (s2 == 8 && (variant ? 10u * ctas > 9u * slots : 4u * ctas > 3u * slots)) ? 2.0 : 0.0;
       const double t = waves * (5.5 + per_stage * stages) + 0.15 * s2 + crowd + (variant ? 0.2 : 0.0);
       if (t < best) { best = t; splits = s2; small = variant != 0; }
     }
