@@ -64,6 +64,16 @@ int ruai_device_count(void);
 /* Library version string. */
 const char* ruai_version(void);
 
+/* Bound of every device-side wait of the persistent kernels, in polls (0 restores the default,
+ * about a second).  A wait that runs out makes the launch return early; the next status check
+ * reports RUAI_ERR_TIMEOUT and the context stays usable.  The reference has no counterpart (its
+ * kernels never wait on one another). */
+int ruai_ctx_set_wait_limit(ruai_ctx* ctx, unsigned polls);
+/* Failure injection, on the host: the next persistent launch on this context is told that `grids`
+ * more grid-wide arrivals precede it than really do, so its first grid barrier can never
+ * complete and its bounded wait runs out.  Nothing faults; used by the timeout tests. */
+int ruai_ctx_inject_barrier_skew(ruai_ctx* ctx, unsigned grids);
+
 /* Device memory for callers without their own allocator (cuda.rs:288-300). */
 int ruai_malloc(ruai_ctx* ctx, size_t bytes, void** out_dev);
 int ruai_free(ruai_ctx* ctx, void* ptr_dev);
@@ -121,6 +131,15 @@ int ruai_matmul_q(ruai_ctx* ctx, int x_dtype, const void* x_dev, const ruai_qwei
  * Only chunk-layout weights (int8, or int4 with group 32). */
 int ruai_matmul_q_static(ruai_ctx* ctx, int x_dtype, const void* x_dev, const ruai_qweight* w,
                          const float* bias_dev_or_null, void* out_dev, uint32_t m);
+/* The same product for 1 or 2 rows of f32 activations through the data path of the persistent
+ * decode kernel (one cooperative launch, one CTA per SM, weights streamed through a ring of bulk
+ * copies in the tile-stream layout, split-k sums met in 64-bit fixed-point accumulators, so the
+ * result is bit-identical from run to run).  The tile-stream copy of the weight is built on the
+ * first call and kept with the qweight.  `repeat` >= 1 runs the product that many times inside
+ * the one launch (the phases of a decode step in miniature; used to time the streaming rate).
+ * Replaces the same reference methods as ruai_matmul_q (mod.rs:675-682, 700-704).           */
+int ruai_matmul_q_stream(ruai_ctx* ctx, const float* x_dev, const ruai_qweight* w, float* out_dev,
+                         uint32_t m, uint32_t repeat);
 /* `Backend::dequant_int4` (mod.rs:689-693, cpu.rs:1023-1033): exact f32 [k,n]. */
 int ruai_dequant_int4(ruai_ctx* ctx, const ruai_qweight* w, float* out_dev);
 /* Same on reference-layout device buffers, without a repack (any even group). */
@@ -170,6 +189,17 @@ int ruai_model_load_synthetic(ruai_model* m, uint64_t seed, uint32_t bits, uint3
 #define RUAI_TN_LAYER_NORM2  0x52000000ull /* + layer: post_attention_layernorm / ln_2 weight */
 #define RUAI_TN_LAYER_NORM2B 0x53000000ull /* + layer: ln_2 bias */
 int ruai_model_set_f32(ruai_model* m, uint64_t tensor_id, const float* data_host, size_t count);
+/* Hand one Linear over already quantized, in the reference's buffer layout (`weight_int8` [k,n] +
+ * `weight_scale` [n], or `weight_int4` [k/2,n] + `weight_int4_scale` [k/group,n]; layers.rs:205-211),
+ * as a checkpoint saved by `serialize::save` of a quantized model holds it (serialize.rs:239-241).
+ * ids: block Linears and RUAI_T_LMHEAD (`lm_head.weight_int8`, also present for a tied model).  The
+ * following ruai_model_quantize(bits, group) repacks these as they are and quantizes only what was
+ * set as f32. */
+int ruai_model_set_quantized(ruai_model* m, uint64_t tensor_id, const int8_t* q_host, const float* scale_host,
+                             uint32_t bits, uint32_t group);
+/* Read back one f32 tensor of a loaded model (embeddings, norm parameters, GPT-2 biases): the
+ * parameters `state_dict()` of a quantized model still holds (llama.rs:559-578, gpt2.rs:344-358). */
+int ruai_model_get_f32(ruai_model* m, uint64_t tensor_id, float* out_host, size_t count);
 /* `Llama::quantize_int8` / `quantize_int4(group)` over the f32 tensors set so far. */
 int ruai_model_quantize(ruai_model* m, uint32_t bits, uint32_t group);
 /* Read back one block Linear (or the head, tensor id RUAI_T_LMHEAD) in the

@@ -59,6 +59,10 @@ def lib():
         L.orc_gpt2_create.argtypes = [C.POINTER(GPT2Config), u64, u32, u32]
         L.orc_gpt2_create.restype = C.c_void_p
         L.orc_model_destroy.argtypes = [C.c_void_p]
+        L.orc_threads.restype = C.c_int
+        L.orc_set_threads.argtypes = [C.c_int]
+        L.orc_model_cache_assume.argtypes = [C.c_void_p, u32, u32]
+        L.orc_model_cache_assume.restype = C.c_int
         L.orc_model_cache_clear.argtypes = [C.c_void_p]
         L.orc_model_cache_len.argtypes = [C.c_void_p]
         L.orc_model_cache_len.restype = u32
@@ -72,6 +76,15 @@ def lib():
         L.orc_model_generate.restype = C.c_int
         _lib = L
     return _lib
+
+
+def threads():
+    """Threads the checker's OpenMP loops run on."""
+    return int(lib().orc_threads())
+
+
+def set_threads(n):
+    lib().orc_set_threads(int(n))
 
 
 def _f32(a):
@@ -229,6 +242,11 @@ class Model:
 
     def cache_clear(self):
         lib().orc_model_cache_clear(self.h)
+
+    def cache_assume(self, B, length):
+        """Zero keys and values for `length` cached positions of batch B (timing aid)."""
+        if lib().orc_model_cache_assume(self.h, B, length):
+            raise RuntimeError("oracle cache_assume failed")
 
     def cache_len(self):
         return lib().orc_model_cache_len(self.h)

@@ -15,6 +15,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <omp.h>
 #include <vector>
 
 #include "../include/ruai_b200.h"
@@ -525,6 +526,23 @@ ORC void* orc_gpt2_create(const ruai_gpt2_config* c, uint64_t seed, uint32_t bit
 }
 
 ORC void orc_model_destroy(void* h) { delete (Model*)h; }
+
+// Threads the OpenMP loops of this library use, and a way to set them (a launcher may have exported
+// OMP_NUM_THREADS=1 for its children).
+ORC int orc_threads(void) { return omp_get_max_threads(); }
+ORC void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+
+// Pretends `len` positions are cached for batch B (zero keys and values): times a decode step at a given
+// context without running the prompt.  Same capacity rule as an append of `len` positions.
+ORC int orc_model_cache_assume(void* h, uint32_t B, uint32_t len) {
+  Model* M = (Model*)h;
+  if (len + 1 > M->max_pos) return 1;
+  for (auto& c : M->kv) { c.k.clear(); c.v.clear(); c.cap = 0; }
+  M->B = B; M->len = 0;
+  for (auto& c : M->kv) kv_append(c, B, M->KV, M->hd, 0, len + 1);
+  M->len = len;
+  return 0;
+}
 ORC void orc_model_cache_clear(void* h) { Model* M = (Model*)h; M->len = 0; }
 ORC uint32_t orc_model_cache_len(void* h) { return ((Model*)h)->len; }
 ORC uint32_t orc_model_cache_capacity(void* h) { return ((Model*)h)->kv.empty() ? 0 : ((Model*)h)->kv[0].cap; }

@@ -63,6 +63,9 @@ _PROTOS = {
     "ruai_qweight_info": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
     "ruai_matmul_q": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32]),
     "ruai_matmul_q_static": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32]),
+    "ruai_matmul_q_stream": (C.c_int, [vp, vp, vp, vp, u32, u32]),
+    "ruai_ctx_set_wait_limit": (C.c_int, [vp, C.c_uint]),
+    "ruai_ctx_inject_barrier_skew": (C.c_int, [vp, C.c_uint]),
     "ruai_dequant_int4": (C.c_int, [vp, vp, vp]),
     "ruai_dequant_int4_ref": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
     "ruai_llama_create": (C.c_int, [vp, C.POINTER(LlamaConfig), C.POINTER(TP), C.POINTER(vp)]),
@@ -71,6 +74,8 @@ _PROTOS = {
     "ruai_model_load_synthetic": (C.c_int, [vp, u64, u32, u32]),
     "ruai_model_set_f32": (C.c_int, [vp, u64, vp, C.c_size_t]),
     "ruai_model_quantize": (C.c_int, [vp, u32, u32]),
+    "ruai_model_set_quantized": (C.c_int, [vp, u64, vp, vp, u32, u32]),
+    "ruai_model_get_f32": (C.c_int, [vp, u64, vp, C.c_size_t]),
     "ruai_model_get_linear": (C.c_int, [vp, u64, vp, vp]),
     "ruai_model_forward_cached": (C.c_int, [vp, vp, u32, u32, vp, C.c_int]),
     "ruai_model_cache_clear": (C.c_int, [vp]),

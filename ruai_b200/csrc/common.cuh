@@ -35,8 +35,13 @@ struct ruai_ctx {
   unsigned force_splits = 0;  // debug: overrides the split-K choice of the tensor-core GEMVs (0 = automatic)
   unsigned long long* trace = nullptr;  // debug: per-launch [first entry, first past the dependency wait, last exit] in ns
   unsigned trace_slots = 0, trace_seq = 0;
-  int* status = nullptr;  // device word: 0 ok, 3 = a bounded wait inside a kernel ran out
+  int* status = nullptr;  // device word: 0 ok, 3 / 4 = a bounded wait inside a kernel ran out (mbarrier / grid barrier), 5 = cache position out of range
   unsigned long long launches = 0;
+  // persistent kernels (pstep.cu)
+  unsigned spin_limit = 1u << 20;  // polls of a bounded device-side wait (about a second)
+  unsigned barrier_skew = 0;       // failure injection: extra arrivals (in grids) the next persistent launch will wait for in vain
+  unsigned* ps_sync = nullptr;     // [0] grid barrier counter, [1] abort flag, [2..3] poison, for ruai_matmul_q_stream
+  unsigned ps_bar_base = 0;
 };
 
 enum QLayout : uint32_t {
@@ -44,8 +49,10 @@ enum QLayout : uint32_t {
   QL_REFERENCE = 1 // the reference's row-major buffers, for shapes the chunk layout does not cover
 };
 
+struct ruai_sweight;
 struct ruai_qweight {
   ruai_ctx* ctx = nullptr;
+  ruai_sweight* stream = nullptr;  // tile-stream copy, built on the first ruai_matmul_q_stream
   uint32_t k = 0, n = 0, bits = 0, group = 0;
   QLayout layout = QL_CHUNK16;
   uint32_t chunks = 0;      // 16-byte chunks per column

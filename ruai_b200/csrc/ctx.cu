@@ -75,6 +75,7 @@ RUAI_API int ruai_ctx_destroy(ruai_ctx* c) {
   cudaFree(c->partial);
   cudaFree(c->counters);
   cudaFree(c->status);
+  cudaFree(c->ps_sync);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->stream);
@@ -110,6 +111,11 @@ int ruai_ctx_check_status(ruai_ctx* c) {
   RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
   if (st == 0) return RUAI_OK;
   cudaMemsetAsync(c->status, 0, sizeof(int), c->stream);
+  if (c->ps_sync) {  // a persistent launch that gave up leaves its barrier count undefined: start over
+    cudaMemsetAsync(c->ps_sync, 0, 64, c->stream);
+    c->ps_bar_base = 0;
+  }
+  if (st == 5) return ruai_fail(c, RUAI_ERR_SHAPE, "a decode step was launched at a position beyond the cache capacity; nothing was written there");
   return ruai_fail(c, RUAI_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (status %d); results of that launch are invalid", st);
 }
 

@@ -18,6 +18,7 @@
 #include <vector>
 
 #include "decode_ops.cuh"
+#include "pstep.cuh"
 #include "tp.cuh"
 
 namespace {
@@ -74,6 +75,7 @@ struct RefQ {
 
 struct Lin {
   ruai_qweight* w = nullptr;
+  ruai_sweight sw;  // the same weight in the tile-stream layout of the persistent decode kernel (Llama only)
   DevBuf bias;
   double bytes() const { return w ? (double)w->k * w->n * w->bits / 8.0 + (double)w->scale_bytes + (double)bias.bytes : 0.0; }
 };
@@ -82,6 +84,15 @@ struct Layer {
   DevBuf n1w, n1b, n2w, n2b;
   Lin qkv, o, up, down;  // up = gate/up interleaved (Llama) or c_fc (GPT-2)
   DevBuf kc, vc;         // KV cache [B, KVl, cap, hd]
+};
+
+// Device state of the persistent decode step (pstep.cu).
+struct PStep {
+  bool tried = false, usable = false;
+  DevBuf layers, x, ss, acc, poison, att_part, arg_slots, sync;  // sync: [0] barrier counter, [1] abort flag
+  unsigned bar_base = 0;
+  uint32_t table_cap = 0, table_B = 0, splits = 0, att_rows = 0;
+  size_t acc_elems = 0;
 };
 
 }  // namespace
@@ -102,6 +113,7 @@ struct ruai_model {
   bool quantized = false;
   uint32_t bits = 0, group = 0;
   std::map<uint64_t, DevBuf> staged;  // f32 tensors set before quantizing
+  std::map<uint64_t, RefQ*> staged_q; // Linears that arrived already quantized (a checkpoint in the reference's format)
   // cache state
   uint32_t B = 0, len = 0, cap = 0;
   // device state
@@ -110,6 +122,8 @@ struct ruai_model {
   // decode graph
   cudaGraphExec_t graph = nullptr;
   uint32_t graph_B = 0, graph_cap = 0, graph_launches = 0;
+  bool len_dirty = true;  // the device copy of `len` may differ from the host's
+  PStep ps;
   ruai_tp_state tp;
 };
 
@@ -199,6 +213,30 @@ int quantize_ref(ruai_model* m, const float* w, uint32_t k, uint32_t n, uint32_t
   return ruai_quantize_int4(c, w, k, n, group, out->q.as<int8_t>(), out->scale.as<float>());
 }
 
+// The reference-layout quantized form of Linear `id`: the buffers a checkpoint supplied, or the quantizer run
+// over the f32 tensor that was set.
+int obtain_ref(ruai_model* m, uint64_t id, uint32_t k, uint32_t n, uint32_t bits, uint32_t group, RefQ* out) {
+  auto it = m->staged_q.find(id);
+  if (it != m->staged_q.end()) {
+    RefQ* r = it->second;
+    const uint32_t g = bits == 4 ? group : 0;
+    if (r->k != k || r->n != n || r->bits != bits || r->group != g)
+      return model_fail(m, RUAI_ERR_SHAPE, "quantized tensor 0x%llx is int%u [%u, %u] group %u; the model needs int%u [%u, %u] group %u",
+                        (unsigned long long)id, r->bits, r->k, r->n, r->group, bits, k, n, g);
+    out->k = k; out->n = n; out->bits = bits; out->group = g;
+    out->q = r->q; out->scale = r->scale;
+    r->q = DevBuf(); r->scale = DevBuf();
+    delete r;
+    m->staged_q.erase(it);
+    return RUAI_OK;
+  }
+  DevBuf* t = nullptr;
+  RUAI_TRY(staged_get(m, id, &t));
+  RUAI_TRY(quantize_ref(m, t->as<float>(), k, n, bits, group, out));
+  staged_drop(m, id);
+  return RUAI_OK;
+}
+
 // One part of a fused local weight: columns [c0, c0+cols) and rows [r0, r0+rows) of a
 // reference Linear, placed at column dst_c0 with column stride dst_cs.
 struct Part { const RefQ* src; uint32_t r0, rows, c0, cols, dst_c0, dst_cs; };
@@ -226,6 +264,7 @@ int build_lin(ruai_model* m, const std::vector<Part>& parts, uint32_t n_local, L
     rc = bits == 8 ? ruai_repack_int8(c, q.as<int8_t>(), s.as<float>(), rows, n_local, &out->w)
                    : ruai_repack_int4(c, q.as<int8_t>(), s.as<float>(), rows, n_local, group, &out->w);
   }
+  if (rc == RUAI_OK && m->llama && ruai_sweight_supported(out->w)) rc = ruai_sweight_create(c, out->w, &out->sw);
   cudaStreamSynchronize(c->stream);
   q.release();
   s.release();
@@ -245,19 +284,19 @@ int quantize_layer(ruai_model* m, uint32_t l, uint32_t bits, uint32_t group) {
   if (m->llama) {
     RefQ q, k, v, o, g, u, dn;
     const uint32_t nq = m->H * hd, nkv = m->KV * hd, nql = m->Hl * hd, nkvl = m->KVl * hd, f = m->ffn, fl = m->fl;
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_Q), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), d, nq, bits, group, &q)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_Q));
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_K), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), d, nkv, bits, group, &k)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_K));
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_V), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), d, nkv, bits, group, &v)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_V));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_Q), d, nq, bits, group, &q));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_K), d, nkv, bits, group, &k));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_V), d, nkv, bits, group, &v));
     RUAI_TRY(build_lin(m, {{&q, 0, d, r * nql, nql, 0, 1}, {&k, 0, d, r * nkvl, nkvl, nql, 1}, {&v, 0, d, r * nkvl, nkvl, nql + nkvl, 1}}, nql + 2 * nkvl, &Ly.qkv));
     q.q.release(); k.q.release(); v.q.release(); q.scale.release(); k.scale.release(); v.scale.release();
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_O), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), nq, d, bits, group, &o)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_O));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_O), nq, d, bits, group, &o));
     RUAI_TRY(build_lin(m, {{&o, r * nql, nql, 0, d, 0, 1}}, d, &Ly.o));
     o.q.release(); o.scale.release();
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_GATE), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), d, f, bits, group, &g)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_GATE));
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_UP), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), d, f, bits, group, &u)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_UP));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_GATE), d, f, bits, group, &g));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_UP), d, f, bits, group, &u));
     RUAI_TRY(build_lin(m, {{&g, 0, d, r * fl, fl, 0, 2}, {&u, 0, d, r * fl, fl, 1, 2}}, 2 * fl, &Ly.up));
     g.q.release(); u.q.release(); g.scale.release(); u.scale.release();
-    RUAI_TRY(staged_get(m, ruai_layer_tensor(l, RUAI_T_DOWN), &t)); RUAI_TRY(quantize_ref(m, t->as<float>(), f, d, bits, group, &dn)); staged_drop(m, ruai_layer_tensor(l, RUAI_T_DOWN));
+    RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, RUAI_T_DOWN), f, d, bits, group, &dn));
     RUAI_TRY(build_lin(m, {{&dn, r * fl, fl, 0, d, 0, 1}}, d, &Ly.down));
   } else {
     const uint32_t f = m->ffn;
@@ -266,9 +305,7 @@ int quantize_layer(ruai_model* m, uint32_t l, uint32_t bits, uint32_t group) {
                            {RUAI_T_CFC, RUAI_T_CFC_B, d, f, &Ly.up}, {RUAI_T_MPROJ, RUAI_T_MPROJ_B, f, d, &Ly.down}};
     for (const Item& it : items) {
       RefQ q;
-      RUAI_TRY(staged_get(m, ruai_layer_tensor(l, it.kind), &t));
-      RUAI_TRY(quantize_ref(m, t->as<float>(), it.k, it.n, bits, group, &q));
-      staged_drop(m, ruai_layer_tensor(l, it.kind));
+      RUAI_TRY(obtain_ref(m, ruai_layer_tensor(l, it.kind), it.k, it.n, bits, group, &q));
       RUAI_TRY(build_lin(m, {{&q, 0, it.k, 0, it.n, 0, 1}}, it.n, it.dst));
       RUAI_TRY(staged_get(m, ruai_layer_tensor(l, it.bias_kind), &t));
       RUAI_TRY(copy_vec(m, &it.dst->bias, t, 0, it.n));
@@ -295,7 +332,10 @@ int quantize_head(ruai_model* m) {
   DevBuf* t = nullptr;
   RUAI_TRY(staged_get(m, RUAI_T_EMBED, &t));
   RefQ h;
-  if (m->llama && !m->tied) {
+  if (m->staged_q.count(RUAI_T_LMHEAD)) {  // `lm_head.weight_int8` of a quantized checkpoint (tied or not)
+    RUAI_TRY(obtain_ref(m, RUAI_T_LMHEAD, m->d, m->V, 8, 0, &h));
+    staged_drop(m, RUAI_T_LMHEAD);
+  } else if (m->llama && !m->tied) {
     DevBuf* lh = nullptr;
     RUAI_TRY(staged_get(m, RUAI_T_LMHEAD, &lh));
     RUAI_TRY(quantize_ref(m, lh->as<float>(), m->d, m->V, 8, 0, &h));
@@ -579,14 +619,123 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
   return RUAI_OK;
 }
 
+int pstep_reset(ruai_model* m);
+
 int check_device_status(ruai_model* m) {
   int32_t e = 0;
   RUAI_CUDA(m->ctx, cudaMemcpyAsync(&e, m->d_err.p, sizeof e, cudaMemcpyDeviceToHost, m->ctx->stream));
   RUAI_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
-  if (e == 0) return ruai_ctx_check_status(m->ctx);
+  if (e == 0) {
+    const int rc = ruai_ctx_check_status(m->ctx);
+    if (rc != RUAI_OK) pstep_reset(m);  // a step that gave up leaves its accumulators and barrier count undefined
+    return rc;
+  }
   cudaMemsetAsync(m->d_err.p, 0, sizeof(int32_t), m->ctx->stream);
   if (e == 1) return model_fail(m, RUAI_ERR_ARG, "token id out of range [0, %u)", m->V);
   return model_fail(m, RUAI_ERR_TIMEOUT, "tensor-parallel exchange timed out waiting for a peer (status %d)", e);
+}
+
+// ---- the persistent decode step (pstep.cu) ---------------------------------------------------
+
+// Whether single-token steps of this model for B sequences run as the one persistent kernel.
+bool pstep_eligible(ruai_model* m, uint32_t B) {
+  PStep& S = m->ps;
+  if (!S.tried) {
+    S.tried = true;
+    const char* env = getenv("RUAI_B200_PSTEP");
+    bool ok = !(env && env[0] == '0') && m->llama && m->world == 1 && m->quantized && m->L >= 1 && m->L <= (uint32_t)ps::kMaxLayers;
+    ok = ok && m->d % 32 == 0 && m->hd % 4 == 0 && m->hd <= 256 && m->KVl > 0;
+    const uint32_t rep = m->KVl ? m->Hl / m->KVl : 0;
+    ok = ok && rep >= 1 && rep <= 8 && rep * (m->hd / 4) <= 448u && m->fl % 4 == 0;
+    for (Layer& L : m->layers)
+      for (Lin* l : {&L.qkv, &L.o, &L.up, &L.down}) ok = ok && l->sw.data != nullptr;
+    ok = ok && m->head.sw.data != nullptr;
+    ok = ok && ruai_pstep_grid(m->ctx) > 0;
+    S.usable = ok;
+  }
+  return S.usable && B >= 1 && B <= (uint32_t)ps::kMaxRows;
+}
+
+int pstep_reset(ruai_model* m) {
+  PStep& S = m->ps;
+  ruai_ctx* c = m->ctx;
+  if (!S.acc.p) return RUAI_OK;
+  RUAI_CUDA(c, cudaMemsetAsync(S.acc.p, 0, S.acc.bytes, c->stream));
+  RUAI_CUDA(c, cudaMemsetAsync(S.poison.p, 0, S.poison.bytes, c->stream));
+  RUAI_CUDA(c, cudaMemsetAsync(S.sync.p, 0, S.sync.bytes, c->stream));
+  S.bar_base = 0;
+  return RUAI_OK;
+}
+
+int pstep_run(ruai_model* m, uint32_t B) {
+  PStep& S = m->ps;
+  ruai_ctx* c = m->ctx;
+  const uint32_t MR = ps::kMaxRows, d = m->d, hd = m->hd, nq = m->Hl * hd, nkv = m->KVl * hd, nqkv = nq + 2 * nkv, rep = m->Hl / m->KVl;
+  const int grid = ruai_pstep_grid(c);
+  if (!S.acc.p) {
+    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+    S.acc_elems = (size_t)MR * ((size_t)nqkv + d + 2 * (size_t)m->fl + d + m->Vl);
+    RUAI_TRY(S.acc.alloc(c, S.acc_elems * sizeof(long long)));
+    RUAI_TRY(S.poison.alloc(c, 5 * MR * sizeof(int)));
+    RUAI_TRY(S.sync.alloc(c, 64));
+    RUAI_TRY(S.x.alloc(c, 2 * (size_t)MR * d * sizeof(float)));
+    RUAI_TRY(S.ss.alloc(c, 3 * (size_t)MR * (d / 32) * sizeof(float)));
+    RUAI_TRY(S.arg_slots.alloc(c, (size_t)grid * MR * sizeof(int2)));
+    RUAI_TRY(S.layers.alloc(c, (size_t)m->L * sizeof(ps::LayerPtrs)));
+    RUAI_TRY(pstep_reset(m));
+  }
+  // key splits: one (sequence, KV head, split) item per CTA where the cache is long enough to share out
+  const uint32_t splits = std::max(1u, std::min(32u, (uint32_t)grid / (B * m->KVl)));
+  const size_t att_floats = (size_t)B * m->KVl * splits * rep * (hd + 4);
+  if (att_floats * sizeof(float) > S.att_part.bytes) {
+    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+    RUAI_TRY(S.att_part.alloc(c, att_floats * sizeof(float)));
+  }
+  if (S.table_cap != m->cap || S.table_B != B) {  // the cache buffers moved (growth) or were made anew
+    std::vector<ps::LayerPtrs> t(m->L);
+    for (uint32_t l = 0; l < m->L; ++l) {
+      Layer& Y = m->layers[l];
+      t[l].w_qkv = Y.qkv.sw.data; t[l].w_o = Y.o.sw.data; t[l].w_gu = Y.up.sw.data; t[l].w_dn = Y.down.sw.data;
+      t[l].s_qkv = Y.qkv.sw.colscale; t[l].s_o = Y.o.sw.colscale; t[l].s_gu = Y.up.sw.colscale; t[l].s_dn = Y.down.sw.colscale;
+      t[l].n1 = Y.n1w.as<float>(); t[l].n2 = Y.n2w.as<float>();
+      t[l].kc = Y.kc.as<float>(); t[l].vc = Y.vc.as<float>();
+    }
+    RUAI_CUDA(c, cudaMemcpyAsync(S.layers.p, t.data(), t.size() * sizeof(ps::LayerPtrs), cudaMemcpyHostToDevice, c->stream));
+    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));  // `t` is a stack object
+    S.table_cap = m->cap; S.table_B = B;
+  }
+  ps::StepParams P{};
+  P.m = B; P.L = m->L; P.d = d; P.nq = nq; P.nkv = nkv; P.hd = hd; P.Hl = m->Hl; P.KVl = m->KVl; P.rep = rep; P.fl = m->fl; P.Vl = m->Vl; P.V = m->V;
+  P.cap = m->cap; P.bits = m->bits; P.splits = splits; P.keys_per_stage = (20480u / 2u) / (hd * 4u); P.col_offset = m->rank * m->Vl;
+  P.eps = m->eps; P.attn_scale = 1.0f / sqrtf((float)hd);
+  auto geom = [](const ruai_sweight& w) { return ps::Geom{w.ntiles, w.nblk, w.n, w.k}; };
+  P.qkv = geom(m->layers[0].qkv.sw); P.o = geom(m->layers[0].o.sw); P.gu = geom(m->layers[0].up.sw); P.dn = geom(m->layers[0].down.sw);
+  P.head = geom(m->head.sw);
+  P.layers = S.layers.as<ps::LayerPtrs>();
+  P.w_head = m->head.sw.data; P.s_head = m->head.sw.colscale;
+  P.final_norm = m->final_w.as<float>(); P.embed = m->embed.as<float>(); P.rope = m->rope_table.as<float2>();
+  P.ids = m->d_ids.as<int32_t>(); P.len = m->d_len.as<int32_t>(); P.err = m->d_err.as<int>();
+  P.x0 = S.x.as<float>(); P.x1 = P.x0 + (size_t)MR * d;
+  P.ss_a = S.ss.as<float>(); P.ss_b = P.ss_a + (size_t)MR * (d / 32); P.ss_c = P.ss_b + (size_t)MR * (d / 32);
+  long long* a = S.acc.as<long long>();
+  P.acc_qkv = a; a += (size_t)MR * nqkv;
+  P.acc_o = a; a += (size_t)MR * d;
+  P.acc_gu = a; a += (size_t)MR * 2 * m->fl;
+  P.acc_dn = a; a += (size_t)MR * d;
+  P.acc_logits = a;
+  P.poison = S.poison.as<int>();
+  P.att_part = S.att_part.as<float>();
+  P.logits = m->logits.as<float>();
+  P.arg_slots = S.arg_slots.as<int2>();
+  P.bar = S.sync.as<unsigned>(); P.bar_base = S.bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status; P.abort_flag = S.sync.as<int>() + 1;
+  P.spin_limit = c->spin_limit;
+  P.want_argmax = 1;
+  c->barrier_skew = 0;
+  RUAI_TRY(ruai_pstep_launch(c, P));
+  S.bar_base += (5u * m->L + 2u) * (unsigned)grid;  // one arrival per CTA at each of the step's barriers
+  m->graph_launches = 1;
+  m->len += 1;
+  return RUAI_OK;
 }
 
 int prepare_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions) {
@@ -656,11 +805,14 @@ RUAI_API int ruai_model_destroy(ruai_model* m) {
   drop_graph(m);
   ruai_tp_destroy(&m->tp);
   for (auto& kv : m->staged) kv.second.release();
+  for (auto& kv : m->staged_q) delete kv.second;
   for (Layer& L : m->layers) {
-    for (Lin* l : {&L.qkv, &L.o, &L.up, &L.down}) { if (l->w) ruai_qweight_free(l->w); l->bias.release(); }
+    for (Lin* l : {&L.qkv, &L.o, &L.up, &L.down}) { if (l->w) ruai_qweight_free(l->w); ruai_sweight_free(&l->sw); l->bias.release(); }
     for (DevBuf* b : {&L.n1w, &L.n1b, &L.n2w, &L.n2b, &L.kc, &L.vc}) b->release();
   }
   if (m->head.w) ruai_qweight_free(m->head.w);
+  ruai_sweight_free(&m->head.sw);
+  for (DevBuf* b : {&m->ps.layers, &m->ps.x, &m->ps.ss, &m->ps.acc, &m->ps.poison, &m->ps.att_part, &m->ps.arg_slots, &m->ps.sync}) b->release();
   for (DevBuf* b : {&m->embed, &m->wpe, &m->final_w, &m->final_b, &m->rope_table, &m->d_ids, &m->d_len, &m->d_err, &m->x, &m->xn, &m->qkv, &m->att,
                     &m->hbuf, &m->xl, &m->logits, &m->attn_scratch, &m->attn_counters, &m->sumsq, &m->arg_slots, &m->arg_counter})
     b->release();
@@ -678,6 +830,65 @@ RUAI_API int ruai_model_set_f32(ruai_model* m, uint64_t id, const float* data, s
   DevBuf* b;
   RUAI_TRY(stage_alloc(m, id, count, &b));
   RUAI_CUDA(m->ctx, cudaMemcpyAsync(b->p, data, count * sizeof(float), cudaMemcpyHostToDevice, m->ctx->stream));
+  RUAI_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_model_set_quantized(ruai_model* m, uint64_t id, const int8_t* q_host, const float* scale_host, uint32_t bits, uint32_t group) {
+  if (!m || !q_host || !scale_host) return ruai_fail(m ? m->ctx : nullptr, RUAI_ERR_ARG, "ruai_model_set_quantized: NULL argument");
+  if (m->quantized) return model_fail(m, RUAI_ERR_UNSUPPORTED, "the model is already quantized");
+  if (m->world > 1) return model_fail(m, RUAI_ERR_UNSUPPORTED, "loading quantized tensors into a sharded model is not implemented");
+  TensorShape s;
+  const bool is_linear = id == RUAI_T_LMHEAD || (id < (uint64_t)m->L * 16 && (m->llama ? (id % 16) <= RUAI_T_DOWN : ((id % 16) >= RUAI_T_CATTN && (id % 16) <= RUAI_T_MPROJ)));
+  if (id == RUAI_T_LMHEAD) s = {m->d, m->V};
+  else if (!is_linear || !tensor_shape(m, id, &s)) return model_fail(m, RUAI_ERR_ARG, "tensor id 0x%llx is not a Linear weight of this model", (unsigned long long)id);
+  if (bits != 8 && bits != 4) return model_fail(m, RUAI_ERR_ARG, "bits must be 8 or 4, got %u", bits);
+  const uint32_t k = (uint32_t)s.rows, n = (uint32_t)s.cols;
+  if (bits == 4 && !(group >= 2 && group % 2 == 0 && k % group == 0))
+    return model_fail(m, RUAI_ERR_SHAPE, "int4 group %u must be even and divide in_features %u", group, k);
+  DeviceGuard g(m->ctx->ordinal);
+  RefQ* r = new RefQ();
+  r->k = k; r->n = n; r->bits = bits; r->group = bits == 4 ? group : 0;
+  const size_t qb = (size_t)r->q_rows() * n, sb = (size_t)r->s_rows() * n * sizeof(float);
+  int rc = r->q.alloc(m->ctx, qb);
+  if (rc == RUAI_OK) rc = r->scale.alloc(m->ctx, sb);
+  if (rc != RUAI_OK) { delete r; return rc; }
+  cudaError_t e = cudaMemcpyAsync(r->q.p, q_host, qb, cudaMemcpyHostToDevice, m->ctx->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(r->scale.p, scale_host, sb, cudaMemcpyHostToDevice, m->ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(m->ctx->stream);
+  if (e != cudaSuccess) { delete r; return model_fail(m, RUAI_ERR_CUDA, "ruai_model_set_quantized: %s", cudaGetErrorString(e)); }
+  auto it = m->staged_q.find(id);
+  if (it != m->staged_q.end()) { delete it->second; m->staged_q.erase(it); }
+  m->staged_q[id] = r;
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_model_get_f32(ruai_model* m, uint64_t id, float* out_host, size_t count) {
+  if (!m || !out_host) return ruai_fail(m ? m->ctx : nullptr, RUAI_ERR_ARG, "ruai_model_get_f32: NULL argument");
+  if (!m->quantized) return model_fail(m, RUAI_ERR_UNSUPPORTED, "the model is not loaded");
+  const DevBuf* b = nullptr;
+  if (id == RUAI_T_EMBED) b = &m->embed;
+  else if (id == RUAI_T_WPE && !m->llama) b = &m->wpe;
+  else if (id == RUAI_TN_FINAL_NORM) b = &m->final_w;
+  else if (id == RUAI_TN_FINAL_NORM_B && !m->llama) b = &m->final_b;
+  else if (id >= RUAI_TN_LAYER_NORM1 && id < RUAI_TN_LAYER_NORM1 + m->L) b = &m->layers[id - RUAI_TN_LAYER_NORM1].n1w;
+  else if (id >= RUAI_TN_LAYER_NORM2 && id < RUAI_TN_LAYER_NORM2 + m->L) b = &m->layers[id - RUAI_TN_LAYER_NORM2].n2w;
+  else if (!m->llama && id >= RUAI_TN_LAYER_NORM1B && id < RUAI_TN_LAYER_NORM1B + m->L) b = &m->layers[id - RUAI_TN_LAYER_NORM1B].n1b;
+  else if (!m->llama && id >= RUAI_TN_LAYER_NORM2B && id < RUAI_TN_LAYER_NORM2B + m->L) b = &m->layers[id - RUAI_TN_LAYER_NORM2B].n2b;
+  else if (!m->llama && id < (uint64_t)m->L * 16) {
+    Layer& Y = m->layers[id / 16];
+    switch ((uint32_t)(id % 16)) {
+      case RUAI_T_CATTN_B: b = &Y.qkv.bias; break;
+      case RUAI_T_CPROJ_B: b = &Y.o.bias; break;
+      case RUAI_T_CFC_B: b = &Y.up.bias; break;
+      case RUAI_T_MPROJ_B: b = &Y.down.bias; break;
+      default: break;
+    }
+  }
+  if (!b || !b->p) return model_fail(m, RUAI_ERR_ARG, "no f32 tensor with id 0x%llx in this model", (unsigned long long)id);
+  if (b->bytes != count * sizeof(float)) return model_fail(m, RUAI_ERR_SHAPE, "tensor 0x%llx has %zu elements, got %zu", (unsigned long long)id, b->bytes / sizeof(float), count);
+  DeviceGuard g(m->ctx->ordinal);
+  RUAI_CUDA(m->ctx, cudaMemcpyAsync(out_host, b->p, b->bytes, cudaMemcpyDeviceToHost, m->ctx->stream));
   RUAI_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
   return RUAI_OK;
 }
@@ -767,7 +978,8 @@ RUAI_API int ruai_model_forward_cached(ruai_model* m, const int32_t* ids, uint32
   RUAI_CUDA(c, cudaMemcpyAsync(m->d_ids.p, ids, (size_t)B * T * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
   const int32_t len = (int32_t)m->len;
   RUAI_CUDA(c, cudaMemcpyAsync(m->d_len.p, &len, sizeof len, cudaMemcpyHostToDevice, c->stream));
-  if (T == 1) RUAI_TRY(run_decode_graph(m, B));  // single-token steps replay the captured graph
+  m->len_dirty = false;
+  if (T == 1) RUAI_TRY(run_decode_graph(m, B));  // single-token steps: the persistent kernel, or the captured graph
   else {
     RUAI_TRY(issue_step(m, B, T, all_positions != 0, false));
     m->len += T;
@@ -783,6 +995,7 @@ RUAI_API int ruai_model_forward_cached(ruai_model* m, const int32_t* ids, uint32
 RUAI_API int ruai_model_cache_clear(ruai_model* m) {
   if (!m) return ruai_fail(nullptr, RUAI_ERR_ARG, "model is NULL");
   m->len = 0;  // KvCache::clear keeps the buffers (transformer.rs:160-165)
+  m->len_dirty = true;
   return RUAI_OK;
 }
 
@@ -810,12 +1023,14 @@ RUAI_API int ruai_model_cache_assume(ruai_model* m, uint32_t B, uint32_t len) {
   const int32_t l = (int32_t)len;
   RUAI_CUDA(m->ctx, cudaMemcpyAsync(m->d_len.p, &l, sizeof l, cudaMemcpyHostToDevice, m->ctx->stream));
   RUAI_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  m->len_dirty = false;
   return RUAI_OK;
 }
 
 // Replays (capturing first if needed) the graph of one greedy decode step for batch B.
 static int run_decode_graph(ruai_model* m, uint32_t B) {
   ruai_ctx* c = m->ctx;
+  if (pstep_eligible(m, B)) return pstep_run(m, B);
   if (!m->graph || m->graph_B != B || m->graph_cap != m->cap) {
     drop_graph(m);
     // split-K partials of one GEMV never exceed (3 * SMs + column tiles) * 256 floats per row;
@@ -849,6 +1064,12 @@ RUAI_API int ruai_model_decode_step(ruai_model* m, const int32_t* ids_dev, uint3
   DeviceGuard g(c->ordinal);
   RUAI_TRY(prepare_step(m, B, 1, false));
   if (ids_dev) RUAI_CUDA(c, cudaMemcpyAsync(m->d_ids.p, ids_dev, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, c->stream));
+  if (m->len_dirty) {  // the host's position is the authority: a cleared or re-assumed cache has not reached the device yet
+    const int32_t len = (int32_t)m->len;
+    RUAI_CUDA(c, cudaMemcpyAsync(m->d_len.p, &len, sizeof len, cudaMemcpyHostToDevice, c->stream));
+    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+    m->len_dirty = false;
+  }
   RUAI_TRY(run_decode_graph(m, B));
   if (next_host) {
     RUAI_CUDA(c, cudaMemcpyAsync(next_host, m->d_ids.p, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
@@ -933,11 +1154,13 @@ RUAI_API int ruai_model_generate(ruai_model* m, const int32_t* prompt, uint32_t 
   const uint32_t max_len = m->max_pos;
   std::vector<int32_t> ids(prompt, prompt + T);
   m->len = 0;
+  m->len_dirty = true;
   std::vector<int32_t> pending(ids.begin() + (ids.size() > max_len ? ids.size() - max_len : 0), ids.end());
   bool on_device = false;  // d_ids already holds the next token (written by the step's argmax)
   for (uint32_t s = 0; s < n_new; ++s) {
     if (m->len + pending.size() > max_len) {
       m->len = 0;
+      m->len_dirty = true;
       pending.assign(ids.end() - max_len, ids.end());
       on_device = false;
     }
@@ -956,6 +1179,7 @@ RUAI_API int ruai_model_generate(ruai_model* m, const int32_t* prompt, uint32_t 
       RUAI_CUDA(c, cudaMemcpyAsync(m->d_ids.p, pending.data(), (size_t)Tn * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
       const int32_t len = (int32_t)m->len;
       RUAI_CUDA(c, cudaMemcpyAsync(m->d_len.p, &len, sizeof len, cudaMemcpyHostToDevice, c->stream));
+      m->len_dirty = false;
       RUAI_TRY(issue_step(m, 1, Tn, false, true));
       m->len += Tn;
       RUAI_CUDA(c, cudaMemcpyAsync(&next, m->d_ids.p, sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));

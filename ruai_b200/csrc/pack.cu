@@ -13,6 +13,7 @@
 // Scales are copied unchanged.  Shapes the chunk layout does not cover (int4 with a
 // group other than 32) keep the reference layout.
 #include "common.cuh"
+#include "pstep.cuh"
 
 namespace {
 
@@ -174,6 +175,7 @@ RUAI_API int ruai_qweight_free(ruai_qweight* w) {
   if (!w) return RUAI_OK;
   DeviceGuard g(w->ctx->ordinal);
   cudaStreamSynchronize(w->ctx->stream);
+  if (w->stream) { ruai_sweight_free(w->stream); delete w->stream; }
   cudaFree(w->data);
   cudaFree(w->scale);
   delete w;

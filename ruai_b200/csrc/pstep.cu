@@ -1,0 +1,1294 @@
+// The persistent decode step: ONE cooperative kernel per generated token.
+//
+// It replaces, for Llama-shaped models and up to two sequences, the chain of launches that
+// Llama::run (src/nn/modules/llama.rs:441-463; DecoderLayer::forward 306-309; Attention::forward
+// 248-277) becomes on a GPU: per layer q/k/v Linear, RoPE + KV append + attention, o_proj, gate/up
+// Linear + SwiGLU, down_proj, then the head and the greedy pick (generation.rs:6-8).  One CTA per SM
+// stays resident for the whole step and walks these as PHASES separated by a grid-wide barrier.
+//
+// What makes it fast is that the weights never stop streaming.  Every CTA owns, per phase, a contiguous
+// run of (128-column tile, block of k) units of the weight in the tile-stream layout (pstep.cuh).  One
+// producer thread walks the stage list of the WHOLE step and keeps a ring of 20 KB bulk copies
+// (cp.async.bulk + mbarrier) full; it is held back only by free ring slots, never by a phase boundary,
+// so while the CTAs meet at a barrier the next phase's weights (or the next layer's cached keys and
+// values) are already landing in shared memory.
+//
+// Arithmetic of a GEMV phase is that of gemv_tc.cu / gemv_tc8.cu: activations as block fixed point
+// (int4: three int8 digits per group of 32; int8: four digits per row of the CTA's window), exact
+// integer products on the tensor cores (tcgen05.mma kind::i8, accumulators in tensor memory), one f32
+// multiply-add per (scale group, column, row).  Four kinds of warps meet only at mbarriers:
+//   producer (1 thread)  : bulk copies into the ring;
+//   expanding (8 warps)  : int4 nibbles -> bytes into one of two A-operand buffers (int8 needs none: the
+//                          ring slot IS the operand);
+//   issuing (1 thread)   : one MMA per scale group (int4) or per 32 rows (int8), commits;
+//   draining (4 warps)   : sums out of tensor memory, scaled, accumulated in f32 per column.
+// A CTA's partial sums of a tile go to a 64-bit fixed-point accumulator in global memory with
+// red.add.u64: integer addition commutes, so the result is bit-identical from run to run whatever the
+// arrival order.  Everything non-linear happens when the NEXT phase loads its activations ("loaders"):
+// residual add, RMSNorm weight (the 1/rms factor is a per-row scalar and is applied one phase later,
+// from per-group sums of squares the loader leaves), SwiGLU, the merge of the attention key splits.
+//
+// Every wait is bounded (mbarrier waits, the grid barrier); a wait that runs out sets an abort flag that
+// the other CTAs see at their next wait, the kernel frees its tensor memory and returns, and the host
+// reports RUAI_ERR_TIMEOUT.
+#include <algorithm>
+
+#include "pipeline.cuh"
+#include "pstep.cuh"
+
+namespace ps {
+
+using namespace pipe;
+
+constexpr int kCols = 128;            // tile columns = MMA M = TMEM lanes
+constexpr int kStage4 = 8;            // int4 scale groups per ring stage
+constexpr int kStage8 = 5;            // int8 32-row blocks per ring stage
+constexpr uint32_t kSlotBytes = 20480;
+constexpr int kSlots = 6;
+constexpr uint32_t kABufBytes = kStage4 * 4096;
+constexpr int kWin = 128;             // window of the activation digits: groups (int4) / blocks (int8)
+constexpr uint32_t kBRec = 256;       // digit operand of one group: [2 k-halves][8 rows][16 bytes]
+constexpr int kThreads = 512;
+constexpr int kConsumers = 480;       // warps 1..15
+constexpr int kConverters = 448;      // warps 2..15
+constexpr int kConvWarps = 14;
+constexpr int kWarpIssuer = 1, kWarpConv0 = 2, kWarpDrain0 = 4, kWarpExpand0 = 8;
+constexpr int kLeaderTid = kWarpConv0 * 32;
+constexpr uint32_t kTmemCols = 512;
+
+constexpr size_t kOffSlots = 0;
+constexpr size_t kOffABuf = kOffSlots + (size_t)kSlots * kSlotBytes;
+constexpr size_t kOffBWin = kOffABuf + 2 * (size_t)kABufBytes;
+constexpr size_t kOffMeta = kOffBWin + (size_t)kWin * kBRec;
+constexpr size_t kOffLayers = kOffMeta + (size_t)kWin * kMaxRows * 8;
+
+enum { PH_GEMV = 0, PH_ATTN = 1, PH_FINAL = 2, PH_PICK = 3, PH_OUT = 4 };
+enum { LD_PLAIN = 0, LD_EMBED = 1, LD_RESID = 2, LD_ATTN = 3, LD_SWIGLU = 4 };
+
+struct PhaseDesc {
+  int type;
+  // GEMV
+  const uint8_t* w; const float* colscale;
+  uint32_t ntiles, nblk, n, k, bits;
+  int loader;
+  const float* norm_w;        // RMSNorm weight multiplied into the digits (NULL: none)
+  const float* x_in; float* x_out;
+  const long long* acc_in; const int* poison_in; uint32_t in_ld;
+  float* ss_out;              // [m][k/32] sums of squares of the x this loader builds
+  const float* ss_in; uint32_t ss_groups; float ss_dim;  // source of this phase's 1/rms factor
+  long long* acc_out; int* poison_out;
+  long long* zero0; uint32_t zero0_n; int* zero0_poison;
+  long long* zero1; uint32_t zero1_n; int* zero1_poison;
+  // ATTN
+  float* kc; float* vc;
+};
+
+struct Bars {
+  uint64_t full[kSlots], empty[kSlots];
+  uint64_t a_ready[2], mma_done[4], acc_free[4], seg_done[2], seg_free[2];
+  uint64_t fin;  // every MMA of the CTA has completed
+};
+
+struct Shared {
+  Bars b;
+  uint32_t tmem;
+  volatile int abort;
+  float rstd[kMaxRows];
+  float wmax[kMaxRows][kConvWarps];
+  float xscale[kMaxRows];
+  int2 arg[kMaxRows][16];
+};
+
+// ---- small device helpers --------------------------------------------------------------------
+
+// Named barrier over `count` threads (whole warps).  bar.sync is warp-aligned, so lanes that took a single-lane
+// branch just before meet the rest of their warp first.
+__device__ __forceinline__ void bar_sync(int id, int count) {
+  __syncwarp();
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void red_add_s64(long long* p, long long v) {
+  asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_inc(unsigned* p) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
+__device__ __forceinline__ float unfix(long long v) { return __ll2float_rn(v) * kUnfix; }
+__device__ __forceinline__ float silu_ref(float v) { return v * (1.0f / (1.0f + expf(-v))); }  // ops.rs:158-160
+__device__ __forceinline__ int32_t ordered_bits(float v) {  // f32::total_cmp order as a signed integer
+  int32_t i = __float_as_int(v);
+  return i ^ (int32_t)(((uint32_t)(i >> 31)) >> 1);
+}
+__device__ __forceinline__ bool finite_f(float v) { return fabsf(v) <= 3.402823466e38f; }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+// ---- the stage list of one CTA in one GEMV phase ----------------------------------------------
+
+struct Stage {
+  uint32_t tile, blk, cnt;  // cnt blocks of `tile` starting at block `blk`
+  uint32_t ws;              // window slot of the first block's digits
+  bool round_start;         // the digits of a new round have to be written before this stage's MMAs
+  bool seg_end;             // last stage of a run inside one tile (and one round): partial sums go out
+  uint32_t round_blk0, round_cnt;  // first block and number of blocks of the round (valid at round_start)
+};
+
+// Units are (tile, block) in tile-major order; CTA b owns units [U*b/G, U*(b+1)/G).  Digits of the
+// activations are kept for a window of kWin blocks: if the weight has at most kWin blocks of k the window
+// slot of a block is the block itself and the phase is one round; otherwise a round is kWin consecutive units.
+struct StageIter {
+  uint32_t u, u0, u1, nblk, smax, tile, blk, round_u0;
+  bool windowed, first;
+  __device__ void init(uint32_t ntiles, uint32_t nblk_, uint32_t smax_) {
+    const uint64_t units = (uint64_t)ntiles * nblk_;
+    u0 = (uint32_t)(units * blockIdx.x / gridDim.x);
+    u1 = (uint32_t)(units * (blockIdx.x + 1) / gridDim.x);
+    u = u0; nblk = nblk_; smax = smax_;
+    tile = u0 / nblk_; blk = u0 - tile * nblk_;
+    windowed = nblk_ > (uint32_t)kWin;
+    round_u0 = u0; first = true;
+  }
+  __device__ bool next(Stage& s) {
+    if (u >= u1) return false;
+    s.round_start = first;
+    first = false;
+    if (windowed && u - round_u0 >= (uint32_t)kWin) { round_u0 = u; s.round_start = true; }
+    uint32_t cnt = min(min(smax, nblk - blk), u1 - u);
+    uint32_t round_end = u1;
+    if (windowed) { round_end = min(u1, round_u0 + (uint32_t)kWin); cnt = min(cnt, round_end - u); }
+    s.tile = tile; s.blk = blk; s.cnt = cnt;
+    s.ws = windowed ? u - round_u0 : blk;
+    s.round_blk0 = windowed ? blk : (u0 % nblk);
+    s.round_cnt = windowed ? round_end - round_u0 : min(u1 - u0, nblk);
+    s.seg_end = (blk + cnt == nblk) || (u + cnt == round_end);
+    u += cnt; blk += cnt;
+    if (blk == nblk) { blk = 0; ++tile; }
+    return true;
+  }
+};
+
+// ---- key/value stages of the attention phase ----------------------------------------------------
+
+struct AttnPlan {
+  uint32_t n_items, S, KS, n_cached, per;
+  __device__ void init(uint32_t m, uint32_t KVl, uint32_t splits, uint32_t keys_per_stage, uint32_t len) {
+    S = splits; KS = keys_per_stage; n_items = m * KVl * splits; n_cached = len;
+    per = (len + splits - 1) / splits;
+  }
+  __device__ void range(uint32_t item, uint32_t& k0, uint32_t& k1) const {
+    const uint32_t split = item % S;
+    k0 = min(n_cached, split * per);
+    k1 = min(n_cached, k0 + per);
+  }
+  __device__ uint32_t stages(uint32_t item) const {
+    uint32_t k0, k1;
+    range(item, k0, k1);
+    return (k1 - k0 + KS - 1) / KS;
+  }
+};
+
+// ---- programs -------------------------------------------------------------------------------------
+
+struct StepProgram {
+  const StepParams& P;
+  const LayerPtrs* lay;  // shared-memory copy
+  __device__ uint32_t nphases() const { return 5u * P.L + 3u; }
+  __device__ void get(uint32_t p, PhaseDesc& D) const {
+    D = PhaseDesc();
+    const uint32_t MT = kMaxRows;
+    D.zero0 = nullptr; D.zero1 = nullptr; D.zero0_n = 0; D.zero1_n = 0;
+    if (p < 5u * P.L) {
+      const uint32_t l = p / 5u, kind = p - 5u * l;
+      const LayerPtrs& Y = lay[l];
+      D.bits = P.bits;
+      switch (kind) {
+        case 0:  // q/k/v Linear on RMSNorm(x); x = embedding (layer 0) or x + down_proj of the previous layer
+          D.type = PH_GEMV; D.w = Y.w_qkv; D.colscale = Y.s_qkv;
+          D.ntiles = P.qkv.ntiles; D.nblk = P.qkv.nblk; D.n = P.qkv.n; D.k = P.qkv.k;
+          D.loader = l == 0 ? LD_EMBED : LD_RESID; D.norm_w = Y.n1; D.x_in = P.x0; D.x_out = P.x1;
+          D.acc_in = P.acc_dn; D.poison_in = P.poison + 3 * MT; D.in_ld = P.d; D.ss_out = P.ss_a;
+          D.acc_out = P.acc_qkv; D.poison_out = P.poison + 0 * MT;
+          D.zero0 = P.acc_o; D.zero0_n = P.m * P.d; D.zero0_poison = P.poison + 1 * MT;
+          break;
+        case 1:  // RoPE, KV append, attention over the cache
+          D.type = PH_ATTN; D.kc = Y.kc; D.vc = Y.vc;
+          D.acc_in = P.acc_qkv; D.poison_in = P.poison + 0 * MT; D.in_ld = P.qkv.n;
+          D.ss_in = P.ss_a; D.ss_groups = P.d / 32; D.ss_dim = (float)P.d;
+          D.zero0 = P.acc_gu; D.zero0_n = P.m * P.gu.n; D.zero0_poison = P.poison + 2 * MT;
+          if (l == 0) { D.zero1 = P.acc_logits; D.zero1_n = P.m * P.Vl; D.zero1_poison = P.poison + 4 * MT; }
+          break;
+        case 2:  // o_proj on the merged attention output
+          D.type = PH_GEMV; D.w = Y.w_o; D.colscale = Y.s_o;
+          D.ntiles = P.o.ntiles; D.nblk = P.o.nblk; D.n = P.o.n; D.k = P.o.k;
+          D.loader = LD_ATTN; D.in_ld = P.nq;
+          D.acc_out = P.acc_o; D.poison_out = P.poison + 1 * MT;
+          D.zero0 = P.acc_dn; D.zero0_n = P.m * P.d; D.zero0_poison = P.poison + 3 * MT;
+          break;
+        case 3:  // gate/up Linear on RMSNorm(x + o_proj)
+          D.type = PH_GEMV; D.w = Y.w_gu; D.colscale = Y.s_gu;
+          D.ntiles = P.gu.ntiles; D.nblk = P.gu.nblk; D.n = P.gu.n; D.k = P.gu.k;
+          D.loader = LD_RESID; D.norm_w = Y.n2; D.x_in = P.x1; D.x_out = P.x0;
+          D.acc_in = P.acc_o; D.poison_in = P.poison + 1 * MT; D.in_ld = P.d; D.ss_out = P.ss_b;
+          D.acc_out = P.acc_gu; D.poison_out = P.poison + 2 * MT;
+          D.zero0 = P.acc_qkv; D.zero0_n = P.m * P.qkv.n; D.zero0_poison = P.poison + 0 * MT;
+          break;
+        default:  // down_proj on silu(gate) * up
+          D.type = PH_GEMV; D.w = Y.w_dn; D.colscale = Y.s_dn;
+          D.ntiles = P.dn.ntiles; D.nblk = P.dn.nblk; D.n = P.dn.n; D.k = P.dn.k;
+          D.loader = LD_SWIGLU; D.acc_in = P.acc_gu; D.poison_in = P.poison + 2 * MT; D.in_ld = P.gu.n;
+          D.ss_in = P.ss_b; D.ss_groups = P.d / 32; D.ss_dim = (float)P.d;
+          D.acc_out = P.acc_dn; D.poison_out = P.poison + 3 * MT;
+          break;
+      }
+      return;
+    }
+    const uint32_t t = p - 5u * P.L;
+    if (t == 0) {  // the head (int8 even for an int4 model, llama.rs:535-542) on RMSNorm(x + down_proj)
+      D.type = PH_GEMV; D.bits = 8; D.w = P.w_head; D.colscale = P.s_head;
+      D.ntiles = P.head.ntiles; D.nblk = P.head.nblk; D.n = P.head.n; D.k = P.head.k;
+      D.loader = LD_RESID; D.norm_w = P.final_norm; D.x_in = P.x0; D.x_out = nullptr;
+      D.acc_in = P.acc_dn; D.poison_in = P.poison + 3 * MT; D.in_ld = P.d; D.ss_out = P.ss_c;
+      D.acc_out = P.acc_logits; D.poison_out = P.poison + 4 * MT;
+    } else if (t == 1) {
+      D.type = PH_FINAL;
+      D.acc_in = P.acc_logits; D.poison_in = P.poison + 4 * MT; D.in_ld = P.Vl;
+      D.ss_in = P.ss_c; D.ss_groups = P.d / 32; D.ss_dim = (float)P.d;
+      D.zero0 = P.acc_dn; D.zero0_n = P.m * P.d; D.zero0_poison = P.poison + 3 * MT;
+    } else {
+      D.type = PH_PICK;
+    }
+  }
+};
+
+struct TestProgram {
+  const GemvTestParams& P;
+  __device__ uint32_t nphases() const { return 2u * P.repeat; }
+  __device__ void get(uint32_t p, PhaseDesc& D) const {
+    D = PhaseDesc();
+    D.zero0 = nullptr; D.zero1 = nullptr; D.zero0_n = 0; D.zero1_n = 0;
+    D.bits = P.bits;
+    if ((p & 1u) == 0) {
+      D.type = PH_GEMV; D.w = P.w; D.colscale = P.colscale;
+      D.ntiles = P.g.ntiles; D.nblk = P.g.nblk; D.n = P.g.n; D.k = P.g.k;
+      D.loader = LD_PLAIN; D.x_in = P.x; D.in_ld = P.g.k;
+      D.acc_out = P.acc; D.poison_out = P.poison;
+    } else {
+      D.type = PH_OUT; D.acc_in = P.acc; D.poison_in = P.poison; D.n = P.g.n;
+    }
+  }
+};
+
+// What the kernel needs from its parameter block whichever program it runs.
+struct Common {
+  uint32_t m;
+  unsigned* bar; unsigned bar_base; int* status; int* abort_flag; unsigned spin_limit;
+  // attention / final (step program only)
+  const StepParams* sp;
+  float* out;  // test program: f32 [m][n]
+};
+
+// ---- the kernel body ------------------------------------------------------------------------------
+
+template <int MT>
+struct Ctx {
+  unsigned char* smem;
+  Shared* sh;
+  Common c;
+  int tid, lane, warp;
+  uint32_t s;    // ring stages so far (all kinds)
+  uint32_t sa;   // int4 stages so far
+  uint32_t sg;   // int8 segments so far
+  uint32_t tmem;
+
+  __device__ unsigned char* slot_ptr(uint32_t stage) const { return smem + kOffSlots + (size_t)(stage % kSlots) * kSlotBytes; }
+  __device__ unsigned char* abuf_ptr(uint32_t a) const { return smem + kOffABuf + (size_t)(a & 1u) * kABufBytes; }
+  __device__ unsigned char* bwin() const { return smem + kOffBWin; }
+  __device__ float* mscale() const { return reinterpret_cast<float*>(smem + kOffMeta); }
+  __device__ int* msum() const { return reinterpret_cast<int*>(smem + kOffMeta) + kWin * kMaxRows; }
+  __device__ bool aborted() const { return sh->abort != 0; }
+  __device__ void give_up(int code) {
+    sh->abort = 1;
+    atomicExch(c.abort_flag, 1);
+    atomicCAS(c.status, 0, code);
+  }
+  // Bounded mbarrier wait that also ends when the CTA has given up; after a failure every later wait falls
+  // through, so that all warps run to the end of the program and the CTA can leave.
+  __device__ bool wait(uint64_t* bar, uint32_t parity, int code) {
+    if (aborted()) return false;
+    const uint32_t a = smem_u32(bar);
+    for (unsigned i = 0; i < c.spin_limit; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(a), "r"(parity)
+          : "memory");
+      if (ok) return true;
+      if ((i & 15u) == 15u && aborted()) return false;
+    }
+    give_up(code);
+    return false;
+  }
+};
+
+// Grid-wide barrier: the p-th one of this launch is passed when the counter reaches base + p * gridDim.
+template <int MT>
+__device__ void grid_barrier(Ctx<MT>& X, uint32_t p, bool wait_for_it) {
+  __threadfence();
+  red_release_gpu_inc(X.c.bar);
+  if (!wait_for_it || X.aborted()) return;
+  const unsigned target = X.c.bar_base + p * gridDim.x;
+  for (unsigned i = 0; i < X.c.spin_limit; ++i) {
+    if ((int)(ld_acquire_gpu(X.c.bar) - target) >= 0) return;
+    if ((i & 31u) == 31u && __ldcg(X.c.abort_flag)) { X.sh->abort = 1; return; }
+    __nanosleep(32);
+  }
+  X.give_up(4);
+}
+
+// ---- loaders: the activations of one group of 32 as the consuming phase needs them -----------------
+
+template <int MT>
+struct Loaded {
+  float4 v[MT];   // values the digits are taken from (before the RMSNorm weight)
+  bool valid;
+};
+
+// This lane's four values (k = 32 g + 4 l8 ...) of every row.
+template <int MT>
+__device__ __forceinline__ void load_group(const Ctx<MT>& X, const PhaseDesc& D, uint32_t g, uint32_t l8, float4 (&v)[MT]) {
+  const uint32_t m = X.c.m;
+  const uint32_t kidx = g * 32u + 4u * l8;
+  const StepParams* P = X.c.sp;
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((uint32_t)r < m && kidx < D.k) {
+      switch (D.loader) {
+        case LD_PLAIN:
+          o = __ldcg(reinterpret_cast<const float4*>(D.x_in + (size_t)r * D.in_ld + kidx));
+          break;
+        case LD_EMBED: {  // Embedding::forward (layers.rs:436-446)
+          int32_t id = P->ids[r];
+          if (id < 0 || (uint32_t)id >= P->V) { if (l8 == 0) atomicExch(P->err, 1); id = 0; }
+          o = __ldg(reinterpret_cast<const float4*>(P->embed + (size_t)id * D.in_ld + kidx));
+          break;
+        }
+        case LD_RESID: {  // x + the finished sums of the previous Linear (llama.rs:306-309)
+          const float4 xv = __ldcg(reinterpret_cast<const float4*>(D.x_in + (size_t)r * D.in_ld + kidx));
+          const longlong2* a = reinterpret_cast<const longlong2*>(D.acc_in + (size_t)r * D.in_ld + kidx);
+          const longlong2 a0 = __ldcg(a), a1 = __ldcg(a + 1);
+          o = make_float4(xv.x + unfix(a0.x), xv.y + unfix(a0.y), xv.z + unfix(a1.x), xv.w + unfix(a1.y));
+          if (__ldcg(D.poison_in + r)) o.x = __int_as_float(0x7fc00000);
+          break;
+        }
+        case LD_SWIGLU: {  // silu(gate) * up (layers.rs:573-576); columns (2i, 2i+1) = (gate_i, up_i)
+          const longlong2* a = reinterpret_cast<const longlong2*>(D.acc_in + (size_t)r * D.in_ld + 2u * kidx);
+          const float rs = X.sh->rstd[r];
+          const longlong2 a0 = __ldcg(a), a1 = __ldcg(a + 1), a2 = __ldcg(a + 2), a3 = __ldcg(a + 3);
+          o.x = silu_ref(unfix(a0.x) * rs) * (unfix(a0.y) * rs);
+          o.y = silu_ref(unfix(a1.x) * rs) * (unfix(a1.y) * rs);
+          o.z = silu_ref(unfix(a2.x) * rs) * (unfix(a2.y) * rs);
+          o.w = silu_ref(unfix(a3.x) * rs) * (unfix(a3.y) * rs);
+          if (__ldcg(D.poison_in + r)) o.x = __int_as_float(0x7fc00000);
+          break;
+        }
+        default: {  // LD_ATTN: merge the key splits of this head (softmax statistics of every split)
+          const uint32_t hd = P->hd, hq = kidx / hd, e = kidx - hq * hd;
+          const uint32_t kvh = hq / P->rep, hr = hq - kvh * P->rep, S = P->splits, stride = hd + 4u;
+          const float* base = P->att_part + ((size_t)((r * P->KVl + kvh) * S) * P->rep + hr) * stride;
+          float M = -INFINITY;
+          for (uint32_t s2 = 0; s2 < S; ++s2) M = fmaxf(M, __ldcg(base + (size_t)s2 * P->rep * stride + hd));
+          float Lsum = 0.0f;
+          for (uint32_t s2 = 0; s2 < S; ++s2) {
+            const float* rec = base + (size_t)s2 * P->rep * stride;
+            const float ms = __ldcg(rec + hd);
+            if (ms == -INFINITY) continue;
+            const float wgt = expf(ms - M);
+            const float4 ov = __ldcg(reinterpret_cast<const float4*>(rec + e));
+            Lsum = fmaf(__ldcg(rec + hd + 1), wgt, Lsum);
+            o.x = fmaf(ov.x, wgt, o.x); o.y = fmaf(ov.y, wgt, o.y); o.z = fmaf(ov.z, wgt, o.z); o.w = fmaf(ov.w, wgt, o.w);
+          }
+          const float inv = 1.0f / Lsum;
+          o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+          break;
+        }
+      }
+    }
+    v[r] = o;
+  }
+}
+
+// int4: block fixed point per group of 32 (gemv_tc.cu): x = f * 2^(e-20), f as three balanced base-128 digits.
+template <int MT>
+__device__ __forceinline__ void digits4(const Ctx<MT>& X, const float4 (&xv)[MT], uint32_t ws, int lane, bool valid) {
+  const uint32_t l8 = lane & 7u;
+  unsigned char* bg = X.bwin() + (size_t)ws * kBRec + (l8 >> 2) * 128u + ((4u * l8) & 15u);
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    const float vv[4] = {xv[r].x, xv[r].y, xv[r].z, xv[r].w};
+    float gmax = fmaxf(fmaxf(fabsf(vv[0]), fabsf(vv[1])), fmaxf(fabsf(vv[2]), fabsf(vv[3])));
+    bool bad = !(finite_f(vv[0]) && finite_f(vv[1]) && finite_f(vv[2]) && finite_f(vv[3]));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 1));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 2));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 4));
+    const unsigned badmask = __ballot_sync(0xFFFFFFFFu, bad);
+    bad = ((badmask >> (lane & 24)) & 0xFFu) != 0u;
+    const uint32_t eb = __float_as_uint(gmax) >> 23;
+    const bool nz = eb >= 20u && eb < 255u && !bad;
+    const float up = nz ? __uint_as_float((273u - eb) << 23) : 0.0f;
+    float xscale = nz ? __uint_as_float((eb - 19u) << 23) : 0.0f;
+    if (bad) xscale = __int_as_float(0x7fc00000);  // NaN / Inf in the group: the row's sums become NaN, as in f32 arithmetic
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    int fs = 0;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int f = __float2int_rn(vv[t] * up);
+      const int d2 = ((f + 64) & 127) - 64;
+      const int t1 = (f - d2) >> 7;
+      const int d1 = ((t1 + 64) & 127) - 64;
+      const int d0 = (t1 - d1) >> 7;
+      fs += f;
+      w0 |= (uint32_t)(d0 & 0xFF) << (8 * t);
+      w1 |= (uint32_t)(d1 & 0xFF) << (8 * t);
+      w2 |= (uint32_t)(d2 & 0xFF) << (8 * t);
+    }
+    fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 1);
+    fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 2);
+    fs += __shfl_xor_sync(0xFFFFFFFFu, fs, 4);
+    if (valid) {
+      *reinterpret_cast<uint32_t*>(bg + (3 * r + 0) * 16) = w0;
+      *reinterpret_cast<uint32_t*>(bg + (3 * r + 1) * 16) = w1;
+      *reinterpret_cast<uint32_t*>(bg + (3 * r + 2) * 16) = w2;
+      if (l8 == 0) {
+        X.mscale()[ws * MT + r] = xscale;
+        X.msum()[ws * MT + r] = fs;
+      }
+    }
+  }
+}
+
+// int8: one exponent per row for the whole window (gemv_tc8.cu): x = f * 2^(e-27), four digits.
+template <int MT>
+__device__ __forceinline__ void digits8(const Ctx<MT>& X, const float4 (&xv)[MT], const float (&up)[MT], uint32_t ws, int lane) {
+  const uint32_t l8 = lane & 7u;
+  unsigned char* bg = X.bwin() + (size_t)ws * kBRec + (l8 >> 2) * 128u + ((4u * l8) & 15u);
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    int f[4] = {__float2int_rn(xv[r].x * up[r]), __float2int_rn(xv[r].y * up[r]), __float2int_rn(xv[r].z * up[r]), __float2int_rn(xv[r].w * up[r])};
+#pragma unroll
+    for (int t = 3; t >= 0; --t) {  // least significant digit first; operand rows: most significant first
+      uint32_t pack = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int dgt = t > 0 ? ((f[e] + 64) & 127) - 64 : f[e];
+        f[e] = (f[e] - dgt) >> 7;
+        pack |= (uint32_t)(dgt & 255) << (8 * e);
+      }
+      *reinterpret_cast<uint32_t*>(bg + (4 * r + t) * 16) = pack;
+    }
+  }
+}
+
+// Writes the digits of one round (converter warps; all of them call it).
+template <int MT>
+__device__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, uint32_t blk0, uint32_t cnt) {
+  const int cw = X.warp - kWarpConv0, lane = X.lane;
+  const uint32_t sgi = lane >> 3, l8 = lane & 7u, m = X.c.m;
+  constexpr int kPasses = 3;  // 14 warps x 4 groups x 3 >= kWin
+  float4 xv[kPasses][MT];
+  uint32_t wsl[kPasses];
+  bool val[kPasses];
+  const bool normed = D.norm_w != nullptr;
+#pragma unroll
+  for (int ps = 0; ps < kPasses; ++ps) {
+    const uint32_t i = 4u * (uint32_t)(cw + kConvWarps * ps) + sgi;
+    val[ps] = i < cnt;
+    uint32_t g = blk0 + i;
+    if (g >= D.nblk) g -= D.nblk;
+    wsl[ps] = it.windowed ? i : g;
+    if (!val[ps]) {
+#pragma unroll
+      for (int r = 0; r < MT; ++r) xv[ps][r] = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    load_group<MT>(X, D, g, l8, xv[ps]);
+    // the loader that builds x also owns writing it back and leaving the group's sum of squares, for the
+    // groups whose (tile 0, group) unit belongs to this CTA: exactly one CTA per group
+    if (D.ss_out) {
+      const bool owner = g >= it.u0 && g < it.u1;
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        const float4 o = xv[ps][r];
+        float q = fmaf(o.x, o.x, fmaf(o.y, o.y, fmaf(o.z, o.z, o.w * o.w)));
+        q += __shfl_xor_sync(0xFFu << (lane & 24), q, 1);
+        q += __shfl_xor_sync(0xFFu << (lane & 24), q, 2);
+        q += __shfl_xor_sync(0xFFu << (lane & 24), q, 4);
+        if (owner && (uint32_t)r < m) {
+          if (D.x_out) *reinterpret_cast<float4*>(D.x_out + (size_t)r * D.in_ld + g * 32u + 4u * l8) = o;
+          if (l8 == 0) D.ss_out[(size_t)r * (D.k / 32u) + g] = q;
+        }
+      }
+    }
+    if (normed) {
+      const float4 nw = __ldg(reinterpret_cast<const float4*>(D.norm_w + g * 32u + 4u * l8));
+#pragma unroll
+      for (int r = 0; r < MT; ++r) { xv[ps][r].x *= nw.x; xv[ps][r].y *= nw.y; xv[ps][r].z *= nw.z; xv[ps][r].w *= nw.w; }
+    }
+  }
+  if (D.bits == 4) {
+#pragma unroll
+    for (int ps = 0; ps < kPasses; ++ps) {
+      if (4u * (uint32_t)(cw + kConvWarps * ps) >= cnt) break;  // warp-uniform
+      digits4<MT>(X, xv[ps], wsl[ps], lane, val[ps]);
+    }
+  } else {
+    // row maxima over the window: warp part, then across the converter warps
+    float mx[MT];
+    bool bad = false;
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+      mx[r] = 0.0f;
+#pragma unroll
+      for (int ps = 0; ps < kPasses; ++ps) {
+        const float4 o = xv[ps][r];
+        mx[r] = fmaxf(mx[r], fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+        bad = bad || !(finite_f(o.x) && finite_f(o.y) && finite_f(o.z) && finite_f(o.w));
+      }
+      if (bad) mx[r] = INFINITY;
+      bad = false;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], off));
+      if (lane == 0) X.sh->wmax[r][cw] = mx[r];
+    }
+    bar_sync(3, kConverters);
+    float up[MT];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+      float gmax = 0.0f;
+#pragma unroll
+      for (int w2 = 0; w2 < kConvWarps; ++w2) gmax = fmaxf(gmax, X.sh->wmax[r][w2]);
+      const uint32_t eb = __float_as_uint(gmax) >> 23;
+      const bool nz = eb >= 27u && eb < 255u;
+      up[r] = nz ? __uint_as_float((280u - eb) << 23) : 0.0f;
+      if (cw == 0 && lane == 0) X.sh->xscale[r] = eb == 255u ? __int_as_float(0x7fc00000) : (nz ? __uint_as_float((eb - 26u) << 23) : 0.0f);
+    }
+#pragma unroll
+    for (int ps = 0; ps < kPasses; ++ps)
+      if (val[ps]) digits8<MT>(X, xv[ps], up, wsl[ps], lane);
+  }
+  fence_proxy_async_smem();
+}
+
+// Zeroes this CTA's share of the accumulators the phase retires, and works out the phase's 1/rms factors.
+template <int MT>
+__device__ void phase_duties(Ctx<MT>& X, const PhaseDesc& D) {
+  const int ct = X.tid - kWarpConv0 * 32;
+  auto zero = [&](long long* p, uint32_t n, int* poison) {
+    if (!p) return;
+    const uint32_t a = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
+    for (uint32_t i = a + ct; i < b; i += kConverters) p[i] = 0;
+    if (blockIdx.x == 0 && ct < MT && poison) poison[ct] = 0;
+  };
+  zero(D.zero0, D.zero0_n, D.zero0_poison);
+  zero(D.zero1, D.zero1_n, D.zero1_poison);
+  if (D.ss_in) {  // functional.rs:151-165: 1 / sqrt(mean(x^2) + eps), the mean from the per-group sums, in a fixed order
+    if (X.warp == kWarpConv0) {
+      for (uint32_t r = 0; r < X.c.m; ++r) {
+        float s = 0.0f;
+        for (uint32_t i = X.lane; i < D.ss_groups; i += 32) s += __ldcg(D.ss_in + (size_t)r * D.ss_groups + i);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+        if (X.lane == 0) X.sh->rstd[r] = 1.0f / sqrtf(s * (1.0f / D.ss_dim) + X.c.sp->eps);
+      }
+    }
+    bar_sync(3, kConverters);
+  }
+}
+
+// ---- producer ---------------------------------------------------------------------------------------
+
+template <int MT>
+__device__ __forceinline__ bool produce(Ctx<MT>& X, const void* src0, uint32_t bytes0, uint32_t off1, const void* src1, uint32_t bytes1) {
+  const uint32_t slot = X.s % kSlots;
+  if (X.s >= (uint32_t)kSlots && !X.wait(&X.sh->b.empty[slot], ((X.s / kSlots) - 1u) & 1u, 10)) return false;
+  unsigned char* dst = X.slot_ptr(X.s);
+  mbar_expect_tx(&X.sh->b.full[slot], bytes0 + bytes1);
+  bulk_load(dst, src0, bytes0, &X.sh->b.full[slot]);
+  if (bytes1) bulk_load(dst + off1, src1, bytes1, &X.sh->b.full[slot]);
+  ++X.s;
+  return true;
+}
+
+template <int MT, typename Prog>
+__device__ void producer_loop(Ctx<MT>& X, const Prog& prog, uint32_t len) {
+  const uint32_t np = prog.nphases();
+  for (uint32_t p = 0; p < np; ++p) {
+    PhaseDesc D;
+    prog.get(p, D);
+    if (D.type == PH_GEMV) {
+      const uint32_t rec = D.bits == 4 ? kStreamRec4 : kStreamRec8;
+      StageIter it;
+      it.init(D.ntiles, D.nblk, D.bits == 4 ? kStage4 : kStage8);
+      Stage st;
+      while (it.next(st)) {
+        const uint8_t* src = D.w + ((size_t)st.tile * D.nblk + st.blk) * rec;
+        if (!produce<MT>(X, src, st.cnt * rec, 0, nullptr, 0)) return;
+      }
+    } else if (D.type == PH_ATTN) {
+      const StepParams* P = X.c.sp;
+      AttnPlan ap;
+      ap.init(X.c.m, P->KVl, P->splits, P->keys_per_stage, len);
+      const uint32_t row = P->hd * 4u;
+      for (uint32_t item = blockIdx.x; item < ap.n_items; item += gridDim.x) {
+        uint32_t k0, k1;
+        ap.range(item, k0, k1);
+        const uint32_t bk = item / ap.S;  // (sequence, KV head)
+        const float* kb = D.kc + (size_t)bk * P->cap * P->hd;
+        const float* vb = D.vc + (size_t)bk * P->cap * P->hd;
+        for (uint32_t c0 = k0; c0 < k1; c0 += ap.KS) {
+          const uint32_t nk = min(ap.KS, k1 - c0);
+          if (!produce<MT>(X, kb + (size_t)c0 * P->hd, nk * row, kSlotBytes / 2, vb + (size_t)c0 * P->hd, nk * row)) return;
+        }
+      }
+    }
+  }
+}
+
+// ---- the GEMV phase, by role --------------------------------------------------------------------------
+
+template <int MT>
+__device__ __forceinline__ void expand_stage(Ctx<MT>& X, const Stage& st) {
+  const int ew = X.warp - kWarpExpand0;          // 0..7
+  const uint32_t col = (uint32_t)(ew & 3) * 32u + X.lane, half = (uint32_t)ew >> 2;
+  const uint32_t slot = X.s % kSlots;
+  X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 11);
+  if (X.sa >= 2u) X.wait(&X.sh->b.mma_done[(X.sa - 2u) & 3u], ((X.sa - 2u) >> 2) & 1u, 12);  // the MMAs that read this buffer last
+  const unsigned char* src = X.slot_ptr(X.s);
+  unsigned char* dst = X.abuf_ptr(X.sa);
+  if (!X.aborted()) {
+#pragma unroll
+    for (uint32_t u = 0; u < 4; ++u) {
+      const uint32_t gi = half * 4u + u;
+      if (gi < st.cnt) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(src + gi * kStreamRec4 + col * 16u);
+        uint4 lo, hi;
+        lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
+        lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
+        lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
+        lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
+        unsigned char* d = dst + gi * 4096u + col * 16u;
+        *reinterpret_cast<uint4*>(d) = lo;           // rows 0..15 of the group: first k-half
+        *reinterpret_cast<uint4*>(d + 2048) = hi;    // rows 16..31: second k-half
+      }
+    }
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (X.lane == 0) mbar_arrive(&X.sh->b.a_ready[X.sa & 1u]);
+}
+
+// Digits of a round: everyone waits until the previous round's sums are out, the converters write, everyone meets again.
+template <int MT>
+__device__ __forceinline__ void round_sync(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, const Stage& st, bool first_round) {
+  if (!first_round) bar_sync(1, kConsumers);
+  if (X.warp >= kWarpConv0) convert_round<MT>(X, D, it, st.round_blk0, st.round_cnt);
+  bar_sync(1, kConsumers);
+}
+
+template <int MT>
+__device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
+  const bool is4 = D.bits == 4;
+  const bool expander = X.warp >= kWarpExpand0, drainer = X.warp >= kWarpDrain0 && X.warp < kWarpExpand0, issuer = X.warp == kWarpIssuer;
+  StageIter it;
+  it.init(D.ntiles, D.nblk, is4 ? kStage4 : kStage8);
+  Stage st;
+  // ---- between the phases: this CTA is done with the previous phase; wait for the others ----
+  if (p > 0) {
+    bar_sync(1, kConsumers);
+    if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
+  }
+  // the expanding warps use the wait: the first two stages of this phase need nothing but their weights
+  Stage pre[2];
+  uint32_t npre = 0;
+  if (expander && is4) {
+    StageIter it2 = it;
+    while (npre < 2 && it2.next(pre[npre])) {
+      expand_stage<MT>(X, pre[npre]);
+      ++X.s; ++X.sa; ++npre;
+    }
+  }
+  if (p > 0) bar_sync(1, kConsumers);
+  if (X.warp >= kWarpConv0) phase_duties<MT>(X, D);
+
+  float acc[MT];
+#pragma unroll
+  for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
+  const uint32_t dq = (uint32_t)(X.warp & 3);                 // TMEM lane quarter of a draining warp
+  const uint32_t col = dq * 32u + X.lane;                     // its column in the tile
+  const uint32_t lane_base = (dq * 32u) << 16;
+  auto flush = [&](uint32_t tile) {
+    const uint32_t j = tile * kCols + col;
+    if (j < D.n) {
+      const float cs = is4 ? 1.0f : __ldg(D.colscale + j);
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        if ((uint32_t)r < X.c.m) {
+          const float v = acc[r] * cs;
+          if (finite_f(v)) red_add_s64(D.acc_out + (size_t)r * D.n + j, __float2ll_rn(v * kFix));
+          else atomicOr(D.poison_out + r, 1);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
+  };
+
+  bool first_round = true;
+  bool any = false;
+  uint32_t idx = 0;  // stage index in the phase
+  bool seg_open = false;
+  while (it.next(st)) {
+    any = true;
+    if (st.round_start) {
+      round_sync<MT>(X, D, it, st, first_round);
+      first_round = false;
+    }
+    const uint32_t slot = X.s % kSlots;
+    if (is4) {
+      if (expander) {
+        if (idx >= npre) { expand_stage<MT>(X, st); ++X.s; ++X.sa; }
+      } else if (issuer) {
+        if (X.lane == 0) {
+          X.wait(&X.sh->b.a_ready[X.sa & 1u], (X.sa >> 1) & 1u, 13);
+          if (X.sa >= 4u) X.wait(&X.sh->b.acc_free[X.sa & 3u], ((X.sa >> 2) - 1u) & 1u, 14);
+          if (!X.aborted()) {
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_i8(16, false);
+            const uint64_t ad = umma_desc_kmajor(smem_u32(X.abuf_ptr(X.sa)), 2048, 128);
+            const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
+            const uint32_t d0 = X.tmem + (X.sa & 3u) * (kStage4 * 16u);
+            for (uint32_t gi = 0; gi < st.cnt; ++gi)
+              umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
+            umma_commit(&X.sh->b.mma_done[X.sa & 3u]);
+          }
+        }
+        __syncwarp();
+        ++X.s; ++X.sa;
+      } else if (drainer) {
+        X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 15);   // the slot's scales are visible to this thread
+        X.wait(&X.sh->b.mma_done[X.sa & 3u], (X.sa >> 2) & 1u, 16);
+        tc_fence_after_sync();
+        const float* sc_src = reinterpret_cast<const float*>(X.slot_ptr(X.s) + 2048) + col;
+        const uint32_t t0 = X.tmem + lane_base + (X.sa & 3u) * (kStage4 * 16u);
+        float sc[kStage4];
+        int32_t dsum[kStage4][MT == 1 ? 4 : 8];
+        if (!X.aborted()) {
+#pragma unroll
+          for (int gi = 0; gi < kStage4; ++gi) {
+            if ((uint32_t)gi < st.cnt) {
+              if constexpr (MT == 1) tmem_ld4(t0 + gi * 16u, dsum[gi]);
+              else tmem_ld8(t0 + gi * 16u, dsum[gi]);
+              sc[gi] = sc_src[gi * (kStreamRec4 / 4)];
+            }
+          }
+          tmem_ld_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (X.lane == 0) { mbar_arrive(&X.sh->b.acc_free[X.sa & 3u]); mbar_arrive(&X.sh->b.empty[slot]); }
+        if (!X.aborted()) {
+#pragma unroll
+          for (int gi = 0; gi < kStage4; ++gi) {
+            if ((uint32_t)gi < st.cnt) {
+              const uint32_t mi = (st.ws + gi) * MT;
+#pragma unroll
+              for (int r = 0; r < MT; ++r) {
+                const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
+                acc[r] = fmaf((float)val, sc[gi] * X.mscale()[mi + r], acc[r]);
+              }
+            }
+          }
+        }
+        if (st.seg_end) flush(st.tile);
+        ++X.s; ++X.sa;
+      } else {
+        ++X.s; ++X.sa;
+      }
+    } else {
+      // int8: the ring slot is the A operand; one accumulator per run inside a tile
+      if (issuer) {
+        if (X.lane == 0) {
+          if (!seg_open && X.sg >= 2u) X.wait(&X.sh->b.seg_free[X.sg & 1u], ((X.sg >> 1) - 1u) & 1u, 17);
+          X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 18);
+          if (!X.aborted()) {
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_i8(16, true);
+            const uint64_t ad = umma_desc_kmajor(smem_u32(X.slot_ptr(X.s)), 2048, 128);
+            const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
+            const uint32_t d0 = X.tmem + (X.sg & 1u) * 16u;
+            for (uint32_t bi = 0; bi < st.cnt; ++bi)
+              umma_i8(d0, umma_desc_advance(ad, bi * 4096u), umma_desc_advance(bd, bi * kBRec), idesc, (seg_open || bi > 0) ? 1u : 0u);
+            umma_commit(&X.sh->b.empty[slot]);   // the slot is free once these MMAs have read it
+            mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]);
+            if (st.seg_end) umma_commit(&X.sh->b.seg_done[X.sg & 1u]);
+          }
+        }
+        __syncwarp();
+      } else if (drainer && st.seg_end) {
+        X.wait(&X.sh->b.seg_done[X.sg & 1u], (X.sg >> 1) & 1u, 19);
+        tc_fence_after_sync();
+        int32_t dg[8];
+        if (!X.aborted()) {
+          tmem_ld8(X.tmem + lane_base + (X.sg & 1u) * 16u, dg);
+          tmem_ld_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (X.lane == 0) mbar_arrive(&X.sh->b.seg_free[X.sg & 1u]);
+        if (!X.aborted()) {
+#pragma unroll
+          for (int r = 0; r < MT; ++r) {
+            float v = (float)dg[4 * r];
+            v = fmaf(v, 128.0f, (float)dg[4 * r + 1]);
+            v = fmaf(v, 128.0f, (float)dg[4 * r + 2]);
+            v = fmaf(v, 128.0f, (float)dg[4 * r + 3]);
+            acc[r] = v * X.sh->xscale[r];
+          }
+        }
+        flush(st.tile);
+      }
+      seg_open = !st.seg_end;
+      if (st.seg_end) ++X.sg;
+      ++X.s;
+    }
+    ++idx;
+  }
+  (void)any;
+}
+
+// ---- attention phase ----------------------------------------------------------------------------------
+
+template <int MT>
+__device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t len) {
+  const StepParams* P = X.c.sp;
+  if (p > 0) {
+    bar_sync(1, kConsumers);
+    if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
+    bar_sync(1, kConsumers);
+  }
+  AttnPlan ap;
+  ap.init(X.c.m, P->KVl, P->splits, P->keys_per_stage, len);
+  if (X.warp < kWarpConv0) {  // the issuing warp only keeps the ring count in step
+    for (uint32_t item = blockIdx.x; item < ap.n_items; item += gridDim.x) X.s += ap.stages(item);
+    return;
+  }
+  phase_duties<MT>(X, D);
+  const int ct = X.tid - kWarpConv0 * 32, cw = X.warp - kWarpConv0, lane = X.lane;
+  const uint32_t hd = P->hd, half = hd / 2, rep = P->rep, nq4 = hd / 4, pos = len;
+  float* qs = reinterpret_cast<float*>(X.bwin());   // [rep][hd]
+  float* knew = qs + rep * hd;
+  float* vnew = knew + hd;
+  float* sc = vnew + hd;                              // [rep][KS]
+  float* snew = sc + rep * ap.KS;                     // [rep]
+  const float2* table = P->rope + (size_t)pos * half;
+  for (uint32_t item = blockIdx.x; item < ap.n_items; item += gridDim.x) {
+    const uint32_t split = item % ap.S, bk = item / ap.S, b = bk / P->KVl, kvh = bk - b * P->KVl;
+    uint32_t k0, k1;
+    ap.range(item, k0, k1);
+    const bool owns_new = split == ap.S - 1;
+    const float rs = X.sh->rstd[b];
+    const long long* arow = D.acc_in + (size_t)b * D.in_ld;
+    const bool poisoned = __ldcg(D.poison_in + b) != 0;
+    // apply_rope (functional.rs:197-204) on the finished q (and k) sums times 1/rms
+    auto rotated = [&](uint32_t base, uint32_t e) {
+      const uint32_t f = e < half ? e : e - half;
+      const float2 cs = table[f];
+      const float x1 = unfix(__ldcg(arow + base + f)) * rs, x2 = unfix(__ldcg(arow + base + f + half)) * rs;
+      const float o = e < half ? x1 * cs.x + (-x2) * cs.y : x2 * cs.x + x1 * cs.y;
+      return poisoned ? __int_as_float(0x7fc00000) : o;
+    };
+    for (uint32_t i = ct; i < rep * hd; i += kConverters) {
+      const uint32_t r = i / hd, e = i - r * hd;
+      qs[i] = rotated((kvh * rep + r) * hd, e);
+    }
+    if (owns_new) {  // KvBuf::append (transformer.rs:27-53): the new key (rotated) and value at position len
+      const bool room = pos < P->cap;  // the host grows the cache before the step; never write past it
+      if (!room && ct == 0) atomicCAS(X.c.status, 0, 5);
+      float* kd = D.kc + ((size_t)bk * P->cap + pos) * hd;
+      float* vd = D.vc + ((size_t)bk * P->cap + pos) * hd;
+      for (uint32_t e = ct; e < hd; e += kConverters) {
+        const float kv = rotated(P->nq + kvh * hd, e);
+        float vv = unfix(__ldcg(arow + P->nq + P->nkv + kvh * hd + e)) * rs;
+        if (poisoned) vv = __int_as_float(0x7fc00000);
+        knew[e] = kv; vnew[e] = vv;
+        if (room) { kd[e] = kv; vd[e] = vv; }
+      }
+    }
+    bar_sync(3, kConverters);
+    // this thread's outputs in the value step: head vr, elements 4 vc .. 4 vc + 3
+    const bool vact = (uint32_t)ct < rep * nq4;
+    const uint32_t vr = vact ? ct / nq4 : 0, vc = vact ? ct - vr * nq4 : 0;
+    float run_m = -INFINITY, run_l = 0.0f;
+    float4 run_o = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint32_t nst = (k1 - k0 + ap.KS - 1) / ap.KS;
+    for (uint32_t j = 0; j < nst || (j == 0 && owns_new); ++j) {
+      const bool have = j < nst;
+      const uint32_t nk = have ? min(ap.KS, k1 - (k0 + j * ap.KS)) : 0;
+      const float* ks = reinterpret_cast<const float*>(X.slot_ptr(X.s));
+      const float* vs = reinterpret_cast<const float*>(X.slot_ptr(X.s) + kSlotBytes / 2);
+      if (have) X.wait(&X.sh->b.full[X.s % kSlots], (X.s / kSlots) & 1u, 20);
+      // scores: a warp per key, the lanes share the head dimension, all heads of the group at once
+      if (!X.aborted()) {
+        for (uint32_t kk = cw; kk < nk + ((j == 0 && owns_new) ? 1u : 0u); kk += kConvWarps) {
+          const bool is_new = kk >= nk;
+          const float4* krow = reinterpret_cast<const float4*>(is_new ? knew : ks + (size_t)kk * hd);
+          float a[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) a[r] = 0.0f;
+          for (uint32_t e4 = lane; e4 < nq4; e4 += 32) {
+            const float4 kv = krow[e4];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if ((uint32_t)r < rep) {
+                const float4 qv = reinterpret_cast<const float4*>(qs + r * hd)[e4];
+                a[r] = fmaf(qv.x, kv.x, a[r]); a[r] = fmaf(qv.y, kv.y, a[r]); a[r] = fmaf(qv.z, kv.z, a[r]); a[r] = fmaf(qv.w, kv.w, a[r]);
+              }
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if ((uint32_t)r < rep) {
+#pragma unroll
+              for (int off = 16; off > 0; off >>= 1) a[r] += __shfl_xor_sync(0xFFFFFFFFu, a[r], off);
+              if (lane == 0) { if (is_new) snew[r] = a[r] * P->attn_scale; else sc[r * ap.KS + kk] = a[r] * P->attn_scale; }
+            }
+          }
+        }
+      }
+      bar_sync(3, kConverters);
+      if (vact && !X.aborted()) {
+        const bool with_new = j == 0 && owns_new;
+        float M = run_m;
+        for (uint32_t kk = 0; kk < nk; ++kk) M = fmaxf(M, sc[vr * ap.KS + kk]);
+        if (with_new) M = fmaxf(M, snew[vr]);
+        const float cr = run_m == -INFINITY ? 0.0f : expf(run_m - M);
+        float Ls = run_l * cr;
+        float4 O = make_float4(run_o.x * cr, run_o.y * cr, run_o.z * cr, run_o.w * cr);
+        for (uint32_t kk = 0; kk < nk; ++kk) {
+          const float pr = expf(sc[vr * ap.KS + kk] - M);
+          const float4 vv = reinterpret_cast<const float4*>(vs + (size_t)kk * hd)[vc];
+          Ls += pr;
+          O.x = fmaf(pr, vv.x, O.x); O.y = fmaf(pr, vv.y, O.y); O.z = fmaf(pr, vv.z, O.z); O.w = fmaf(pr, vv.w, O.w);
+        }
+        if (with_new) {
+          const float pr = expf(snew[vr] - M);
+          const float4 vv = reinterpret_cast<const float4*>(vnew)[vc];
+          Ls += pr;
+          O.x = fmaf(pr, vv.x, O.x); O.y = fmaf(pr, vv.y, O.y); O.z = fmaf(pr, vv.z, O.z); O.w = fmaf(pr, vv.w, O.w);
+        }
+        run_m = M; run_l = Ls; run_o = O;
+      }
+      bar_sync(3, kConverters);
+      if (have) {
+        if (cw < 4 && lane == 0) mbar_arrive(&X.sh->b.empty[X.s % kSlots]);
+        ++X.s;
+      }
+    }
+    if (vact) {
+      float* rec = P->att_part + ((size_t)item * rep + vr) * (hd + 4u);
+      *reinterpret_cast<float4*>(rec + 4u * vc) = run_o;
+      if (vc == 0) { rec[hd] = run_m; rec[hd + 1] = run_l; }
+    }
+    bar_sync(3, kConverters);  // qs / knew are rewritten by the next item
+  }
+}
+
+// ---- logits out, greedy pick ------------------------------------------------------------------------------
+
+template <int MT>
+__device__ void final_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
+  const StepParams* P = X.c.sp;
+  bar_sync(1, kConsumers);
+  if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
+  bar_sync(1, kConsumers);
+  if (X.warp < kWarpConv0) return;
+  phase_duties<MT>(X, D);
+  const int ct = X.tid - kWarpConv0 * 32, cw = X.warp - kWarpConv0;
+  const uint32_t n = P->Vl;
+  const uint32_t a = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
+  for (uint32_t r = 0; r < X.c.m; ++r) {
+    const float rs = X.sh->rstd[r];
+    const bool poisoned = __ldcg(D.poison_in + r) != 0;
+    int32_t bv = INT32_MIN, bj = -1;
+    for (uint32_t j = a + ct; j < b; j += kConverters) {
+      float v = unfix(__ldcg(D.acc_in + (size_t)r * n + j)) * rs;
+      if (poisoned) v = __int_as_float(0x7fc00000);
+      P->logits[(size_t)r * n + j] = v;
+      const int32_t ov = ordered_bits(v);
+      if (ov >= bv) { bv = ov; bj = (int32_t)(j + P->col_offset); }  // ascending j: >= keeps the last maximum (generation.rs:6-8)
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const int32_t ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off), oj = __shfl_xor_sync(0xFFFFFFFFu, bj, off);
+      if (ov > bv || (ov == bv && oj > bj)) { bv = ov; bj = oj; }
+    }
+    if (X.lane == 0) X.sh->arg[r][cw] = make_int2(bv, bj);
+  }
+  bar_sync(3, kConverters);
+  if (ct < (int)X.c.m) {
+    int2 best = X.sh->arg[ct][0];
+    for (int w = 1; w < kConvWarps; ++w) {
+      const int2 o = X.sh->arg[ct][w];
+      if (o.x > best.x || (o.x == best.x && o.y > best.y)) best = o;
+    }
+    P->arg_slots[(size_t)blockIdx.x * kMaxRows + ct] = best;
+  }
+}
+
+template <int MT>
+__device__ void pick_phase(Ctx<MT>& X, uint32_t p) {
+  const StepParams* P = X.c.sp;
+  bar_sync(1, kConsumers);
+  if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, blockIdx.x == 0);
+  bar_sync(1, kConsumers);
+  if (blockIdx.x != 0 || X.warp < kWarpConv0 || X.aborted()) return;
+  const int cw = X.warp - kWarpConv0;
+  if (cw < (int)X.c.m && P->want_argmax) {
+    int32_t bv = INT32_MIN, bj = -1;
+    for (uint32_t t = X.lane; t < gridDim.x; t += 32) {
+      const int2 o = __ldcg(P->arg_slots + (size_t)t * kMaxRows + cw);
+      if (o.y >= 0 && (o.x > bv || (o.x == bv && o.y > bj))) { bv = o.x; bj = o.y; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const int32_t ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off), oj = __shfl_xor_sync(0xFFFFFFFFu, bj, off);
+      if (oj >= 0 && (bj < 0 || ov > bv || (ov == bv && oj > bj))) { bv = ov; bj = oj; }
+    }
+    if (X.lane == 0) P->ids[cw] = bj;
+  }
+  if (X.tid == kLeaderTid) *P->len += 1;
+}
+
+// f32 out of the accumulator, which is left zero (test program).
+template <int MT>
+__device__ void out_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
+  bar_sync(1, kConsumers);
+  if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
+  bar_sync(1, kConsumers);
+  if (X.warp < kWarpConv0) return;
+  const int ct = X.tid - kWarpConv0 * 32;
+  const uint32_t total = X.c.m * D.n;
+  const uint32_t a = (uint32_t)((uint64_t)total * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)total * (blockIdx.x + 1) / gridDim.x);
+  for (uint32_t i = a + ct; i < b; i += kConverters) {
+    float v = unfix(__ldcg(D.acc_in + i));
+    if (__ldcg(D.poison_in + i / D.n)) v = __int_as_float(0x7fc00000);
+    X.c.out[i] = v;
+    const_cast<long long*>(D.acc_in)[i] = 0;
+  }
+}
+
+template <int MT, typename Prog>
+__device__ void run_program(const Prog& prog, const Common& cm, unsigned char* smem, Shared* sh, uint32_t len) {
+  Ctx<MT> X;
+  X.smem = smem; X.sh = sh; X.c = cm;
+  X.tid = threadIdx.x; X.lane = X.tid & 31; X.warp = X.tid >> 5;
+  X.s = 0; X.sa = 0; X.sg = 0;
+  if (X.tid == 0) {
+    for (int i = 0; i < kSlots; ++i) { mbar_init(&sh->b.full[i], 1); mbar_init(&sh->b.empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh->b.a_ready[i], 8); mbar_init(&sh->b.seg_done[i], 1); mbar_init(&sh->b.seg_free[i], 4); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&sh->b.mma_done[i], 1); mbar_init(&sh->b.acc_free[i], 4); }
+    mbar_init(&sh->b.fin, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    sh->abort = 0;
+  }
+  __syncwarp();
+  if (X.warp == kWarpIssuer) tmem_alloc(&sh->tmem, kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  X.tmem = sh->tmem;
+
+  const uint32_t np = prog.nphases();
+  if (X.warp == 0) {
+    if (X.lane == 0) {
+      producer_loop<MT>(X, prog, len);
+      // no copy may be in flight when the CTA leaves
+      const uint32_t issued = X.s;
+      for (uint32_t i = issued > (uint32_t)kSlots ? issued - kSlots : 0u; i < issued; ++i) mbar_wait(&sh->b.full[i % kSlots], (i / kSlots) & 1u);
+    }
+  } else {
+    for (uint32_t p = 0; p < np; ++p) {
+      PhaseDesc D;
+      prog.get(p, D);
+      switch (D.type) {
+        case PH_GEMV: gemv_phase<MT>(X, D, p); break;
+        case PH_ATTN: attn_phase<MT>(X, D, p, len); break;
+        case PH_FINAL: final_phase<MT>(X, D, p); break;
+        case PH_PICK: pick_phase<MT>(X, p); break;
+        default: out_phase<MT>(X, D, p); break;
+      }
+    }
+    // every MMA has completed before the tensor memory goes back (normally their sums were all read long ago; a CTA
+    // that gave up may still have some in flight)
+    if (X.warp == kWarpIssuer && X.lane == 0) {
+      umma_commit(&sh->b.fin);
+      mbar_wait(&sh->b.fin, 0);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (X.warp == kWarpIssuer) tmem_dealloc(X.tmem, kTmemCols);
+}
+
+// The parameter block is copied into shared memory once and used from there; nothing takes the address of the
+// kernel parameter itself.
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 1) pstep_kernel(const StepParams Pin) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ Shared sh;
+  __shared__ StepParams P;
+  if (threadIdx.x == 0) P = Pin;
+  __syncthreads();
+  LayerPtrs* lay = reinterpret_cast<LayerPtrs*>(smem + kOffLayers);
+  for (uint32_t i = threadIdx.x; i < P.L * (sizeof(LayerPtrs) / 8); i += kThreads)
+    reinterpret_cast<unsigned long long*>(lay)[i] = reinterpret_cast<const unsigned long long*>(P.layers)[i];
+  const uint32_t len = (uint32_t)*P.len;
+  __syncthreads();
+  Common cm;
+  cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
+  cm.sp = &P; cm.out = nullptr;
+  StepProgram prog{P, lay};
+  run_program<MT>(prog, cm, smem, &sh, len);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 1) pgemv_kernel(const GemvTestParams Pin) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ Shared sh;
+  __shared__ GemvTestParams P;
+  if (threadIdx.x == 0) P = Pin;
+  __syncthreads();
+  Common cm;
+  cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
+  cm.sp = nullptr; cm.out = P.out;
+  TestProgram prog{P};
+  run_program<MT>(prog, cm, smem, &sh, 0u);
+}
+
+template <typename K>
+int launch_coop(ruai_ctx* c, K kernel, int grid, size_t smem, void* params) {
+  static bool attr_done[64][4] = {};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)attr_done;
+  void* args[1] = {params};
+  c->launches++;
+  cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)kernel, args);
+  if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "persistent kernel launch failed: %s", cudaGetErrorString(e));
+  return RUAI_OK;
+}
+
+size_t smem_bytes(uint32_t L) { return kOffLayers + (size_t)L * sizeof(LayerPtrs) + 64; }
+
+}  // namespace ps
+
+int ruai_pstep_grid(ruai_ctx* c) {
+  static int cached[64] = {};
+  int& g = cached[c->ordinal & 63];
+  if (g) return g > 0 ? g : 0;
+  const size_t smem = ps::smem_bytes(ps::kMaxLayers);
+  for (auto k : {(const void*)ps::pstep_kernel<1>, (const void*)ps::pstep_kernel<2>, (const void*)ps::pgemv_kernel<1>, (const void*)ps::pgemv_kernel<2>})
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); g = -1; return 0; }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ps::pstep_kernel<2>, ps::kThreads, smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); g = -1; return 0; }
+  int coop = 0;
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c->ordinal);
+  if (!coop) { g = -1; return 0; }
+  g = c->sm_count;
+  return g;
+}
+
+int ruai_pstep_launch(ruai_ctx* c, const ps::StepParams& p) {
+  const int grid = ruai_pstep_grid(c);
+  if (grid <= 0) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent decode kernel cannot be resident on this device");
+  if (p.L > (uint32_t)ps::kMaxLayers) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent decode kernel takes at most %d layers", ps::kMaxLayers);
+  ps::StepParams q = p;
+  return p.m <= 1 ? ps::launch_coop(c, ps::pstep_kernel<1>, grid, ps::smem_bytes(p.L), &q)
+                  : ps::launch_coop(c, ps::pstep_kernel<2>, grid, ps::smem_bytes(p.L), &q);
+}
+
+int ruai_pgemv_launch(ruai_ctx* c, const ps::GemvTestParams& p) {
+  const int grid = ruai_pstep_grid(c);
+  if (grid <= 0) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent decode kernel cannot be resident on this device");
+  ps::GemvTestParams q = p;
+  return p.m <= 1 ? ps::launch_coop(c, ps::pgemv_kernel<1>, grid, ps::smem_bytes(0), &q)
+                  : ps::launch_coop(c, ps::pgemv_kernel<2>, grid, ps::smem_bytes(0), &q);
+}
+
+// ---- one Linear through the persistent kernel's data path -----------------------------------------------
+
+RUAI_API int ruai_matmul_q_stream(ruai_ctx* c, const float* x_dev, const ruai_qweight* w_in, float* out_dev, uint32_t m, uint32_t repeat) {
+  if (!c || !x_dev || !w_in || !out_dev) return ruai_fail(c, RUAI_ERR_ARG, "ruai_matmul_q_stream: NULL argument");
+  if (m < 1 || m > (uint32_t)ps::kMaxRows) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "ruai_matmul_q_stream takes 1..%d rows, got %u", ps::kMaxRows, m);
+  if (repeat < 1) repeat = 1;
+  ruai_qweight* w = const_cast<ruai_qweight*>(w_in);
+  if (!ruai_sweight_supported(w)) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "ruai_matmul_q_stream takes int8 or int4 group-32 weights with k a multiple of 4");
+  DeviceGuard g(c->ordinal);
+  const int grid = ruai_pstep_grid(c);
+  if (grid <= 0) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent kernel cannot be resident on this device");
+  if (!w->stream) {
+    w->stream = new ruai_sweight();
+    const int rc = ruai_sweight_create(c, w, w->stream);
+    if (rc != RUAI_OK) { delete w->stream; w->stream = nullptr; return rc; }
+  }
+  if (!c->ps_sync) {
+    RUAI_CUDA(c, cudaMalloc(&c->ps_sync, 64));
+    RUAI_CUDA(c, cudaMemsetAsync(c->ps_sync, 0, 64, c->stream));
+    c->ps_bar_base = 0;
+  }
+  const size_t acc_bytes = (size_t)m * w->n * sizeof(long long);
+  RUAI_TRY(ruai_ctx_reserve(c, acc_bytes, 0));
+  RUAI_CUDA(c, cudaMemsetAsync(c->partial, 0, acc_bytes, c->stream));
+  RUAI_CUDA(c, cudaMemsetAsync(c->ps_sync + 2, 0, 2 * sizeof(unsigned), c->stream));
+  ps::GemvTestParams P{};
+  P.m = m; P.repeat = repeat;
+  P.g = ps::Geom{w->stream->ntiles, w->stream->nblk, w->stream->n, w->stream->k};
+  P.bits = w->bits; P.w = w->stream->data; P.colscale = w->stream->colscale;
+  P.x = x_dev; P.acc = reinterpret_cast<long long*>(c->partial); P.poison = reinterpret_cast<int*>(c->ps_sync + 2); P.out = out_dev;
+  P.bar = c->ps_sync; P.bar_base = c->ps_bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status;
+  P.abort_flag = reinterpret_cast<int*>(c->ps_sync + 1); P.spin_limit = c->spin_limit;
+  c->barrier_skew = 0;
+  RUAI_TRY(ruai_pgemv_launch(c, P));
+  c->ps_bar_base += (2u * repeat - 1u) * (unsigned)grid;
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_ctx_set_wait_limit(ruai_ctx* c, unsigned polls) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  c->spin_limit = polls ? polls : (1u << 20);
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_ctx_inject_barrier_skew(ruai_ctx* c, unsigned grids) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  c->barrier_skew = grids;
+  return RUAI_OK;
+}

@@ -46,6 +46,12 @@ class Device:
     def synchronize(self):
         self.check(self.L.ruai_ctx_synchronize(self.ctx))
 
+    def set_wait_limit(self, polls):
+        self.check(self.L.ruai_ctx_set_wait_limit(self.ctx, polls))
+
+    def inject_barrier_skew(self, grids):
+        self.check(self.L.ruai_ctx_inject_barrier_skew(self.ctx, grids))
+
     def timer_start(self):
         self.check(self.L.ruai_timer_start(self.ctx))
 
@@ -169,6 +175,18 @@ def _matmul_q(x, w, bias=None):
     m = int(np.prod(x.shape[:-1], dtype=np.int64))
     out = Tensor(x.dev, x.shape[:-1] + (w.n,), x.np_dtype, x.rdtype)
     x.dev.check(x.dev.L.ruai_matmul_q(x.dev.ctx, x.rdtype, x.ptr, w.h, bias.ptr if bias is not None else None, out.ptr, m))
+    return out
+
+
+def matmul_q_stream(x, w, repeat=1):
+    """`matmul_int8` / `matmul_int4` for 1 or 2 rows through the persistent kernel's data path (f32)."""
+    if x.rdtype != F32:
+        raise TypeError("matmul_q_stream: activations must be f32")
+    if x.shape[-1] != w.k:
+        raise ValueError(f"inner dims differ ({x.shape} @ int{w.bits} [{w.k}, {w.n}])")
+    m = int(np.prod(x.shape[:-1], dtype=np.int64))
+    out = Tensor(x.dev, x.shape[:-1] + (w.n,), np.float32, F32)
+    x.dev.check(x.dev.L.ruai_matmul_q_stream(x.dev.ctx, x.ptr, w.h, out.ptr, m, repeat))
     return out
 
 

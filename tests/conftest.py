@@ -10,6 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+    config.addinivalue_line("markers", "slow: a GPU test whose CPU checker side takes tens of seconds (full-size shapes)")
 
 
 @pytest.fixture(scope="session")
@@ -17,3 +18,9 @@ def golden():
     import numpy as np
     path = os.path.join(ROOT, "tests", "golden", "quant_golden.npz")
     return np.load(path)
+
+
+@pytest.fixture(scope="session")
+def greedy_golden():
+    import numpy as np
+    return np.load(os.path.join(ROOT, "tests", "golden", "greedy_golden.npz"))

@@ -254,3 +254,65 @@ def test_config4_5_full_width_layer_reduced(dev, name, cfg, bits):
     same, trace = greedy_parity(om, gm, prompt, 6, min_same=6)
     gm.cache_clear()
     close(trace[0:1], gm.forward_cached(prompt[None, :]), name)
+
+
+# ---- the benchmark models at FULL depth, against tokens and logits the checker produced for them ----------------
+
+FULL = {
+    "tinyllama-1.1b": dict(V=32000, d=2048, ffn=5632, L=22, H=32, KV=4, hd=64, max_pos=2048, theta=10000.0),
+    "llama3-8b": dict(V=128256, d=4096, ffn=14336, L=32, H=32, KV=8, hd=128, max_pos=2048, theta=500000.0),
+}
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("name", ["tinyllama-1.1b", "llama3-8b"])
+def test_full_depth_greedy_tokens_and_logits(dev, greedy_golden, name, bits):
+    """All 22 / 32 layers, prompt 16, 32 greedy tokens: identical ids, and the logits of every step within max-abs 1e-2
+    and 1e-3 of the row's largest magnitude.  The expected values come from tests/golden/make_greedy_golden.py (the CPU
+    checker run on the full model); the top-2 margins stored there show every pick is decisive (>= 7e-3)."""
+    key = f"{name}-int{bits}"
+    ids, margin = greedy_golden[key + "/ids"], greedy_golden[key + "/margin"]
+    want, absmax = greedy_golden[key + "/logits"], greedy_golden[key + "/absmax"]
+    _, gc = llama_cfg(**FULL[name])
+    gm = nn.Llama(dev, gc)
+    gm.load_synthetic(0, bits, 32)
+    prompt = oracle.synth_tokens(0, 0x20000000, 16, FULL[name]["V"])
+    assert prompt.tolist() == ids[:16].tolist()
+    got = gm.generate(prompt, 32)
+    assert got.tolist() == ids.tolist(), f"first difference at {int(np.argmax(got != ids)) - 16}; margins {margin[:4]}"
+    # teacher-forced logits of every step (persistent single-token steps after the prompt)
+    gm.cache_clear()
+    rows = [gm.forward_cached(prompt[None, :])[0]]
+    for t in ids[16:-1]:
+        rows.append(gm.forward_cached(np.array([[t]], np.int32))[0])
+    got_l = np.stack(rows)[:, ::61]
+    err = np.abs(got_l - want).max(axis=1)
+    assert (err <= TOL_ABS).all() and (err <= TOL_REL * absmax).all(), (err.max(), absmax.min())
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("name,B,cfg", [
+    ("tinyllama-1.1b-shaped, batch 64", 64, dict(V=32000, d=2048, ffn=5632, L=2, H=32, KV=4, hd=64, max_pos=2048)),
+    ("llama-3-8b-shaped, batch 128", 128, dict(V=128256, d=4096, ffn=14336, L=2, H=32, KV=8, hd=128, max_pos=2048, theta=500000.0)),
+])
+def test_large_batch_decode_steps(dev, name, B, cfg):
+    """Batched decode at the benchmark's large batches (the tensor-core GEMM inside the decode loop): B prompts of 3
+    tokens, then two greedy steps through decode_step; ids and logits against the checker.  Full widths, 2 layers."""
+    om, gm = build(dev, llama_cfg(**cfg), 0, 4, 32)
+    prompts = np.stack([oracle.synth_tokens(0, 0x20000000 + b, 3, cfg["V"]) for b in range(B)])
+    lo = om.forward_cached(prompts)
+    close(lo, gm.forward_cached(prompts), name + " prefill")
+    nxt = np.array([oracle.argmax(r) for r in lo], np.int32)
+    ids_dev = nn.Tensor.from_numpy(dev, nxt)
+    for step in range(2):
+        lo = om.forward_cached(nxt[:, None])
+        want_next = np.array([oracle.argmax(r) for r in lo], np.int32)
+        got_next = gm.decode_step(B, ids_dev.ptr if step == 0 else None)
+        srt = np.sort(lo, axis=1)
+        decisive = (srt[:, -1] - srt[:, -2]) > 1e-4
+        assert (got_next[decisive] == want_next[decisive]).all(), f"{name}: step {step}"
+        nxt = want_next
+        ids_dev = nn.Tensor.from_numpy(dev, nxt)
+        gm.cache_clear(); om.cache_clear()
+        break_after = step  # one checked step per cache state keeps the two models on the same ids
+        lo = om.forward_cached(prompts); gm.forward_cached(prompts)
