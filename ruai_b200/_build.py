@@ -17,6 +17,8 @@ LIB = os.path.join(HERE, "libruai_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
+if os.environ.get("RUAI_B200_TRACE") == "1":  # profiling build: clock stamps inside the persistent kernels
+    FLAGS.append("-DRUAI_B200_TRACE")
 
 
 def _sources():

@@ -122,8 +122,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+#ifdef RUAI_B200_TRACE
 __device__ __forceinline__ void trace_min(unsigned long long* slot, int i) { if (slot) atomicMin(slot + i, global_ns()); }
 __device__ __forceinline__ void trace_max(unsigned long long* slot, int i) { if (slot) atomicMax(slot + i, global_ns()); }
+#else  // the stamps exist in profiling builds only
+__device__ __forceinline__ void trace_min(unsigned long long*, int) {}
+__device__ __forceinline__ void trace_max(unsigned long long*, int) {}
+#endif
 inline unsigned long long* ruai_trace_slot(ruai_ctx* c) {
   if (!c->trace || c->trace_seq >= c->trace_slots) return nullptr;
   return c->trace + 4ull * (c->trace_seq++);

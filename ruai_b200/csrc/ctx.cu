@@ -171,7 +171,8 @@ RUAI_API int ruai_timer_stop_ms(ruai_ctx* c, float* ms) {
   return RUAI_OK;
 }
 
-// Debug hooks (not declared in the public header).
+// Profiling hooks, present only in builds made with RUAI_B200_TRACE=1 (never in the library as shipped).
+#ifdef RUAI_B200_TRACE
 RUAI_API int ruai_debug_force_splits(ruai_ctx* c, unsigned splits) {
   c->force_splits = splits;
   return RUAI_OK;
@@ -183,3 +184,4 @@ RUAI_API int ruai_debug_trace(ruai_ctx* c, void* dev_buf, unsigned slots) {
   c->trace_seq = 0;
   return RUAI_OK;
 }
+#endif

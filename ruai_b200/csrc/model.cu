@@ -706,7 +706,7 @@ int pstep_run(ruai_model* m, uint32_t B) {
   }
   ps::StepParams P{};
   P.m = B; P.L = m->L; P.d = d; P.nq = nq; P.nkv = nkv; P.hd = hd; P.Hl = m->Hl; P.KVl = m->KVl; P.rep = rep; P.fl = m->fl; P.Vl = m->Vl; P.V = m->V;
-  P.cap = m->cap; P.bits = m->bits; P.splits = splits; P.keys_per_stage = (20480u / 2u) / (hd * 4u); P.col_offset = m->rank * m->Vl;
+  P.cap = m->cap; P.bits = m->bits; P.splits = splits; P.keys_per_stage = (kRingSlotBytes / 2u) / (hd * 4u); P.col_offset = m->rank * m->Vl;
   P.eps = m->eps; P.attn_scale = 1.0f / sqrtf((float)hd);
   auto geom = [](const ruai_sweight& w) { return ps::Geom{w.ntiles, w.nblk, w.n, w.k}; };
   P.qkv = geom(m->layers[0].qkv.sw); P.o = geom(m->layers[0].o.sw); P.gu = geom(m->layers[0].up.sw); P.dn = geom(m->layers[0].down.sw);
@@ -730,6 +730,7 @@ int pstep_run(ruai_model* m, uint32_t B) {
   P.bar = S.sync.as<unsigned>(); P.bar_base = S.bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status; P.abort_flag = S.sync.as<int>() + 1;
   P.spin_limit = c->spin_limit;
   P.want_argmax = 1;
+  P.trace = c->trace;
   c->barrier_skew = 0;
   RUAI_TRY(ruai_pstep_launch(c, P));
   S.bar_base += (5u * m->L + 2u) * (unsigned)grid;  // one arrival per CTA at each of the step's barriers

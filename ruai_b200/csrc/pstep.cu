@@ -41,24 +41,27 @@ namespace ps {
 using namespace pipe;
 
 constexpr int kCols = 128;            // tile columns = MMA M = TMEM lanes
-constexpr int kStage4 = 8;            // int4 scale groups per ring stage
-constexpr int kStage8 = 5;            // int8 32-row blocks per ring stage
-constexpr uint32_t kSlotBytes = 20480;
-constexpr int kSlots = 6;
-constexpr uint32_t kABufBytes = kStage4 * 4096;
+constexpr int kStage4 = 4;            // int4 scale groups per ring stage: the unit one warpgroup works on
+constexpr int kStage8 = 3;            // int8 32-row blocks per ring stage
+constexpr uint32_t kSlotBytes = kRingSlotBytes;
+constexpr int kSlots = 7;
+constexpr int kGroups = 3;            // warpgroups of four warps; ring stage s belongs to warpgroup s % kGroups
+constexpr uint32_t kABufBytes = kStage4 * 4096;  // A-operand buffer of one stage; two per warpgroup
+constexpr uint32_t kAcc8 = 8;         // int8: independent accumulators a warpgroup's MMAs rotate through
 constexpr int kWin = 128;             // window of the activation digits: groups (int4) / blocks (int8)
 constexpr uint32_t kBRec = 256;       // digit operand of one group: [2 k-halves][8 rows][16 bytes]
-constexpr int kThreads = 512;
-constexpr int kConsumers = 480;       // warps 1..15
-constexpr int kConverters = 448;      // warps 2..15
+// 15 warps: at most four on an SM sub-partition, so its 16 K registers allow 128 per thread (a sixteenth warp fits; a
+// seventeenth would cut every thread to 96 registers, and the spills that follow cost more than the warps bring).
+constexpr int kThreads = 480;         // warp 0: producer; warp 1: leader + MMA issuer 0; warp 2: MMA issuer 1; warps 3..14: three warpgroups
+constexpr int kConsumers = 448;       // warps 1..14
 constexpr int kConvWarps = 14;
-constexpr int kWarpIssuer = 1, kWarpConv0 = 2, kWarpDrain0 = 4, kWarpExpand0 = 8;
-constexpr int kLeaderTid = kWarpConv0 * 32;
+constexpr int kWarpLeader = 1, kWarpIssuer1 = 2, kWarpWg0 = 3;
+constexpr int kLeaderTid = kWarpLeader * 32;
 constexpr uint32_t kTmemCols = 512;
 
 constexpr size_t kOffSlots = 0;
 constexpr size_t kOffABuf = kOffSlots + (size_t)kSlots * kSlotBytes;
-constexpr size_t kOffBWin = kOffABuf + 2 * (size_t)kABufBytes;
+constexpr size_t kOffBWin = kOffABuf + 2 * (size_t)kGroups * kABufBytes;
 constexpr size_t kOffMeta = kOffBWin + (size_t)kWin * kBRec;
 constexpr size_t kOffLayers = kOffMeta + (size_t)kWin * kMaxRows * 8;
 
@@ -85,8 +88,12 @@ struct PhaseDesc {
 
 struct Bars {
   uint64_t full[kSlots], empty[kSlots];
-  uint64_t a_ready[2], mma_done[4], acc_free[4], seg_done[2], seg_free[2];
-  uint64_t fin;  // every MMA of the CTA has completed
+  uint64_t a_ready[kGroups][2];   // a warpgroup's A buffer 0 / 1 is written (its 4 warps arrive); one barrier per buffer,
+                                  // because a warpgroup may be a stage ahead of the issuer
+  uint64_t mma_done[kGroups][2];  // the MMAs of a warpgroup's stage into accumulator buffer 0 / 1 have completed
+  uint64_t seg_done[2];           // int8: the MMAs of an issuer's part of a run have completed
+  uint64_t seg_free[2];           // int8: its sums are read out (the 4 warps of warpgroup 0 / 1 arrive)
+  uint64_t fin[2];                // every MMA of an issuer has completed (before the tensor memory goes back)
 };
 
 struct Shared {
@@ -96,7 +103,7 @@ struct Shared {
   float rstd[kMaxRows];
   float wmax[kMaxRows][kConvWarps];
   float xscale[kMaxRows];
-  int2 arg[kMaxRows][16];
+  int2 arg[kMaxRows][kConvWarps];
 };
 
 // ---- small device helpers --------------------------------------------------------------------
@@ -146,7 +153,7 @@ struct Stage {
 // activations are kept for a window of kWin blocks: if the weight has at most kWin blocks of k the window
 // slot of a block is the block itself and the phase is one round; otherwise a round is kWin consecutive units.
 struct StageIter {
-  uint32_t u, u0, u1, nblk, smax, tile, blk, round_u0;
+  uint32_t u, u0, u1, nblk, smax, tile, blk, round_u0, blk_at_u0;
   bool windowed, first;
   __device__ void init(uint32_t ntiles, uint32_t nblk_, uint32_t smax_) {
     const uint64_t units = (uint64_t)ntiles * nblk_;
@@ -154,20 +161,24 @@ struct StageIter {
     u1 = (uint32_t)(units * (blockIdx.x + 1) / gridDim.x);
     u = u0; nblk = nblk_; smax = smax_;
     tile = u0 / nblk_; blk = u0 - tile * nblk_;
+    blk_at_u0 = blk;
     windowed = nblk_ > (uint32_t)kWin;
     round_u0 = u0; first = true;
   }
-  __device__ bool next(Stage& s) {
+  // a handful of adds and compares: every warp walks every stage of its CTA
+  __device__ __forceinline__ bool next(Stage& s) {
     if (u >= u1) return false;
     s.round_start = first;
     first = false;
-    if (windowed && u - round_u0 >= (uint32_t)kWin) { round_u0 = u; s.round_start = true; }
-    uint32_t cnt = min(min(smax, nblk - blk), u1 - u);
     uint32_t round_end = u1;
-    if (windowed) { round_end = min(u1, round_u0 + (uint32_t)kWin); cnt = min(cnt, round_end - u); }
+    if (windowed) {
+      if (u - round_u0 >= (uint32_t)kWin) { round_u0 = u; s.round_start = true; }
+      round_end = min(u1, round_u0 + (uint32_t)kWin);
+    }
+    const uint32_t cnt = min(min(smax, nblk - blk), round_end - u);
     s.tile = tile; s.blk = blk; s.cnt = cnt;
     s.ws = windowed ? u - round_u0 : blk;
-    s.round_blk0 = windowed ? blk : (u0 % nblk);
+    s.round_blk0 = windowed ? blk : blk_at_u0;
     s.round_cnt = windowed ? round_end - round_u0 : min(u1 - u0, nblk);
     s.seg_end = (blk + cnt == nblk) || (u + cnt == round_end);
     u += cnt; blk += cnt;
@@ -294,7 +305,31 @@ struct Common {
   // attention / final (step program only)
   const StepParams* sp;
   float* out;  // test program: f32 [m][n]
+  unsigned long long* trace;
 };
+
+// Profiling builds only (-DRUAI_B200_TRACE): CTA 0 stamps its SM clock at the hand-overs of the first stages.
+// Layout: stage events [kTraceStages][8], then phase events [kTracePhases][4].
+constexpr uint32_t kTraceStages = 192, kTracePhases = 192;
+#ifdef RUAI_B200_TRACE
+#define PS_TRACE_STAGE(X, stage, ev)                                                                       \
+  do {                                                                                                     \
+    if ((X).c.trace && blockIdx.x == 0 && (stage) < kTraceStages) (X).c.trace[(size_t)(stage) * 8 + (ev)] = clock64(); \
+  } while (0)
+#define PS_TRACE_PHASE(X, phase, ev)                                                                       \
+  do {                                                                                                     \
+    if ((X).c.trace && blockIdx.x == 0 && (phase) < kTracePhases) (X).c.trace[(size_t)kTraceStages * 8 + (size_t)(phase) * 4 + (ev)] = clock64(); \
+  } while (0)
+#define PS_TRACE_ISSUE(X, stage, ev)                                                                       \
+  do {                                                                                                     \
+    if ((X).c.trace && blockIdx.x == 0 && (stage) < kTraceStages)                                          \
+      (X).c.trace[(size_t)kTraceStages * 8 + (size_t)kTracePhases * 4 + (size_t)(stage) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define PS_TRACE_ISSUE(X, stage, ev) do { } while (0)
+#define PS_TRACE_STAGE(X, stage, ev) do { } while (0)
+#define PS_TRACE_PHASE(X, phase, ev) do { } while (0)
+#endif
 
 // ---- the kernel body ------------------------------------------------------------------------------
 
@@ -304,13 +339,14 @@ struct Ctx {
   Shared* sh;
   Common c;
   int tid, lane, warp;
-  uint32_t s;    // ring stages so far (all kinds)
-  uint32_t sa;   // int4 stages so far
-  uint32_t sg;   // int8 segments so far
+  uint32_t cur_phase;
+  uint32_t s;    // ring stages so far (all kinds, all warpgroups)
+  uint32_t mc0, mc1, mc2;  // int4 stages of warpgroup 0 / 1 / 2 so far (every consumer thread keeps all three)
+  uint32_t sgc;  // int8 runs closed so far (issuer i and warpgroup i count the same runs)
   uint32_t tmem;
 
   __device__ unsigned char* slot_ptr(uint32_t stage) const { return smem + kOffSlots + (size_t)(stage % kSlots) * kSlotBytes; }
-  __device__ unsigned char* abuf_ptr(uint32_t a) const { return smem + kOffABuf + (size_t)(a & 1u) * kABufBytes; }
+  __device__ unsigned char* abuf_ptr(uint32_t wg, uint32_t k) const { return smem + kOffABuf + (size_t)(2u * wg + (k & 1u)) * kABufBytes; }
   __device__ unsigned char* bwin() const { return smem + kOffBWin; }
   __device__ float* mscale() const { return reinterpret_cast<float*>(smem + kOffMeta); }
   __device__ int* msum() const { return reinterpret_cast<int*>(smem + kOffMeta) + kWin * kMaxRows; }
@@ -325,15 +361,25 @@ struct Ctx {
   __device__ bool wait(uint64_t* bar, uint32_t parity, int code) {
     if (aborted()) return false;
     const uint32_t a = smem_u32(bar);
+    uint32_t ok;
+    // the common case is "already complete": a plain test returns at once
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    // otherwise poll with a short sleep in between: a suspending try_wait was seen to wake up more than a thousand cycles
+    // after the barrier completed, and a tight polling loop takes the issue slots of the warps it waits for
     for (unsigned i = 0; i < c.spin_limit; ++i) {
-      uint32_t ok;
+      __nanosleep(40);
       asm volatile(
-          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+          "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(ok)
           : "r"(a), "r"(parity)
           : "memory");
       if (ok) return true;
-      if ((i & 15u) == 15u && aborted()) return false;
+      if ((i & 7u) == 7u && aborted()) return false;
     }
     give_up(code);
     return false;
@@ -349,8 +395,8 @@ __device__ void grid_barrier(Ctx<MT>& X, uint32_t p, bool wait_for_it) {
   const unsigned target = X.c.bar_base + p * gridDim.x;
   for (unsigned i = 0; i < X.c.spin_limit; ++i) {
     if ((int)(ld_acquire_gpu(X.c.bar) - target) >= 0) return;
-    if ((i & 31u) == 31u && __ldcg(X.c.abort_flag)) { X.sh->abort = 1; return; }
-    __nanosleep(32);
+    if ((i & 63u) == 63u && __ldcg(X.c.abort_flag)) { X.sh->abort = 1; return; }
+    __nanosleep(20);
   }
   X.give_up(4);
 }
@@ -499,12 +545,12 @@ __device__ __forceinline__ void digits8(const Ctx<MT>& X, const float4 (&xv)[MT]
   }
 }
 
-// Writes the digits of one round (converter warps; all of them call it).
+// Writes the digits of one round (all consumer warps call it).
 template <int MT>
 __device__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, uint32_t blk0, uint32_t cnt) {
-  const int cw = X.warp - kWarpConv0, lane = X.lane;
+  const int cw = X.warp - kWarpLeader, lane = X.lane;
   const uint32_t sgi = lane >> 3, l8 = lane & 7u, m = X.c.m;
-  constexpr int kPasses = 3;  // 14 warps x 4 groups x 3 >= kWin
+  constexpr int kPasses = (kWin + 4 * kConvWarps - 1) / (4 * kConvWarps);  // every consumer warp converts 4 groups per pass
   float4 xv[kPasses][MT];
   uint32_t wsl[kPasses];
   bool val[kPasses];
@@ -570,7 +616,7 @@ __device__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& i
       for (int off = 16; off > 0; off >>= 1) mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], off));
       if (lane == 0) X.sh->wmax[r][cw] = mx[r];
     }
-    bar_sync(3, kConverters);
+    bar_sync(1, kConsumers);
     float up[MT];
 #pragma unroll
     for (int r = 0; r < MT; ++r) {
@@ -592,17 +638,17 @@ __device__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& i
 // Zeroes this CTA's share of the accumulators the phase retires, and works out the phase's 1/rms factors.
 template <int MT>
 __device__ void phase_duties(Ctx<MT>& X, const PhaseDesc& D) {
-  const int ct = X.tid - kWarpConv0 * 32;
+  const int ct = X.tid - kWarpLeader * 32;
   auto zero = [&](long long* p, uint32_t n, int* poison) {
     if (!p) return;
     const uint32_t a = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
-    for (uint32_t i = a + ct; i < b; i += kConverters) p[i] = 0;
+    for (uint32_t i = a + ct; i < b; i += kConsumers) p[i] = 0;
     if (blockIdx.x == 0 && ct < MT && poison) poison[ct] = 0;
   };
   zero(D.zero0, D.zero0_n, D.zero0_poison);
   zero(D.zero1, D.zero1_n, D.zero1_poison);
   if (D.ss_in) {  // functional.rs:151-165: 1 / sqrt(mean(x^2) + eps), the mean from the per-group sums, in a fixed order
-    if (X.warp == kWarpConv0) {
+    if (X.warp == kWarpLeader) {
       for (uint32_t r = 0; r < X.c.m; ++r) {
         float s = 0.0f;
         for (uint32_t i = X.lane; i < D.ss_groups; i += 32) s += __ldcg(D.ss_in + (size_t)r * D.ss_groups + i);
@@ -611,7 +657,7 @@ __device__ void phase_duties(Ctx<MT>& X, const PhaseDesc& D) {
         if (X.lane == 0) X.sh->rstd[r] = 1.0f / sqrtf(s * (1.0f / D.ss_dim) + X.c.sp->eps);
       }
     }
-    bar_sync(3, kConverters);
+    bar_sync(1, kConsumers);
   }
 }
 
@@ -622,6 +668,7 @@ __device__ __forceinline__ bool produce(Ctx<MT>& X, const void* src0, uint32_t b
   const uint32_t slot = X.s % kSlots;
   if (X.s >= (uint32_t)kSlots && !X.wait(&X.sh->b.empty[slot], ((X.s / kSlots) - 1u) & 1u, 10)) return false;
   unsigned char* dst = X.slot_ptr(X.s);
+  PS_TRACE_STAGE(X, X.s, 0);
   mbar_expect_tx(&X.sh->b.full[slot], bytes0 + bytes1);
   bulk_load(dst, src0, bytes0, &X.sh->b.full[slot]);
   if (bytes1) bulk_load(dst + off1, src1, bytes1, &X.sh->b.full[slot]);
@@ -666,79 +713,97 @@ __device__ void producer_loop(Ctx<MT>& X, const Prog& prog, uint32_t len) {
 
 // ---- the GEMV phase, by role --------------------------------------------------------------------------
 
-template <int MT>
-__device__ __forceinline__ void expand_stage(Ctx<MT>& X, const Stage& st) {
-  const int ew = X.warp - kWarpExpand0;          // 0..7
-  const uint32_t col = (uint32_t)(ew & 3) * 32u + X.lane, half = (uint32_t)ew >> 2;
-  const uint32_t slot = X.s % kSlots;
-  X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 11);
-  if (X.sa >= 2u) X.wait(&X.sh->b.mma_done[(X.sa - 2u) & 3u], ((X.sa - 2u) >> 2) & 1u, 12);  // the MMAs that read this buffer last
-  const unsigned char* src = X.slot_ptr(X.s);
-  unsigned char* dst = X.abuf_ptr(X.sa);
-  if (!X.aborted()) {
-#pragma unroll
-    for (uint32_t u = 0; u < 4; ++u) {
-      const uint32_t gi = half * 4u + u;
-      if (gi < st.cnt) {
-        const uint4 wv = *reinterpret_cast<const uint4*>(src + gi * kStreamRec4 + col * 16u);
-        uint4 lo, hi;
-        lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
-        lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
-        lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
-        lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
-        unsigned char* d = dst + gi * 4096u + col * 16u;
-        *reinterpret_cast<uint4*>(d) = lo;           // rows 0..15 of the group: first k-half
-        *reinterpret_cast<uint4*>(d + 2048) = hi;    // rows 16..31: second k-half
-      }
-    }
-  }
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (X.lane == 0) mbar_arrive(&X.sh->b.a_ready[X.sa & 1u]);
-}
-
-// Digits of a round: everyone waits until the previous round's sums are out, the converters write, everyone meets again.
+// Digits of a round: everyone waits until the previous round's sums are out, all consumer warps write, everyone meets again.
 template <int MT>
 __device__ __forceinline__ void round_sync(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, const Stage& st, bool first_round) {
   if (!first_round) bar_sync(1, kConsumers);
-  if (X.warp >= kWarpConv0) convert_round<MT>(X, D, it, st.round_blk0, st.round_cnt);
+  convert_round<MT>(X, D, it, st.round_blk0, st.round_cnt);
   bar_sync(1, kConsumers);
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, X.cur_phase, 2);
 }
 
+__device__ __forceinline__ void wg_bar(int g) { bar_sync(4 + g, 128); }
+
+// A GEMV phase.  Ring stage s belongs to warpgroup s % 3 (thread = column of the tile, as expanding and as draining
+// thread) and to MMA issuer s % 2 (one thread of warp 1 / warp 2: a thread needs well over a hundred cycles per
+// tcgen05.mma, so the issuing is spread over two threads that do nothing else).
+// int4, per stage of a warpgroup, in program order: request the sums of its PREVIOUS stage out of tensor memory;
+// packed nibbles of the ring slot -> bytes in the warpgroup's A buffer (the slot goes back to the producer at once;
+// the group scales stay in registers); tell the issuer; then finish the previous stage (scale, accumulate in f32).
+// The issuer waits for the A buffer, issues one MMA per scale group, each into its own accumulator, and commits.
+// int8: the ring slot is the operand; an issuer rotates its MMAs over eight accumulators of its own, and warpgroup
+// 0 / 1 reads issuer 0's / 1's out when the run inside the tile ends.  Every part of a tile is added to the global
+// fixed-point accumulator.
 template <int MT>
 __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   const bool is4 = D.bits == 4;
-  const bool expander = X.warp >= kWarpExpand0, drainer = X.warp >= kWarpDrain0 && X.warp < kWarpExpand0, issuer = X.warp == kWarpIssuer;
+  const bool worker = X.warp >= kWarpWg0;
+  const int g = worker ? (X.warp - kWarpWg0) >> 2 : 0;
+  const int issuer_idx = X.warp == kWarpLeader ? 0 : (X.warp == kWarpIssuer1 ? 1 : -1);
+  const bool issuer = issuer_idx >= 0 && X.lane == 0;
+  const bool tracer = worker && g == 0 && X.lane == 0 && ((X.warp - kWarpWg0) & 3) == 0;
+  const uint32_t quarter = (uint32_t)(X.warp & 3);            // TMEM lanes 32 * (warp % 4) .. belong to this warp
+  const uint32_t col = quarter * 32u + X.lane;                // its column of the tile
+  const uint32_t lane_base = (quarter * 32u) << 16;
+  (void)tracer;
   StageIter it;
   it.init(D.ntiles, D.nblk, is4 ? kStage4 : kStage8);
   Stage st;
-  // ---- between the phases: this CTA is done with the previous phase; wait for the others ----
-  if (p > 0) {
-    bar_sync(1, kConsumers);
-    if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
-  }
-  // the expanding warps use the wait: the first two stages of this phase need nothing but their weights
-  Stage pre[2];
-  uint32_t npre = 0;
-  if (expander && is4) {
-    StageIter it2 = it;
-    while (npre < 2 && it2.next(pre[npre])) {
-      expand_stage<MT>(X, pre[npre]);
-      ++X.s; ++X.sa; ++npre;
-    }
-  }
-  if (p > 0) bar_sync(1, kConsumers);
-  if (X.warp >= kWarpConv0) phase_duties<MT>(X, D);
+  X.cur_phase = p;
 
+  // int4 stages of warpgroup wg so far (constant-indexed, so the counters stay in registers)
+  auto wg_count = [&](uint32_t wg) { return wg == 0u ? X.mc0 : (wg == 1u ? X.mc1 : X.mc2); };
+  float sc_cur[kStage4], sc_pend[kStage4];
+#pragma unroll
+  for (int i = 0; i < kStage4; ++i) { sc_cur[i] = 0.0f; sc_pend[i] = 0.0f; }
+  uint32_t pend_ws = 0, pend_cnt = 0, pend_mc = 0;
+  bool have_pending = false;
+  int32_t dsum[kStage4][MT == 1 ? 4 : 8];
+
+  // sums of the warpgroup's previous stage: the loads are requested early and collected late
+  auto drain_request = [&]() {
+    X.wait(&X.sh->b.mma_done[g][pend_mc & 1u], (pend_mc >> 1) & 1u, 16);
+    if (tracer) PS_TRACE_STAGE(X, 4u * pend_mc, 5);
+    tc_fence_after_sync();
+    if (!X.aborted()) {
+      const uint32_t t0 = X.tmem + lane_base + (uint32_t)g * 128u + (pend_mc & 1u) * 64u;
+#pragma unroll
+      for (int gi = 0; gi < kStage4; ++gi) {
+        if ((uint32_t)gi < pend_cnt) {
+          if constexpr (MT == 1) tmem_ld4(t0 + gi * 16u, dsum[gi]);
+          else tmem_ld8(t0 + gi * 16u, dsum[gi]);
+        }
+      }
+    }
+  };
   float acc[MT];
 #pragma unroll
   for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
-  const uint32_t dq = (uint32_t)(X.warp & 3);                 // TMEM lane quarter of a draining warp
-  const uint32_t col = dq * 32u + X.lane;                     // its column in the tile
-  const uint32_t lane_base = (dq * 32u) << 16;
+  bool dirty = false;  // acc holds something that has not gone out yet
+  auto drain_collect = [&]() {
+    tmem_ld_wait();
+    tc_fence_before_sync();
+    if (tracer) PS_TRACE_STAGE(X, 4u * pend_mc, 6);
+    if (!X.aborted()) {
+#pragma unroll
+      for (int gi = 0; gi < kStage4; ++gi) {
+        if ((uint32_t)gi < pend_cnt) {
+          const uint32_t mi = (pend_ws + gi) * MT;
+#pragma unroll
+          for (int r = 0; r < MT; ++r) {
+            const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
+            acc[r] = fmaf((float)val, sc_pend[gi] * X.mscale()[mi + r], acc[r]);
+          }
+        }
+      }
+      dirty = true;
+    }
+    have_pending = false;
+    if (tracer) PS_TRACE_STAGE(X, 4u * pend_mc, 7);
+  };
   auto flush = [&](uint32_t tile) {
     const uint32_t j = tile * kCols + col;
-    if (j < D.n) {
+    if (dirty && j < D.n) {
       const float cs = is4 ? 1.0f : __ldg(D.colscale + j);
 #pragma unroll
       for (int r = 0; r < MT; ++r) {
@@ -751,129 +816,204 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
     }
 #pragma unroll
     for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
+    dirty = false;
+  };
+  // packed weights of ring stage s -> the warpgroup's A buffer; the slot is released; the issuer is told
+  auto expand = [&](const Stage& t, uint32_t s) {
+    const uint32_t slot = s % kSlots;
+    X.wait(&X.sh->b.full[slot], (s / kSlots) & 1u, 11);
+    // the MMAs that read the A buffer last (this warpgroup's previous stage) are done
+    // the MMAs that read this A buffer last (this warpgroup's stage before the previous one) are done
+    const uint32_t mc = wg_count((uint32_t)g);
+    if (mc >= 2u) X.wait(&X.sh->b.mma_done[g][mc & 1u], ((mc - 2u) >> 1) & 1u, 12);
+    if (tracer) PS_TRACE_STAGE(X, s, 1);
+    const unsigned char* src = X.slot_ptr(s);
+    unsigned char* dst = X.abuf_ptr(g, mc);
+    if (!X.aborted()) {
+#pragma unroll
+      for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi) {
+        if (gi < t.cnt) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(src + gi * kStreamRec4 + col * 16u);
+          sc_cur[gi] = *reinterpret_cast<const float*>(src + gi * kStreamRec4 + 2048u + col * 4u);
+          uint4 lo, hi;
+          lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
+          lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
+          lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
+          lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
+          unsigned char* d = dst + gi * 4096u + col * 16u;
+          *reinterpret_cast<uint4*>(d) = lo;           // rows 0..15 of the group: first k-half
+          *reinterpret_cast<uint4*>(d + 2048) = hi;    // rows 16..31: second k-half
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (X.lane == 0) {
+      mbar_arrive(&X.sh->b.empty[slot]);   // packed weights and scales are out of the slot
+      mbar_arrive(&X.sh->b.a_ready[g][mc & 1u]);
+    }
+    if (tracer) PS_TRACE_STAGE(X, s, 2);
   };
 
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 0);
+  // ---- between the phases: this CTA is done with the previous phase; wait for the others ----
+  if (p > 0) {
+    bar_sync(1, kConsumers);
+    if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
+  }
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 1);
+  // every warpgroup uses the wait: its first stage of this phase needs nothing but its weights
+  uint32_t pre_stage = 0xFFFFFFFFu;
+  if (worker && is4) {
+    StageIter it2 = it;
+    Stage t2;
+    uint32_t s2 = X.s;
+    while (it2.next(t2)) {
+      if ((s2 % kGroups) == (uint32_t)g) {
+        expand(t2, s2);
+        pre_stage = s2;
+        break;
+      }
+      ++s2;
+    }
+  }
+  if (p > 0) bar_sync(1, kConsumers);
+  phase_duties<MT>(X, D);
+
   bool first_round = true;
-  bool any = false;
-  uint32_t idx = 0;  // stage index in the phase
-  bool seg_open = false;
+  uint32_t seg_mmas = 0;      // int8: MMAs of issuer (stage & 1) in the open run, tracked by that issuer and its warpgroup
   while (it.next(st)) {
-    any = true;
     if (st.round_start) {
       round_sync<MT>(X, D, it, st, first_round);
       first_round = false;
     }
     const uint32_t slot = X.s % kSlots;
+    const uint32_t sg = X.s % kGroups;           // warpgroup of this stage
     if (is4) {
-      if (expander) {
-        if (idx >= npre) { expand_stage<MT>(X, st); ++X.s; ++X.sa; }
-      } else if (issuer) {
-        if (X.lane == 0) {
-          X.wait(&X.sh->b.a_ready[X.sa & 1u], (X.sa >> 1) & 1u, 13);
-          if (X.sa >= 4u) X.wait(&X.sh->b.acc_free[X.sa & 3u], ((X.sa >> 2) - 1u) & 1u, 14);
-          if (!X.aborted()) {
-            tc_fence_after_sync();
-            constexpr uint32_t idesc = umma_idesc_i8(16, false);
-            const uint64_t ad = umma_desc_kmajor(smem_u32(X.abuf_ptr(X.sa)), 2048, 128);
-            const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
-            const uint32_t d0 = X.tmem + (X.sa & 3u) * (kStage4 * 16u);
+      if (worker && sg == (uint32_t)g) {
+        if (X.s != pre_stage) expand(st, X.s);
+        if (have_pending) { drain_request(); drain_collect(); }  // while the MMAs of this stage are issued and run
+        pend_ws = st.ws; pend_cnt = st.cnt; pend_mc = wg_count((uint32_t)g);
+#pragma unroll
+        for (int i = 0; i < kStage4; ++i) sc_pend[i] = sc_cur[i];
+        have_pending = true;
+      }
+      if (issuer && (X.s & 1u) == (uint32_t)issuer_idx) {
+        const uint32_t k = wg_count(sg);  // this is the k-th stage of warpgroup sg since the kernel started
+        X.wait(&X.sh->b.a_ready[sg][k & 1u], (k >> 1) & 1u, 13);
+        PS_TRACE_STAGE(X, X.s, 3);
+        if (!X.aborted()) {
+          tc_fence_after_sync();
+          constexpr uint32_t idesc = umma_idesc_i8(16, false);
+          const uint64_t ad = umma_desc_kmajor(smem_u32(X.abuf_ptr(sg, k)), 2048, 128);
+          const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
+          const uint32_t d0 = X.tmem + sg * 128u + (k & 1u) * 64u;
+          if (st.cnt == (uint32_t)kStage4) {
+#pragma unroll
+            for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi)
+              umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
+          } else {
             for (uint32_t gi = 0; gi < st.cnt; ++gi)
               umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
-            umma_commit(&X.sh->b.mma_done[X.sa & 3u]);
           }
+          umma_commit(&X.sh->b.mma_done[sg][k & 1u]);
         }
-        __syncwarp();
-        ++X.s; ++X.sa;
-      } else if (drainer) {
-        X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 15);   // the slot's scales are visible to this thread
-        X.wait(&X.sh->b.mma_done[X.sa & 3u], (X.sa >> 2) & 1u, 16);
-        tc_fence_after_sync();
-        const float* sc_src = reinterpret_cast<const float*>(X.slot_ptr(X.s) + 2048) + col;
-        const uint32_t t0 = X.tmem + lane_base + (X.sa & 3u) * (kStage4 * 16u);
-        float sc[kStage4];
-        int32_t dsum[kStage4][MT == 1 ? 4 : 8];
+        PS_TRACE_STAGE(X, X.s, 4);
+      }
+      if (sg == 0u) ++X.mc0; else if (sg == 1u) ++X.mc1; else ++X.mc2;
+      if (st.seg_end && worker) {  // the run inside this tile (and round) ends: every warpgroup's part goes out
+        if (have_pending) { drain_request(); drain_collect(); }
+        flush(st.tile);
+      }
+    } else {
+      const uint32_t ii = X.s & 1u;  // issuer of this stage; warpgroup ii reads its sums out
+      if (issuer && ii == (uint32_t)issuer_idx) {
+        if (seg_mmas == 0 && X.sgc >= 1u) X.wait(&X.sh->b.seg_free[ii], (X.sgc - 1u) & 1u, 17);  // the previous run's sums are read out
+        X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 18);
+        PS_TRACE_STAGE(X, X.s, 3);
         if (!X.aborted()) {
-#pragma unroll
-          for (int gi = 0; gi < kStage4; ++gi) {
-            if ((uint32_t)gi < st.cnt) {
-              if constexpr (MT == 1) tmem_ld4(t0 + gi * 16u, dsum[gi]);
-              else tmem_ld8(t0 + gi * 16u, dsum[gi]);
-              sc[gi] = sc_src[gi * (kStreamRec4 / 4)];
-            }
+          tc_fence_after_sync();
+          constexpr uint32_t idesc = umma_idesc_i8(16, true);
+          const uint64_t ad = umma_desc_kmajor(smem_u32(X.slot_ptr(X.s)), 2048, 128);
+          const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
+          const uint32_t d0 = X.tmem + ii * 128u;
+          // consecutive MMAs go to kAcc8 different accumulators: one accumulator would make every MMA wait for the
+          // one before it, and a 128 x 16 x 32 MMA is all latency
+          for (uint32_t bi = 0; bi < st.cnt; ++bi) {
+            const uint32_t j = seg_mmas + bi;
+            umma_i8(d0 + (j & (kAcc8 - 1u)) * 16u, umma_desc_advance(ad, bi * 4096u), umma_desc_advance(bd, bi * kBRec), idesc, j >= kAcc8 ? 1u : 0u);
           }
-          tmem_ld_wait();
+          umma_commit(&X.sh->b.empty[slot]);  // the slot is free once these MMAs have read it
+          mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (X.lane == 0) { mbar_arrive(&X.sh->b.acc_free[X.sa & 3u]); mbar_arrive(&X.sh->b.empty[slot]); }
-        if (!X.aborted()) {
+        PS_TRACE_STAGE(X, X.s, 4);
+      }
+      // issuer ii and warpgroup ii count the MMAs of issuer ii's part of the run
+      const bool counts = (issuer_idx == (int)ii) || (worker && g == (int)ii);
+      if (counts) seg_mmas += st.cnt;
+    }
+    ++X.s;
+    if (!is4 && st.seg_end) {
+      // ---- int8: the run inside this tile ends ----
+      if (issuer_idx >= 0) {
+        if (seg_mmas > 0) {
+          if (issuer && !X.aborted()) umma_commit(&X.sh->b.seg_done[issuer_idx]);
+          ++X.sgc;
+        }
+        seg_mmas = 0;
+      } else if (worker && g < 2) {
+        if (seg_mmas > 0) {
+          X.wait(&X.sh->b.seg_done[g], X.sgc & 1u, 19);
+          ++X.sgc;
+          tc_fence_after_sync();
+          int32_t dg[4 * MT];
 #pragma unroll
-          for (int gi = 0; gi < kStage4; ++gi) {
-            if ((uint32_t)gi < st.cnt) {
-              const uint32_t mi = (st.ws + gi) * MT;
+          for (int t = 0; t < 4 * MT; ++t) dg[t] = 0;
+          if (!X.aborted()) {
+            const uint32_t nacc = min(seg_mmas, kAcc8);
+            constexpr int kBatch = MT == 1 ? (int)kAcc8 : (int)kAcc8 / 2;  // accumulators in registers at once
 #pragma unroll
-              for (int r = 0; r < MT; ++r) {
-                const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
-                acc[r] = fmaf((float)val, sc[gi] * X.mscale()[mi + r], acc[r]);
+            for (int a0 = 0; a0 < (int)kAcc8; a0 += kBatch) {
+              if ((uint32_t)a0 < nacc) {
+                int32_t part[kBatch][MT == 1 ? 4 : 8];
+#pragma unroll
+                for (int a = 0; a < kBatch; ++a) {
+                  if ((uint32_t)(a0 + a) < nacc) {
+                    if constexpr (MT == 1) tmem_ld4(X.tmem + lane_base + (uint32_t)g * 128u + (a0 + a) * 16u, part[a]);
+                    else tmem_ld8(X.tmem + lane_base + (uint32_t)g * 128u + (a0 + a) * 16u, part[a]);
+                  }
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int a = 0; a < kBatch; ++a)
+                  if ((uint32_t)(a0 + a) < nacc) {
+#pragma unroll
+                    for (int t = 0; t < 4 * MT; ++t) dg[t] += part[a][t];  // integer sums: exact
+                  }
               }
             }
           }
-        }
-        if (st.seg_end) flush(st.tile);
-        ++X.s; ++X.sa;
-      } else {
-        ++X.s; ++X.sa;
-      }
-    } else {
-      // int8: the ring slot is the A operand; one accumulator per run inside a tile
-      if (issuer) {
-        if (X.lane == 0) {
-          if (!seg_open && X.sg >= 2u) X.wait(&X.sh->b.seg_free[X.sg & 1u], ((X.sg >> 1) - 1u) & 1u, 17);
-          X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 18);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (X.lane == 0) mbar_arrive(&X.sh->b.seg_free[g]);  // the issuer may start its next run
           if (!X.aborted()) {
-            tc_fence_after_sync();
-            constexpr uint32_t idesc = umma_idesc_i8(16, true);
-            const uint64_t ad = umma_desc_kmajor(smem_u32(X.slot_ptr(X.s)), 2048, 128);
-            const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
-            const uint32_t d0 = X.tmem + (X.sg & 1u) * 16u;
-            for (uint32_t bi = 0; bi < st.cnt; ++bi)
-              umma_i8(d0, umma_desc_advance(ad, bi * 4096u), umma_desc_advance(bd, bi * kBRec), idesc, (seg_open || bi > 0) ? 1u : 0u);
-            umma_commit(&X.sh->b.empty[slot]);   // the slot is free once these MMAs have read it
-            mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]);
-            if (st.seg_end) umma_commit(&X.sh->b.seg_done[X.sg & 1u]);
-          }
-        }
-        __syncwarp();
-      } else if (drainer && st.seg_end) {
-        X.wait(&X.sh->b.seg_done[X.sg & 1u], (X.sg >> 1) & 1u, 19);
-        tc_fence_after_sync();
-        int32_t dg[8];
-        if (!X.aborted()) {
-          tmem_ld8(X.tmem + lane_base + (X.sg & 1u) * 16u, dg);
-          tmem_ld_wait();
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (X.lane == 0) mbar_arrive(&X.sh->b.seg_free[X.sg & 1u]);
-        if (!X.aborted()) {
 #pragma unroll
-          for (int r = 0; r < MT; ++r) {
-            float v = (float)dg[4 * r];
-            v = fmaf(v, 128.0f, (float)dg[4 * r + 1]);
-            v = fmaf(v, 128.0f, (float)dg[4 * r + 2]);
-            v = fmaf(v, 128.0f, (float)dg[4 * r + 3]);
-            acc[r] = v * X.sh->xscale[r];
+            for (int r = 0; r < MT; ++r) {
+              float v = (float)dg[4 * r];
+              v = fmaf(v, 128.0f, (float)dg[4 * r + 1]);
+              v = fmaf(v, 128.0f, (float)dg[4 * r + 2]);
+              v = fmaf(v, 128.0f, (float)dg[4 * r + 3]);
+              acc[r] = v * X.sh->xscale[r];
+            }
+            dirty = true;
           }
+          flush(st.tile);
         }
-        flush(st.tile);
+        seg_mmas = 0;
       }
-      seg_open = !st.seg_end;
-      if (st.seg_end) ++X.sg;
-      ++X.s;
     }
-    ++idx;
   }
-  (void)any;
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 3);
 }
 
 // ---- attention phase ----------------------------------------------------------------------------------
@@ -881,19 +1021,17 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
 template <int MT>
 __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t len) {
   const StepParams* P = X.c.sp;
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 0);
   if (p > 0) {
     bar_sync(1, kConsumers);
     if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
     bar_sync(1, kConsumers);
   }
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 1);
   AttnPlan ap;
   ap.init(X.c.m, P->KVl, P->splits, P->keys_per_stage, len);
-  if (X.warp < kWarpConv0) {  // the issuing warp only keeps the ring count in step
-    for (uint32_t item = blockIdx.x; item < ap.n_items; item += gridDim.x) X.s += ap.stages(item);
-    return;
-  }
   phase_duties<MT>(X, D);
-  const int ct = X.tid - kWarpConv0 * 32, cw = X.warp - kWarpConv0, lane = X.lane;
+  const int ct = X.tid - kWarpLeader * 32, cw = X.warp - kWarpLeader, lane = X.lane;
   const uint32_t hd = P->hd, half = hd / 2, rep = P->rep, nq4 = hd / 4, pos = len;
   float* qs = reinterpret_cast<float*>(X.bwin());   // [rep][hd]
   float* knew = qs + rep * hd;
@@ -917,7 +1055,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       const float o = e < half ? x1 * cs.x + (-x2) * cs.y : x2 * cs.x + x1 * cs.y;
       return poisoned ? __int_as_float(0x7fc00000) : o;
     };
-    for (uint32_t i = ct; i < rep * hd; i += kConverters) {
+    for (uint32_t i = ct; i < rep * hd; i += kConsumers) {
       const uint32_t r = i / hd, e = i - r * hd;
       qs[i] = rotated((kvh * rep + r) * hd, e);
     }
@@ -926,7 +1064,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       if (!room && ct == 0) atomicCAS(X.c.status, 0, 5);
       float* kd = D.kc + ((size_t)bk * P->cap + pos) * hd;
       float* vd = D.vc + ((size_t)bk * P->cap + pos) * hd;
-      for (uint32_t e = ct; e < hd; e += kConverters) {
+      for (uint32_t e = ct; e < hd; e += kConsumers) {
         const float kv = rotated(P->nq + kvh * hd, e);
         float vv = unfix(__ldcg(arow + P->nq + P->nkv + kvh * hd + e)) * rs;
         if (poisoned) vv = __int_as_float(0x7fc00000);
@@ -934,7 +1072,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
         if (room) { kd[e] = kv; vd[e] = vv; }
       }
     }
-    bar_sync(3, kConverters);
+    bar_sync(1, kConsumers);
     // this thread's outputs in the value step: head vr, elements 4 vc .. 4 vc + 3
     const bool vact = (uint32_t)ct < rep * nq4;
     const uint32_t vr = vact ? ct / nq4 : 0, vc = vact ? ct - vr * nq4 : 0;
@@ -975,7 +1113,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
           }
         }
       }
-      bar_sync(3, kConverters);
+      bar_sync(1, kConsumers);
       if (vact && !X.aborted()) {
         const bool with_new = j == 0 && owns_new;
         float M = run_m;
@@ -998,9 +1136,9 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
         }
         run_m = M; run_l = Ls; run_o = O;
       }
-      bar_sync(3, kConverters);
+      bar_sync(1, kConsumers);
       if (have) {
-        if (cw < 4 && lane == 0) mbar_arrive(&X.sh->b.empty[X.s % kSlots]);
+        if (cw < 4 && lane == 0) mbar_arrive(&X.sh->b.empty[X.s % kSlots]);  // count 4
         ++X.s;
       }
     }
@@ -1009,8 +1147,9 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       *reinterpret_cast<float4*>(rec + 4u * vc) = run_o;
       if (vc == 0) { rec[hd] = run_m; rec[hd + 1] = run_l; }
     }
-    bar_sync(3, kConverters);  // qs / knew are rewritten by the next item
+    bar_sync(1, kConsumers);  // qs / knew are rewritten by the next item
   }
+  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 3);
 }
 
 // ---- logits out, greedy pick ------------------------------------------------------------------------------
@@ -1021,16 +1160,15 @@ __device__ void final_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   bar_sync(1, kConsumers);
   if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
   bar_sync(1, kConsumers);
-  if (X.warp < kWarpConv0) return;
   phase_duties<MT>(X, D);
-  const int ct = X.tid - kWarpConv0 * 32, cw = X.warp - kWarpConv0;
+  const int ct = X.tid - kWarpLeader * 32, cw = X.warp - kWarpLeader;
   const uint32_t n = P->Vl;
   const uint32_t a = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
   for (uint32_t r = 0; r < X.c.m; ++r) {
     const float rs = X.sh->rstd[r];
     const bool poisoned = __ldcg(D.poison_in + r) != 0;
     int32_t bv = INT32_MIN, bj = -1;
-    for (uint32_t j = a + ct; j < b; j += kConverters) {
+    for (uint32_t j = a + ct; j < b; j += kConsumers) {
       float v = unfix(__ldcg(D.acc_in + (size_t)r * n + j)) * rs;
       if (poisoned) v = __int_as_float(0x7fc00000);
       P->logits[(size_t)r * n + j] = v;
@@ -1044,7 +1182,7 @@ __device__ void final_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
     }
     if (X.lane == 0) X.sh->arg[r][cw] = make_int2(bv, bj);
   }
-  bar_sync(3, kConverters);
+  bar_sync(1, kConsumers);
   if (ct < (int)X.c.m) {
     int2 best = X.sh->arg[ct][0];
     for (int w = 1; w < kConvWarps; ++w) {
@@ -1061,8 +1199,8 @@ __device__ void pick_phase(Ctx<MT>& X, uint32_t p) {
   bar_sync(1, kConsumers);
   if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, blockIdx.x == 0);
   bar_sync(1, kConsumers);
-  if (blockIdx.x != 0 || X.warp < kWarpConv0 || X.aborted()) return;
-  const int cw = X.warp - kWarpConv0;
+  if (blockIdx.x != 0 || X.aborted()) return;
+  const int cw = X.warp - kWarpLeader;
   if (cw < (int)X.c.m && P->want_argmax) {
     int32_t bv = INT32_MIN, bj = -1;
     for (uint32_t t = X.lane; t < gridDim.x; t += 32) {
@@ -1085,11 +1223,10 @@ __device__ void out_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   bar_sync(1, kConsumers);
   if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
   bar_sync(1, kConsumers);
-  if (X.warp < kWarpConv0) return;
-  const int ct = X.tid - kWarpConv0 * 32;
+  const int ct = X.tid - kWarpLeader * 32;
   const uint32_t total = X.c.m * D.n;
   const uint32_t a = (uint32_t)((uint64_t)total * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)total * (blockIdx.x + 1) / gridDim.x);
-  for (uint32_t i = a + ct; i < b; i += kConverters) {
+  for (uint32_t i = a + ct; i < b; i += kConsumers) {
     float v = unfix(__ldcg(D.acc_in + i));
     if (__ldcg(D.poison_in + i / D.n)) v = __int_as_float(0x7fc00000);
     X.c.out[i] = v;
@@ -1102,17 +1239,16 @@ __device__ void run_program(const Prog& prog, const Common& cm, unsigned char* s
   Ctx<MT> X;
   X.smem = smem; X.sh = sh; X.c = cm;
   X.tid = threadIdx.x; X.lane = X.tid & 31; X.warp = X.tid >> 5;
-  X.s = 0; X.sa = 0; X.sg = 0;
+  X.s = 0; X.mc0 = 0; X.mc1 = 0; X.mc2 = 0; X.sgc = 0; X.cur_phase = 0;
   if (X.tid == 0) {
     for (int i = 0; i < kSlots; ++i) { mbar_init(&sh->b.full[i], 1); mbar_init(&sh->b.empty[i], 4); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh->b.a_ready[i], 8); mbar_init(&sh->b.seg_done[i], 1); mbar_init(&sh->b.seg_free[i], 4); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&sh->b.mma_done[i], 1); mbar_init(&sh->b.acc_free[i], 4); }
-    mbar_init(&sh->b.fin, 1);
+    for (int i = 0; i < kGroups; ++i) { mbar_init(&sh->b.a_ready[i][0], 4); mbar_init(&sh->b.a_ready[i][1], 4); mbar_init(&sh->b.mma_done[i][0], 1); mbar_init(&sh->b.mma_done[i][1], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh->b.seg_done[i], 1); mbar_init(&sh->b.seg_free[i], 4); mbar_init(&sh->b.fin[i], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     sh->abort = 0;
   }
   __syncwarp();
-  if (X.warp == kWarpIssuer) tmem_alloc(&sh->tmem, kTmemCols);
+  if (X.warp == kWarpLeader) tmem_alloc(&sh->tmem, kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -1140,14 +1276,15 @@ __device__ void run_program(const Prog& prog, const Common& cm, unsigned char* s
     }
     // every MMA has completed before the tensor memory goes back (normally their sums were all read long ago; a CTA
     // that gave up may still have some in flight)
-    if (X.warp == kWarpIssuer && X.lane == 0) {
-      umma_commit(&sh->b.fin);
-      mbar_wait(&sh->b.fin, 0);
+    if ((X.warp == kWarpLeader || X.warp == kWarpIssuer1) && X.lane == 0) {
+      const int ii = X.warp == kWarpLeader ? 0 : 1;
+      umma_commit(&sh->b.fin[ii]);
+      mbar_wait(&sh->b.fin[ii], 0);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (X.warp == kWarpIssuer) tmem_dealloc(X.tmem, kTmemCols);
+  if (X.warp == kWarpLeader) tmem_dealloc(X.tmem, kTmemCols);
 }
 
 // The parameter block is copied into shared memory once and used from there; nothing takes the address of the
@@ -1166,7 +1303,7 @@ __global__ void __launch_bounds__(kThreads, 1) pstep_kernel(const StepParams Pin
   __syncthreads();
   Common cm;
   cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
-  cm.sp = &P; cm.out = nullptr;
+  cm.sp = &P; cm.out = nullptr; cm.trace = P.trace;
   StepProgram prog{P, lay};
   run_program<MT>(prog, cm, smem, &sh, len);
 }
@@ -1180,7 +1317,7 @@ __global__ void __launch_bounds__(kThreads, 1) pgemv_kernel(const GemvTestParams
   __syncthreads();
   Common cm;
   cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
-  cm.sp = nullptr; cm.out = P.out;
+  cm.sp = nullptr; cm.out = P.out; cm.trace = P.trace;
   TestProgram prog{P};
   run_program<MT>(prog, cm, smem, &sh, 0u);
 }
@@ -1214,21 +1351,34 @@ int ruai_pstep_grid(ruai_ctx* c) {
   static int cached[64] = {};
   int& g = cached[c->ordinal & 63];
   if (g) return g > 0 ? g : 0;
+  g = -1;
   const size_t smem = ps::smem_bytes(ps::kMaxLayers);
-  for (auto k : {(const void*)ps::pstep_kernel<1>, (const void*)ps::pstep_kernel<2>, (const void*)ps::pgemv_kernel<1>, (const void*)ps::pgemv_kernel<2>})
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); g = -1; return 0; }
+  for (auto k : {(const void*)ps::pstep_kernel<1>, (const void*)ps::pstep_kernel<2>, (const void*)ps::pgemv_kernel<1>, (const void*)ps::pgemv_kernel<2>}) {
+    const cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      ruai_fail(c, RUAI_ERR_UNSUPPORTED, "persistent kernel: %zu bytes of dynamic shared memory refused (%s)", smem, cudaGetErrorString(e));
+      return 0;
+    }
+  }
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ps::pstep_kernel<2>, ps::kThreads, smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); g = -1; return 0; }
+  const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ps::pstep_kernel<2>, ps::kThreads, smem);
+  if (e != cudaSuccess || per_sm < 1) {
+    cudaGetLastError();
+    ruai_fail(c, RUAI_ERR_UNSUPPORTED, "persistent kernel: occupancy %d with %d threads and %zu bytes of shared memory (%s)", per_sm, ps::kThreads, smem,
+              cudaGetErrorString(e));
+    return 0;
+  }
   int coop = 0;
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c->ordinal);
-  if (!coop) { g = -1; return 0; }
+  if (!coop) { ruai_fail(c, RUAI_ERR_UNSUPPORTED, "persistent kernel: the device has no cooperative launch"); return 0; }
   g = c->sm_count;
   return g;
 }
 
 int ruai_pstep_launch(ruai_ctx* c, const ps::StepParams& p) {
   const int grid = ruai_pstep_grid(c);
-  if (grid <= 0) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent decode kernel cannot be resident on this device");
+  if (grid <= 0) return RUAI_ERR_UNSUPPORTED;  // the reason is in the context's error text
   if (p.L > (uint32_t)ps::kMaxLayers) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent decode kernel takes at most %d layers", ps::kMaxLayers);
   ps::StepParams q = p;
   return p.m <= 1 ? ps::launch_coop(c, ps::pstep_kernel<1>, grid, ps::smem_bytes(p.L), &q)
@@ -1237,7 +1387,7 @@ int ruai_pstep_launch(ruai_ctx* c, const ps::StepParams& p) {
 
 int ruai_pgemv_launch(ruai_ctx* c, const ps::GemvTestParams& p) {
   const int grid = ruai_pstep_grid(c);
-  if (grid <= 0) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent decode kernel cannot be resident on this device");
+  if (grid <= 0) return RUAI_ERR_UNSUPPORTED;
   ps::GemvTestParams q = p;
   return p.m <= 1 ? ps::launch_coop(c, ps::pgemv_kernel<1>, grid, ps::smem_bytes(0), &q)
                   : ps::launch_coop(c, ps::pgemv_kernel<2>, grid, ps::smem_bytes(0), &q);
@@ -1253,7 +1403,7 @@ RUAI_API int ruai_matmul_q_stream(ruai_ctx* c, const float* x_dev, const ruai_qw
   if (!ruai_sweight_supported(w)) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "ruai_matmul_q_stream takes int8 or int4 group-32 weights with k a multiple of 4");
   DeviceGuard g(c->ordinal);
   const int grid = ruai_pstep_grid(c);
-  if (grid <= 0) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the persistent kernel cannot be resident on this device");
+  if (grid <= 0) return RUAI_ERR_UNSUPPORTED;  // the reason is in the context's error text
   if (!w->stream) {
     w->stream = new ruai_sweight();
     const int rc = ruai_sweight_create(c, w, w->stream);
@@ -1275,6 +1425,7 @@ RUAI_API int ruai_matmul_q_stream(ruai_ctx* c, const float* x_dev, const ruai_qw
   P.x = x_dev; P.acc = reinterpret_cast<long long*>(c->partial); P.poison = reinterpret_cast<int*>(c->ps_sync + 2); P.out = out_dev;
   P.bar = c->ps_sync; P.bar_base = c->ps_bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status;
   P.abort_flag = reinterpret_cast<int*>(c->ps_sync + 1); P.spin_limit = c->spin_limit;
+  P.trace = c->trace;
   c->barrier_skew = 0;
   RUAI_TRY(ruai_pgemv_launch(c, P));
   c->ps_bar_base += (2u * repeat - 1u) * (unsigned)grid;

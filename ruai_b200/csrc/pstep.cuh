@@ -20,6 +20,7 @@ struct ruai_sweight {
 };
 
 constexpr uint32_t kStreamTileCols = 128;
+constexpr uint32_t kRingSlotBytes = 12288;  // one ring stage of the persistent kernel: 4 int4 groups (10240 B), 3 int8 blocks, or K + V rows
 constexpr uint32_t kStreamRec4 = 2560, kStreamRec8 = 4096;
 
 bool ruai_sweight_supported(const ruai_qweight* w);
@@ -29,7 +30,7 @@ void ruai_sweight_free(ruai_sweight* s);
 namespace ps {
 
 constexpr int kMaxRows = 2;    // sequences per step the persistent kernel takes
-constexpr int kMaxLayers = 80;  // layer pointer table kept in shared memory
+constexpr int kMaxLayers = 64;  // layer pointer table kept in shared memory
 
 // Accumulators of the split-k sums are 64-bit fixed point (value * 2^36): integer adds commute, so the
 // result does not depend on the order in which CTAs (or GPUs) deliver their parts.
@@ -69,6 +70,7 @@ struct StepParams {
   int* abort_flag;          // set by the first CTA that gives up; everyone else leaves at its next wait
   unsigned spin_limit;      // polls of a grid-barrier wait
   int want_argmax;
+  unsigned long long* trace;  // profiling builds (RUAI_B200_TRACE): per-stage clock stamps of CTA 0, else unused
 };
 
 // One generic quantized GEMV as its own (test / microbenchmark) program: out[m][n] = x[m][k] @ W.
@@ -81,6 +83,7 @@ struct GemvTestParams {
   int* poison;           // [kMaxRows]
   float* out;            // f32 [m][n]
   unsigned* bar; unsigned bar_base; int* status; int* abort_flag; unsigned spin_limit;
+  unsigned long long* trace;
 };
 
 }  // namespace ps

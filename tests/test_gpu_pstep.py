@@ -55,6 +55,7 @@ SHAPES = [
     (4096, 4096),    # o_proj of the 8B shape
     (4096, 6144),    # q/k/v of the 8B shape
     (14336, 4096),   # down_proj: k beyond the digit window (int4: 448 groups)
+    (512, 20000),    # many tiles per CTA: runs of whole tiles and the accumulator rotation
 ]
 
 
@@ -269,7 +270,8 @@ def test_cache_clear_then_decode_step_with_a_new_batch(dev):
     gm.cache_clear()
     om.cache_clear()
     ids = np.array([3, 9], np.int32)
-    nxt = gm.decode_step(2, nn.Tensor.from_numpy(dev, ids).ptr)
+    ids_dev = nn.Tensor.from_numpy(dev, ids)
+    nxt = gm.decode_step(2, ids_dev.ptr)
     want = om.forward_cached(ids[:, None])
     assert nxt.tolist() == [oracle.argmax(r) for r in want]
     assert gm.cache_len() == 1
