@@ -677,8 +677,8 @@ int pstep_run(ruai_model* m, uint32_t B) {
     S.acc_elems = (size_t)MR * ((size_t)nqkv + d + 2 * (size_t)m->fl + d + m->Vl);
     RUAI_TRY(S.acc.alloc(c, S.acc_elems * sizeof(long long)));
     RUAI_TRY(S.poison.alloc(c, 5 * MR * sizeof(int)));
-    RUAI_TRY(S.sync.alloc(c, 64));
-    RUAI_TRY(S.x.alloc(c, 2 * (size_t)MR * d * sizeof(float)));
+    RUAI_TRY(S.sync.alloc(c, 64 + (size_t)MR * m->KVl * sizeof(unsigned)));  // barrier counter, abort flag; from byte 64: attention item counters
+    RUAI_TRY(S.x.alloc(c, (2 * (size_t)MR * d + (size_t)MR * nq) * sizeof(float)));
     RUAI_TRY(S.ss.alloc(c, 3 * (size_t)MR * (d / 32) * sizeof(float)));
     RUAI_TRY(S.arg_slots.alloc(c, (size_t)grid * MR * sizeof(int2)));
     RUAI_TRY(S.layers.alloc(c, (size_t)m->L * sizeof(ps::LayerPtrs)));
@@ -725,6 +725,8 @@ int pstep_run(ruai_model* m, uint32_t B) {
   P.acc_logits = a;
   P.poison = S.poison.as<int>();
   P.att_part = S.att_part.as<float>();
+  P.att_out = P.x1 + (size_t)MR * d;
+  P.att_cnt = S.sync.as<unsigned>() + 16;
   P.logits = m->logits.as<float>();
   P.arg_slots = S.arg_slots.as<int2>();
   P.bar = S.sync.as<unsigned>(); P.bar_base = S.bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status; P.abort_flag = S.sync.as<int>() + 1;

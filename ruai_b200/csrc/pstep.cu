@@ -36,6 +36,12 @@
 #include "pipeline.cuh"
 #include "pstep.cuh"
 
+#ifndef PS_POLL_SPECIAL
+#define PS_POLL_SPECIAL 0
+#endif
+#ifndef PS_SLEEP_NS
+#define PS_SLEEP_NS 40
+#endif
 namespace ps {
 
 using namespace pipe;
@@ -66,7 +72,7 @@ constexpr size_t kOffMeta = kOffBWin + (size_t)kWin * kBRec;
 constexpr size_t kOffLayers = kOffMeta + (size_t)kWin * kMaxRows * 8;
 
 enum { PH_GEMV = 0, PH_ATTN = 1, PH_FINAL = 2, PH_PICK = 3, PH_OUT = 4 };
-enum { LD_PLAIN = 0, LD_EMBED = 1, LD_RESID = 2, LD_ATTN = 3, LD_SWIGLU = 4 };
+enum { LD_PLAIN = 0, LD_EMBED = 1, LD_RESID = 2, LD_SWIGLU = 3 };
 
 struct PhaseDesc {
   int type;
@@ -86,21 +92,39 @@ struct PhaseDesc {
   float* kc; float* vc;
 };
 
+// What the kernel needs from its parameter block whichever program it runs.
+struct Common {
+  uint32_t m;
+  unsigned* bar; unsigned bar_base; int* status; int* abort_flag; unsigned spin_limit;
+  // attention / final (step program only)
+  const StepParams* sp;
+  float* out;  // test program: f32 [m][n]
+  unsigned long long* trace;
+};
+
 struct Bars {
   uint64_t full[kSlots], empty[kSlots];
   uint64_t a_ready[kGroups][2];   // a warpgroup's A buffer 0 / 1 is written (its 4 warps arrive); one barrier per buffer,
                                   // because a warpgroup may be a stage ahead of the issuer
   uint64_t mma_done[kGroups][2];  // the MMAs of a warpgroup's stage into accumulator buffer 0 / 1 have completed
-  uint64_t seg_done[2];           // int8: the MMAs of an issuer's part of a run have completed
-  uint64_t seg_free[2];           // int8: its sums are read out (the 4 warps of warpgroup 0 / 1 arrive)
+  uint64_t seg_done[2][2];        // int8: the MMAs of an issuer's part of a run (into accumulator set 0 / 1) have completed
+  uint64_t seg_free[2][2];        // int8: the sums of that set are read out (the 4 warps of warpgroup 0 / 1 arrive)
   uint64_t fin[2];                // every MMA of an issuer has completed (before the tensor memory goes back)
 };
 
+// The phase descriptors and the common parameters live in shared memory: with nearly all of the SM's memory configured
+// as shared memory the L1 is small, per-thread stack slots fall out of it, and each later touch of one costs a trip to L2.
 struct Shared {
   Bars b;
+  PhaseDesc D[3];             // the consumers' phase p descriptor is D[p % 3], written during phase p - 1 by a spare lane
+  PhaseDesc Dp;               // the producer's (it runs ahead)
+  Common c;
+  uint2 rec[kSlots];          // per ring slot, left by the producer: x = tile, y = window slot | blocks << 16
+  uint32_t wgrec[kGroups][2]; // per A buffer, left by the warpgroup for the issuer: window slot | blocks << 16
+  uint4 segrec[2][2];         // int8, per issuer and accumulator set: x = tile, y = MMAs of the run, z = last run of the round
   uint32_t tmem;
   volatile int abort;
-  float rstd[kMaxRows];
+  int att_last;                // attention: this CTA completed its item and merges the splits
   float wmax[kMaxRows][kConvWarps];
   float xscale[kMaxRows];
   int2 arg[kMaxRows][kConvWarps];
@@ -240,7 +264,7 @@ struct StepProgram {
         case 2:  // o_proj on the merged attention output
           D.type = PH_GEMV; D.w = Y.w_o; D.colscale = Y.s_o;
           D.ntiles = P.o.ntiles; D.nblk = P.o.nblk; D.n = P.o.n; D.k = P.o.k;
-          D.loader = LD_ATTN; D.in_ld = P.nq;
+          D.loader = LD_PLAIN; D.x_in = P.att_out; D.in_ld = P.nq;
           D.acc_out = P.acc_o; D.poison_out = P.poison + 1 * MT;
           D.zero0 = P.acc_dn; D.zero0_n = P.m * P.d; D.zero0_poison = P.poison + 3 * MT;
           break;
@@ -298,16 +322,6 @@ struct TestProgram {
   }
 };
 
-// What the kernel needs from its parameter block whichever program it runs.
-struct Common {
-  uint32_t m;
-  unsigned* bar; unsigned bar_base; int* status; int* abort_flag; unsigned spin_limit;
-  // attention / final (step program only)
-  const StepParams* sp;
-  float* out;  // test program: f32 [m][n]
-  unsigned long long* trace;
-};
-
 // Profiling builds only (-DRUAI_B200_TRACE): CTA 0 stamps its SM clock at the hand-overs of the first stages.
 // Layout: stage events [kTraceStages][8], then phase events [kTracePhases][4].
 constexpr uint32_t kTraceStages = 192, kTracePhases = 192;
@@ -337,13 +351,14 @@ template <int MT>
 struct Ctx {
   unsigned char* smem;
   Shared* sh;
-  Common c;
+  const Common& c;
   int tid, lane, warp;
   uint32_t cur_phase;
   uint32_t s;    // ring stages so far (all kinds, all warpgroups)
   uint32_t mc0, mc1, mc2;  // int4 stages of warpgroup 0 / 1 / 2 so far (every consumer thread keeps all three)
   uint32_t sgc;  // int8 runs closed so far (issuer i and warpgroup i count the same runs)
   uint32_t tmem;
+  __device__ Ctx(unsigned char* smem_, Shared* sh_) : smem(smem_), sh(sh_), c(sh_->c) {}
 
   __device__ unsigned char* slot_ptr(uint32_t stage) const { return smem + kOffSlots + (size_t)(stage % kSlots) * kSlotBytes; }
   __device__ unsigned char* abuf_ptr(uint32_t wg, uint32_t k) const { return smem + kOffABuf + (size_t)(2u * wg + (k & 1u)) * kABufBytes; }
@@ -372,7 +387,13 @@ struct Ctx {
     // otherwise poll with a short sleep in between: a suspending try_wait was seen to wake up more than a thousand cycles
     // after the barrier completed, and a tight polling loop takes the issue slots of the warps it waits for
     for (unsigned i = 0; i < c.spin_limit; ++i) {
-      __nanosleep(40);
+#if PS_POLL_SPECIAL == 1
+      if (warp > 2) __nanosleep(PS_SLEEP_NS);
+#elif PS_POLL_SPECIAL == 2
+      if (warp > 2) { if (i > 4) __nanosleep(PS_SLEEP_NS); }
+#else
+      __nanosleep(PS_SLEEP_NS);
+#endif
       asm volatile(
           "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(ok)
@@ -403,15 +424,26 @@ __device__ void grid_barrier(Ctx<MT>& X, uint32_t p, bool wait_for_it) {
 
 // ---- loaders: the activations of one group of 32 as the consuming phase needs them -----------------
 
+// The phase's 1/rms factors (functional.rs:151-165: 1 / sqrt(mean(x^2) + eps)) from the per-group sums of squares, in
+// a fixed order.  Every warp works them out for itself (same loads, same order, same result): no shared memory, no
+// barrier, and the loads overlap with whatever the warp has in flight.
 template <int MT>
-struct Loaded {
-  float4 v[MT];   // values the digits are taken from (before the RMSNorm weight)
-  bool valid;
-};
+__device__ __forceinline__ void warp_rstd(const Ctx<MT>& X, const PhaseDesc& D, float (&rs)[MT]) {
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    float s = 0.0f;
+    if ((uint32_t)r < X.c.m)
+      for (uint32_t i = X.lane; i < D.ss_groups; i += 32) s += __ldcg(D.ss_in + (size_t)r * D.ss_groups + i);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+    rs[r] = 1.0f / sqrtf(s * (1.0f / D.ss_dim) + X.c.sp->eps);
+  }
+}
 
-// This lane's four values (k = 32 g + 4 l8 ...) of every row.
+// This lane's four values (k = 32 g + 4 l8 ...) of every row, as the digits are taken from them (before the RMSNorm weight).
 template <int MT>
-__device__ __forceinline__ void load_group(const Ctx<MT>& X, const PhaseDesc& D, uint32_t g, uint32_t l8, float4 (&v)[MT]) {
+__device__ __forceinline__ void load_group(const Ctx<MT>& X, const PhaseDesc& D, uint32_t g, uint32_t l8, const float (&rs)[MT], const bool (&poisoned)[MT],
+                                           float4 (&v)[MT]) {
   const uint32_t m = X.c.m;
   const uint32_t kidx = g * 32u + 4u * l8;
   const StepParams* P = X.c.sp;
@@ -434,38 +466,17 @@ __device__ __forceinline__ void load_group(const Ctx<MT>& X, const PhaseDesc& D,
           const longlong2* a = reinterpret_cast<const longlong2*>(D.acc_in + (size_t)r * D.in_ld + kidx);
           const longlong2 a0 = __ldcg(a), a1 = __ldcg(a + 1);
           o = make_float4(xv.x + unfix(a0.x), xv.y + unfix(a0.y), xv.z + unfix(a1.x), xv.w + unfix(a1.y));
-          if (__ldcg(D.poison_in + r)) o.x = __int_as_float(0x7fc00000);
+          if (poisoned[r]) o.x = __int_as_float(0x7fc00000);
           break;
         }
-        case LD_SWIGLU: {  // silu(gate) * up (layers.rs:573-576); columns (2i, 2i+1) = (gate_i, up_i)
+        default: {  // LD_SWIGLU: silu(gate) * up (layers.rs:573-576); columns (2i, 2i+1) = (gate_i, up_i)
           const longlong2* a = reinterpret_cast<const longlong2*>(D.acc_in + (size_t)r * D.in_ld + 2u * kidx);
-          const float rs = X.sh->rstd[r];
           const longlong2 a0 = __ldcg(a), a1 = __ldcg(a + 1), a2 = __ldcg(a + 2), a3 = __ldcg(a + 3);
-          o.x = silu_ref(unfix(a0.x) * rs) * (unfix(a0.y) * rs);
-          o.y = silu_ref(unfix(a1.x) * rs) * (unfix(a1.y) * rs);
-          o.z = silu_ref(unfix(a2.x) * rs) * (unfix(a2.y) * rs);
-          o.w = silu_ref(unfix(a3.x) * rs) * (unfix(a3.y) * rs);
-          if (__ldcg(D.poison_in + r)) o.x = __int_as_float(0x7fc00000);
-          break;
-        }
-        default: {  // LD_ATTN: merge the key splits of this head (softmax statistics of every split)
-          const uint32_t hd = P->hd, hq = kidx / hd, e = kidx - hq * hd;
-          const uint32_t kvh = hq / P->rep, hr = hq - kvh * P->rep, S = P->splits, stride = hd + 4u;
-          const float* base = P->att_part + ((size_t)((r * P->KVl + kvh) * S) * P->rep + hr) * stride;
-          float M = -INFINITY;
-          for (uint32_t s2 = 0; s2 < S; ++s2) M = fmaxf(M, __ldcg(base + (size_t)s2 * P->rep * stride + hd));
-          float Lsum = 0.0f;
-          for (uint32_t s2 = 0; s2 < S; ++s2) {
-            const float* rec = base + (size_t)s2 * P->rep * stride;
-            const float ms = __ldcg(rec + hd);
-            if (ms == -INFINITY) continue;
-            const float wgt = expf(ms - M);
-            const float4 ov = __ldcg(reinterpret_cast<const float4*>(rec + e));
-            Lsum = fmaf(__ldcg(rec + hd + 1), wgt, Lsum);
-            o.x = fmaf(ov.x, wgt, o.x); o.y = fmaf(ov.y, wgt, o.y); o.z = fmaf(ov.z, wgt, o.z); o.w = fmaf(ov.w, wgt, o.w);
-          }
-          const float inv = 1.0f / Lsum;
-          o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+          o.x = silu_ref(unfix(a0.x) * rs[r]) * (unfix(a0.y) * rs[r]);
+          o.y = silu_ref(unfix(a1.x) * rs[r]) * (unfix(a1.y) * rs[r]);
+          o.z = silu_ref(unfix(a2.x) * rs[r]) * (unfix(a2.y) * rs[r]);
+          o.w = silu_ref(unfix(a3.x) * rs[r]) * (unfix(a3.y) * rs[r]);
+          if (poisoned[r]) o.x = __int_as_float(0x7fc00000);
           break;
         }
       }
@@ -545,73 +556,103 @@ __device__ __forceinline__ void digits8(const Ctx<MT>& X, const float4 (&xv)[MT]
   }
 }
 
+// One pass of a converter warp: four groups (8 lanes each) loaded as the phase's loader says; the loader that builds x
+// also writes it back and leaves the group's sum of squares, for the groups whose (tile 0, group) unit belongs to this
+// CTA (exactly one CTA per group); then the RMSNorm weight.  Returns the window slot of the lane's group.
+template <int MT>
+__device__ __forceinline__ uint32_t load_pass(const Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, uint32_t blk0, uint32_t cnt, uint32_t i,
+                                              const float (&rs)[MT], const bool (&poisoned)[MT], float4 (&xv)[MT], bool& valid) {
+  const int lane = X.lane;
+  const uint32_t l8 = lane & 7u, m = X.c.m;
+  valid = i < cnt;
+  uint32_t g = blk0 + i;
+  if (g >= D.nblk) g -= D.nblk;
+  const uint32_t ws = it.windowed ? i : g;
+  if (!valid) {
+#pragma unroll
+    for (int r = 0; r < MT; ++r) xv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    return ws;
+  }
+  // the weight's load goes out with the others, not after them
+  float4 nw = make_float4(1.f, 1.f, 1.f, 1.f);
+  if (D.norm_w) nw = __ldg(reinterpret_cast<const float4*>(D.norm_w + g * 32u + 4u * l8));
+  load_group<MT>(X, D, g, l8, rs, poisoned, xv);
+  if (D.ss_out) {
+    const bool owner = g >= it.u0 && g < it.u1;
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+      const float4 o = xv[r];
+      float q = fmaf(o.x, o.x, fmaf(o.y, o.y, fmaf(o.z, o.z, o.w * o.w)));
+      q += __shfl_xor_sync(0xFFu << (lane & 24), q, 1);
+      q += __shfl_xor_sync(0xFFu << (lane & 24), q, 2);
+      q += __shfl_xor_sync(0xFFu << (lane & 24), q, 4);
+      if (owner && (uint32_t)r < m) {
+        if (D.x_out) *reinterpret_cast<float4*>(D.x_out + (size_t)r * D.in_ld + g * 32u + 4u * l8) = o;
+        if (l8 == 0) D.ss_out[(size_t)r * (D.k / 32u) + g] = q;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < MT; ++r) { xv[r].x *= nw.x; xv[r].y *= nw.y; xv[r].z *= nw.z; xv[r].w *= nw.w; }
+  return ws;
+}
+
 // Writes the digits of one round (all consumer warps call it).
 template <int MT>
-__device__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, uint32_t blk0, uint32_t cnt) {
+__device__ __forceinline__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, uint32_t blk0, uint32_t cnt) {
   const int cw = X.warp - kWarpLeader, lane = X.lane;
-  const uint32_t sgi = lane >> 3, l8 = lane & 7u, m = X.c.m;
+  const uint32_t sgi = lane >> 3;
   constexpr int kPasses = (kWin + 4 * kConvWarps - 1) / (4 * kConvWarps);  // every consumer warp converts 4 groups per pass
-  float4 xv[kPasses][MT];
-  uint32_t wsl[kPasses];
-  bool val[kPasses];
-  const bool normed = D.norm_w != nullptr;
+  float rs[MT];
+  bool poisoned[MT];
 #pragma unroll
-  for (int ps = 0; ps < kPasses; ++ps) {
-    const uint32_t i = 4u * (uint32_t)(cw + kConvWarps * ps) + sgi;
-    val[ps] = i < cnt;
-    uint32_t g = blk0 + i;
-    if (g >= D.nblk) g -= D.nblk;
-    wsl[ps] = it.windowed ? i : g;
-    if (!val[ps]) {
+  for (int r = 0; r < MT; ++r) { rs[r] = 0.0f; poisoned[r] = false; }
+  if (D.poison_in) {
 #pragma unroll
-      for (int r = 0; r < MT; ++r) xv[ps][r] = make_float4(0.f, 0.f, 0.f, 0.f);
-      continue;
+    for (int r = 0; r < MT; ++r) poisoned[r] = (uint32_t)r < X.c.m && __ldcg(D.poison_in + r) != 0;
+  }
+  if (D.ss_in) warp_rstd<MT>(X, D, rs);
+  if (D.bits == 4) {
+#pragma unroll 1
+    for (int ps = 0; ps < kPasses; ++ps) {
+      if (4u * (uint32_t)(cw + kConvWarps * ps) >= cnt) break;  // warp-uniform
+      float4 xv[MT];
+      bool valid;
+      const uint32_t ws = load_pass<MT>(X, D, it, blk0, cnt, 4u * (uint32_t)(cw + kConvWarps * ps) + sgi, rs, poisoned, xv, valid);
+      digits4<MT>(X, xv, ws, lane, valid);
     }
-    load_group<MT>(X, D, g, l8, xv[ps]);
-    // the loader that builds x also owns writing it back and leaving the group's sum of squares, for the
-    // groups whose (tile 0, group) unit belongs to this CTA: exactly one CTA per group
-    if (D.ss_out) {
-      const bool owner = g >= it.u0 && g < it.u1;
+  } else {
+    // One exponent per row for the whole window, so two sweeps: the values go into shared memory as they are (a lane's
+    // four f32 of a row take exactly the room of its four digit words), then each lane turns its own words into digits.
+    float mx[MT];
+    bool bad[MT];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) { mx[r] = 0.0f; bad[r] = false; }
+    const uint32_t l8 = lane & 7u;
+#pragma unroll 1
+    for (int ps = 0; ps < kPasses; ++ps) {
+      if (4u * (uint32_t)(cw + kConvWarps * ps) >= cnt) break;  // warp-uniform
+      float4 xv[MT];
+      bool valid;
+      const uint32_t ws = load_pass<MT>(X, D, it, blk0, cnt, 4u * (uint32_t)(cw + kConvWarps * ps) + sgi, rs, poisoned, xv, valid);
+      unsigned char* bg = X.bwin() + (size_t)ws * kBRec + (l8 >> 2) * 128u + ((4u * l8) & 15u);
 #pragma unroll
       for (int r = 0; r < MT; ++r) {
-        const float4 o = xv[ps][r];
-        float q = fmaf(o.x, o.x, fmaf(o.y, o.y, fmaf(o.z, o.z, o.w * o.w)));
-        q += __shfl_xor_sync(0xFFu << (lane & 24), q, 1);
-        q += __shfl_xor_sync(0xFFu << (lane & 24), q, 2);
-        q += __shfl_xor_sync(0xFFu << (lane & 24), q, 4);
-        if (owner && (uint32_t)r < m) {
-          if (D.x_out) *reinterpret_cast<float4*>(D.x_out + (size_t)r * D.in_ld + g * 32u + 4u * l8) = o;
-          if (l8 == 0) D.ss_out[(size_t)r * (D.k / 32u) + g] = q;
+        const float4 o = xv[r];
+        mx[r] = fmaxf(mx[r], fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+        bad[r] = bad[r] || !(finite_f(o.x) && finite_f(o.y) && finite_f(o.z) && finite_f(o.w));
+        if (valid) {
+          *reinterpret_cast<float*>(bg + (4 * r + 0) * 16) = o.x;
+          *reinterpret_cast<float*>(bg + (4 * r + 1) * 16) = o.y;
+          *reinterpret_cast<float*>(bg + (4 * r + 2) * 16) = o.z;
+          *reinterpret_cast<float*>(bg + (4 * r + 3) * 16) = o.w;
         }
       }
     }
-    if (normed) {
-      const float4 nw = __ldg(reinterpret_cast<const float4*>(D.norm_w + g * 32u + 4u * l8));
-#pragma unroll
-      for (int r = 0; r < MT; ++r) { xv[ps][r].x *= nw.x; xv[ps][r].y *= nw.y; xv[ps][r].z *= nw.z; xv[ps][r].w *= nw.w; }
-    }
-  }
-  if (D.bits == 4) {
-#pragma unroll
-    for (int ps = 0; ps < kPasses; ++ps) {
-      if (4u * (uint32_t)(cw + kConvWarps * ps) >= cnt) break;  // warp-uniform
-      digits4<MT>(X, xv[ps], wsl[ps], lane, val[ps]);
-    }
-  } else {
     // row maxima over the window: warp part, then across the converter warps
-    float mx[MT];
-    bool bad = false;
 #pragma unroll
     for (int r = 0; r < MT; ++r) {
-      mx[r] = 0.0f;
-#pragma unroll
-      for (int ps = 0; ps < kPasses; ++ps) {
-        const float4 o = xv[ps][r];
-        mx[r] = fmaxf(mx[r], fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
-        bad = bad || !(finite_f(o.x) && finite_f(o.y) && finite_f(o.z) && finite_f(o.w));
-      }
-      if (bad) mx[r] = INFINITY;
-      bad = false;
+      if (bad[r]) mx[r] = INFINITY;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], off));
       if (lane == 0) X.sh->wmax[r][cw] = mx[r];
@@ -628,14 +669,28 @@ __device__ void convert_round(Ctx<MT>& X, const PhaseDesc& D, const StageIter& i
       up[r] = nz ? __uint_as_float((280u - eb) << 23) : 0.0f;
       if (cw == 0 && lane == 0) X.sh->xscale[r] = eb == 255u ? __int_as_float(0x7fc00000) : (nz ? __uint_as_float((eb - 26u) << 23) : 0.0f);
     }
+#pragma unroll 1
+    for (int ps = 0; ps < kPasses; ++ps) {
+      const uint32_t i = 4u * (uint32_t)(cw + kConvWarps * ps) + sgi;
+      if (4u * (uint32_t)(cw + kConvWarps * ps) >= cnt) break;  // warp-uniform
+      uint32_t g = blk0 + i;
+      if (g >= D.nblk) g -= D.nblk;
+      const uint32_t ws = it.windowed ? i : g;
+      if (i < cnt) {
+        const unsigned char* bg = X.bwin() + (size_t)ws * kBRec + (l8 >> 2) * 128u + ((4u * l8) & 15u);
+        float4 xv[MT];
 #pragma unroll
-    for (int ps = 0; ps < kPasses; ++ps)
-      if (val[ps]) digits8<MT>(X, xv[ps], up, wsl[ps], lane);
+        for (int r = 0; r < MT; ++r)
+          xv[r] = make_float4(*reinterpret_cast<const float*>(bg + (4 * r + 0) * 16), *reinterpret_cast<const float*>(bg + (4 * r + 1) * 16),
+                              *reinterpret_cast<const float*>(bg + (4 * r + 2) * 16), *reinterpret_cast<const float*>(bg + (4 * r + 3) * 16));
+        digits8<MT>(X, xv, up, ws, lane);
+      }
+    }
   }
   fence_proxy_async_smem();
 }
 
-// Zeroes this CTA's share of the accumulators the phase retires, and works out the phase's 1/rms factors.
+// Zeroes this CTA's share of the accumulators the phase retires.
 template <int MT>
 __device__ void phase_duties(Ctx<MT>& X, const PhaseDesc& D) {
   const int ct = X.tid - kWarpLeader * 32;
@@ -647,21 +702,21 @@ __device__ void phase_duties(Ctx<MT>& X, const PhaseDesc& D) {
   };
   zero(D.zero0, D.zero0_n, D.zero0_poison);
   zero(D.zero1, D.zero1_n, D.zero1_poison);
-  if (D.ss_in) {  // functional.rs:151-165: 1 / sqrt(mean(x^2) + eps), the mean from the per-group sums, in a fixed order
-    if (X.warp == kWarpLeader) {
-      for (uint32_t r = 0; r < X.c.m; ++r) {
-        float s = 0.0f;
-        for (uint32_t i = X.lane; i < D.ss_groups; i += 32) s += __ldcg(D.ss_in + (size_t)r * D.ss_groups + i);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
-        if (X.lane == 0) X.sh->rstd[r] = 1.0f / sqrtf(s * (1.0f / D.ss_dim) + X.c.sp->eps);
-      }
-    }
-    bar_sync(1, kConsumers);
-  }
 }
 
 // ---- producer ---------------------------------------------------------------------------------------
+
+// Ring stages of units [a, b) of a weight with nblk blocks per tile, at most smax blocks per stage, a stage
+// never crossing a tile: every role of the CTA works its share of the phase out from this count alone.
+__device__ __forceinline__ uint32_t count_stages(uint32_t a, uint32_t b, uint32_t nblk, uint32_t smax) {
+  uint32_t n = 0, blk = a % nblk;
+  while (a < b) {
+    const uint32_t len = min(nblk - blk, b - a);
+    n += smax == 4u ? (len + 3u) >> 2 : (len + smax - 1u) / 3u;
+    a += len; blk = 0;
+  }
+  return n;
+}
 
 template <int MT>
 __device__ __forceinline__ bool produce(Ctx<MT>& X, const void* src0, uint32_t bytes0, uint32_t off1, const void* src1, uint32_t bytes1) {
@@ -676,21 +731,47 @@ __device__ __forceinline__ bool produce(Ctx<MT>& X, const void* src0, uint32_t b
   return true;
 }
 
+// The weights of one GEMV phase: per stage a record (tile, window slot, blocks) for the consumers, then one bulk copy.
+template <int MT>
+__device__ bool produce_gemv(Ctx<MT>& X, const PhaseDesc& D) {
+  const uint32_t rec = D.bits == 4 ? kStreamRec4 : kStreamRec8;
+  const uint32_t smax = D.bits == 4 ? kStage4 : kStage8;
+  const uint64_t units = (uint64_t)D.ntiles * D.nblk;
+  const uint32_t u0 = (uint32_t)(units * blockIdx.x / gridDim.x), u1 = (uint32_t)(units * (blockIdx.x + 1) / gridDim.x);
+  const bool windowed = D.nblk > (uint32_t)kWin;
+  uint32_t u = u0, tile = u0 / D.nblk, blk = u0 - tile * D.nblk;
+  uint32_t slot = X.s % kSlots, use = X.s / kSlots;
+  const uint8_t* src = D.w + (size_t)u0 * rec;   // units are consecutive records of the stream
+  while (u < u1) {
+    const uint32_t rend = windowed ? min(u1, u + (uint32_t)kWin) : u1;
+    const uint32_t ru = u;
+    while (u < rend) {
+      const uint32_t seg_end = min(rend, u + (D.nblk - blk));
+      while (u < seg_end) {
+        const uint32_t cnt = min(smax, seg_end - u);
+        if (use > 0u && !X.wait(&X.sh->b.empty[slot], (use - 1u) & 1u, 10)) return false;
+        PS_TRACE_STAGE(X, X.s, 0);
+        X.sh->rec[slot] = make_uint2(tile, (windowed ? u - ru : blk) | (cnt << 16));
+        const uint32_t bytes = cnt * rec;
+        mbar_expect_tx(&X.sh->b.full[slot], bytes);
+        bulk_load(X.smem + kOffSlots + (size_t)slot * kSlotBytes, src, bytes, &X.sh->b.full[slot]);
+        src += bytes; u += cnt; blk += cnt; ++X.s;
+        if (++slot == (uint32_t)kSlots) { slot = 0; ++use; }
+      }
+      if (blk == D.nblk) { blk = 0; ++tile; }
+    }
+  }
+  return true;
+}
+
 template <int MT, typename Prog>
 __device__ void producer_loop(Ctx<MT>& X, const Prog& prog, uint32_t len) {
   const uint32_t np = prog.nphases();
   for (uint32_t p = 0; p < np; ++p) {
-    PhaseDesc D;
+    PhaseDesc& D = X.sh->Dp;
     prog.get(p, D);
     if (D.type == PH_GEMV) {
-      const uint32_t rec = D.bits == 4 ? kStreamRec4 : kStreamRec8;
-      StageIter it;
-      it.init(D.ntiles, D.nblk, D.bits == 4 ? kStage4 : kStage8);
-      Stage st;
-      while (it.next(st)) {
-        const uint8_t* src = D.w + ((size_t)st.tile * D.nblk + st.blk) * rec;
-        if (!produce<MT>(X, src, st.cnt * rec, 0, nullptr, 0)) return;
-      }
+      if (!produce_gemv<MT>(X, D)) return;
     } else if (D.type == PH_ATTN) {
       const StepParams* P = X.c.sp;
       AttnPlan ap;
@@ -713,27 +794,19 @@ __device__ void producer_loop(Ctx<MT>& X, const Prog& prog, uint32_t len) {
 
 // ---- the GEMV phase, by role --------------------------------------------------------------------------
 
-// Digits of a round: everyone waits until the previous round's sums are out, all consumer warps write, everyone meets again.
-template <int MT>
-__device__ __forceinline__ void round_sync(Ctx<MT>& X, const PhaseDesc& D, const StageIter& it, const Stage& st, bool first_round) {
-  if (!first_round) bar_sync(1, kConsumers);
-  convert_round<MT>(X, D, it, st.round_blk0, st.round_cnt);
-  bar_sync(1, kConsumers);
-  if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, X.cur_phase, 2);
-}
-
-__device__ __forceinline__ void wg_bar(int g) { bar_sync(4 + g, 128); }
-
-// A GEMV phase.  Ring stage s belongs to warpgroup s % 3 (thread = column of the tile, as expanding and as draining
-// thread) and to MMA issuer s % 2 (one thread of warp 1 / warp 2: a thread needs well over a hundred cycles per
-// tcgen05.mma, so the issuing is spread over two threads that do nothing else).
-// int4, per stage of a warpgroup, in program order: request the sums of its PREVIOUS stage out of tensor memory;
-// packed nibbles of the ring slot -> bytes in the warpgroup's A buffer (the slot goes back to the producer at once;
-// the group scales stay in registers); tell the issuer; then finish the previous stage (scale, accumulate in f32).
+// A GEMV phase.  The units of the CTA are worked in rounds (one round unless the weight has more than kWin blocks of
+// k): the consumer warps write the digits of the round's activations, then every role runs over the round's ring
+// stages.  Stage s belongs to warpgroup s % 3 (thread = column of the tile, as expanding and as draining thread) and
+// to MMA issuer s % 2 (one thread of warp 1 / warp 2: a thread needs well over a hundred cycles per tcgen05.mma, so
+// the issuing is spread over two threads that do nothing else).  Nobody walks stages that are not its own: the
+// round's stage count is a closed form and what a stage holds is in the record the producer left with it.
+// int4, per stage of a warpgroup: packed nibbles of the ring slot -> bytes in one of the warpgroup's two A buffers
+// (the slot goes back to the producer at once; the group scales stay in registers); tell the issuer; then read the
+// sums of its PREVIOUS stage out of tensor memory (scale, accumulate in f32) while the MMAs of this one run.
 // The issuer waits for the A buffer, issues one MMA per scale group, each into its own accumulator, and commits.
-// int8: the ring slot is the operand; an issuer rotates its MMAs over eight accumulators of its own, and warpgroup
-// 0 / 1 reads issuer 0's / 1's out when the run inside the tile ends.  Every part of a tile is added to the global
-// fixed-point accumulator.
+// int8: the ring slot is the operand; an issuer rotates its MMAs over eight accumulators (two sets, so that the next
+// run starts while the last one is read), and warpgroup 0 / 1 reads issuer 0's / 1's out when the run inside the tile
+// ends.  Every part of a tile is added to the global fixed-point accumulator.
 template <int MT>
 __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   const bool is4 = D.bits == 4;
@@ -747,256 +820,285 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   const uint32_t lane_base = (quarter * 32u) << 16;
   (void)tracer;
   StageIter it;
-  it.init(D.ntiles, D.nblk, is4 ? kStage4 : kStage8);
-  Stage st;
+  const uint32_t smax = is4 ? kStage4 : kStage8;
+  it.init(D.ntiles, D.nblk, smax);
   X.cur_phase = p;
 
-  // int4 stages of warpgroup wg so far (constant-indexed, so the counters stay in registers)
-  auto wg_count = [&](uint32_t wg) { return wg == 0u ? X.mc0 : (wg == 1u ? X.mc1 : X.mc2); };
-  float sc_cur[kStage4], sc_pend[kStage4];
-#pragma unroll
-  for (int i = 0; i < kStage4; ++i) { sc_cur[i] = 0.0f; sc_pend[i] = 0.0f; }
-  uint32_t pend_ws = 0, pend_cnt = 0, pend_mc = 0;
-  bool have_pending = false;
-  int32_t dsum[kStage4][MT == 1 ? 4 : 8];
-
-  // sums of the warpgroup's previous stage: the loads are requested early and collected late
-  auto drain_request = [&]() {
-    X.wait(&X.sh->b.mma_done[g][pend_mc & 1u], (pend_mc >> 1) & 1u, 16);
-    if (tracer) PS_TRACE_STAGE(X, 4u * pend_mc, 5);
-    tc_fence_after_sync();
-    if (!X.aborted()) {
-      const uint32_t t0 = X.tmem + lane_base + (uint32_t)g * 128u + (pend_mc & 1u) * 64u;
-#pragma unroll
-      for (int gi = 0; gi < kStage4; ++gi) {
-        if ((uint32_t)gi < pend_cnt) {
-          if constexpr (MT == 1) tmem_ld4(t0 + gi * 16u, dsum[gi]);
-          else tmem_ld8(t0 + gi * 16u, dsum[gi]);
-        }
-      }
-    }
-  };
-  float acc[MT];
-#pragma unroll
-  for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
-  bool dirty = false;  // acc holds something that has not gone out yet
-  auto drain_collect = [&]() {
-    tmem_ld_wait();
-    tc_fence_before_sync();
-    if (tracer) PS_TRACE_STAGE(X, 4u * pend_mc, 6);
-    if (!X.aborted()) {
-#pragma unroll
-      for (int gi = 0; gi < kStage4; ++gi) {
-        if ((uint32_t)gi < pend_cnt) {
-          const uint32_t mi = (pend_ws + gi) * MT;
-#pragma unroll
-          for (int r = 0; r < MT; ++r) {
-            const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
-            acc[r] = fmaf((float)val, sc_pend[gi] * X.mscale()[mi + r], acc[r]);
-          }
-        }
-      }
-      dirty = true;
-    }
-    have_pending = false;
-    if (tracer) PS_TRACE_STAGE(X, 4u * pend_mc, 7);
-  };
-  auto flush = [&](uint32_t tile) {
-    const uint32_t j = tile * kCols + col;
-    if (dirty && j < D.n) {
-      const float cs = is4 ? 1.0f : __ldg(D.colscale + j);
-#pragma unroll
-      for (int r = 0; r < MT; ++r) {
-        if ((uint32_t)r < X.c.m) {
-          const float v = acc[r] * cs;
-          if (finite_f(v)) red_add_s64(D.acc_out + (size_t)r * D.n + j, __float2ll_rn(v * kFix));
-          else atomicOr(D.poison_out + r, 1);
-        }
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
-    dirty = false;
-  };
-  // packed weights of ring stage s -> the warpgroup's A buffer; the slot is released; the issuer is told
-  auto expand = [&](const Stage& t, uint32_t s) {
-    const uint32_t slot = s % kSlots;
-    X.wait(&X.sh->b.full[slot], (s / kSlots) & 1u, 11);
-    // the MMAs that read the A buffer last (this warpgroup's previous stage) are done
-    // the MMAs that read this A buffer last (this warpgroup's stage before the previous one) are done
-    const uint32_t mc = wg_count((uint32_t)g);
-    if (mc >= 2u) X.wait(&X.sh->b.mma_done[g][mc & 1u], ((mc - 2u) >> 1) & 1u, 12);
-    if (tracer) PS_TRACE_STAGE(X, s, 1);
-    const unsigned char* src = X.slot_ptr(s);
-    unsigned char* dst = X.abuf_ptr(g, mc);
-    if (!X.aborted()) {
-#pragma unroll
-      for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi) {
-        if (gi < t.cnt) {
-          const uint4 wv = *reinterpret_cast<const uint4*>(src + gi * kStreamRec4 + col * 16u);
-          sc_cur[gi] = *reinterpret_cast<const float*>(src + gi * kStreamRec4 + 2048u + col * 4u);
-          uint4 lo, hi;
-          lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
-          lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
-          lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
-          lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
-          unsigned char* d = dst + gi * 4096u + col * 16u;
-          *reinterpret_cast<uint4*>(d) = lo;           // rows 0..15 of the group: first k-half
-          *reinterpret_cast<uint4*>(d + 2048) = hi;    // rows 16..31: second k-half
-        }
-      }
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (X.lane == 0) {
-      mbar_arrive(&X.sh->b.empty[slot]);   // packed weights and scales are out of the slot
-      mbar_arrive(&X.sh->b.a_ready[g][mc & 1u]);
-    }
-    if (tracer) PS_TRACE_STAGE(X, s, 2);
-  };
+  // the rounds of this CTA: [ru, rend) units each
+  const uint32_t rend0 = it.windowed ? min(it.u1, it.u0 + (uint32_t)kWin) : it.u1;
+  const uint32_t nst0 = it.u0 < it.u1 ? count_stages(it.u0, rend0, D.nblk, smax) : 0u;
+  // first stage of warpgroup w at or after ring stage `base`
+  auto first_of = [](uint32_t base, uint32_t w) { return base + (w + 3u - base % 3u) % 3u; };
 
   if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 0);
   // ---- between the phases: this CTA is done with the previous phase; wait for the others ----
-  if (p > 0) {
-    bar_sync(1, kConsumers);
-    if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
-  }
+  if (p > 0 && X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
   if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 1);
-  // every warpgroup uses the wait: its first stage of this phase needs nothing but its weights
-  uint32_t pre_stage = 0xFFFFFFFFu;
-  if (worker && is4) {
-    StageIter it2 = it;
-    Stage t2;
-    uint32_t s2 = X.s;
-    while (it2.next(t2)) {
-      if ((s2 % kGroups) == (uint32_t)g) {
-        expand(t2, s2);
-        pre_stage = s2;
-        break;
-      }
-      ++s2;
-    }
-  }
   if (p > 0) bar_sync(1, kConsumers);
   phase_duties<MT>(X, D);
 
-  bool first_round = true;
-  uint32_t seg_mmas = 0;      // int8: MMAs of issuer (stage & 1) in the open run, tracked by that issuer and its warpgroup
-  while (it.next(st)) {
-    if (st.round_start) {
-      round_sync<MT>(X, D, it, st, first_round);
-      first_round = false;
-    }
-    const uint32_t slot = X.s % kSlots;
-    const uint32_t sg = X.s % kGroups;           // warpgroup of this stage
-    if (is4) {
-      if (worker && sg == (uint32_t)g) {
-        if (X.s != pre_stage) expand(st, X.s);
-        if (have_pending) { drain_request(); drain_collect(); }  // while the MMAs of this stage are issued and run
-        pend_ws = st.ws; pend_cnt = st.cnt; pend_mc = wg_count((uint32_t)g);
-#pragma unroll
-        for (int i = 0; i < kStage4; ++i) sc_pend[i] = sc_cur[i];
-        have_pending = true;
-      }
-      if (issuer && (X.s & 1u) == (uint32_t)issuer_idx) {
-        const uint32_t k = wg_count(sg);  // this is the k-th stage of warpgroup sg since the kernel started
-        X.wait(&X.sh->b.a_ready[sg][k & 1u], (k >> 1) & 1u, 13);
-        PS_TRACE_STAGE(X, X.s, 3);
-        if (!X.aborted()) {
-          tc_fence_after_sync();
-          constexpr uint32_t idesc = umma_idesc_i8(16, false);
-          const uint64_t ad = umma_desc_kmajor(smem_u32(X.abuf_ptr(sg, k)), 2048, 128);
-          const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
-          const uint32_t d0 = X.tmem + sg * 128u + (k & 1u) * 64u;
-          if (st.cnt == (uint32_t)kStage4) {
-#pragma unroll
-            for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi)
-              umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
-          } else {
-            for (uint32_t gi = 0; gi < st.cnt; ++gi)
-              umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
+  for (uint32_t ru = it.u0; ru < it.u1;) {
+    const bool first_round = ru == it.u0;
+    const uint32_t rend = it.windowed ? min(it.u1, ru + (uint32_t)kWin) : it.u1;
+    const uint32_t nst = first_round ? nst0 : count_stages(ru, rend, D.nblk, smax);
+    // digits of the round: everyone waits until the previous round's sums are out, all consumer warps write, everyone meets again
+    if (!first_round) bar_sync(1, kConsumers);
+    convert_round<MT>(X, D, it, it.windowed ? ru % D.nblk : it.blk_at_u0, it.windowed ? rend - ru : min(it.u1 - it.u0, D.nblk));
+    bar_sync(1, kConsumers);
+    if (X.tid == kLeaderTid && first_round) PS_TRACE_PHASE(X, p, 2);
+    if (tracer && first_round) PS_TRACE_ISSUE(X, p, 4);
+    const uint32_t base = X.s, end = base + nst;
+
+    // The streaming state lives inside the round, after the conversion: the two never hold registers at the same time.
+    float acc[MT];
+  #pragma unroll
+    for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
+    bool dirty = false;  // acc holds something that has not gone out yet
+    auto flush = [&](uint32_t tile) {
+      const uint32_t j = tile * kCols + col;
+      if (dirty && j < D.n) {
+        const float cs = is4 ? 1.0f : __ldg(D.colscale + j);
+  #pragma unroll
+        for (int r = 0; r < MT; ++r) {
+          if ((uint32_t)r < X.c.m) {
+            const float v = acc[r] * cs;
+            if (finite_f(v)) red_add_s64(D.acc_out + (size_t)r * D.n + j, __float2ll_rn(v * kFix));
+            else atomicOr(D.poison_out + r, 1);
           }
-          umma_commit(&X.sh->b.mma_done[sg][k & 1u]);
         }
-        PS_TRACE_STAGE(X, X.s, 4);
       }
-      if (sg == 0u) ++X.mc0; else if (sg == 1u) ++X.mc1; else ++X.mc2;
-      if (st.seg_end && worker) {  // the run inside this tile (and round) ends: every warpgroup's part goes out
-        if (have_pending) { drain_request(); drain_collect(); }
-        flush(st.tile);
+  #pragma unroll
+      for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
+      dirty = false;
+    };
+
+    // ---- int4, warpgroup side ----
+    float sc_cur[kStage4], sc_pend[kStage4];
+  #pragma unroll
+    for (int i = 0; i < kStage4; ++i) { sc_cur[i] = 0.0f; sc_pend[i] = 0.0f; }
+    uint32_t pend_ws = 0, pend_cnt = 0, pend_k = 0, pend_tile = 0;
+    bool have_pending = false;
+    // sums of the warpgroup's previous stage out of tensor memory, scaled and added up
+    auto drain = [&]() {
+      constexpr int kHalf = MT == 1 ? kStage4 : kStage4 / 2;  // groups read out at once (more would spill)
+      X.wait(&X.sh->b.mma_done[g][pend_k & 1u], (pend_k >> 1) & 1u, 16);
+      tc_fence_after_sync();
+      if (!X.aborted()) {
+        const uint32_t t0 = X.tmem + lane_base + (uint32_t)g * 128u + (pend_k & 1u) * 64u;
+#pragma unroll
+        for (int h0 = 0; h0 < kStage4; h0 += kHalf) {
+          if ((uint32_t)h0 >= pend_cnt) break;
+          int32_t dsum[kHalf][MT == 1 ? 4 : 8];
+#pragma unroll
+          for (int gi = 0; gi < kHalf; ++gi) {
+            if ((uint32_t)(h0 + gi) < pend_cnt) {
+              if constexpr (MT == 1) tmem_ld4(t0 + (h0 + gi) * 16u, dsum[gi]);
+              else tmem_ld8(t0 + (h0 + gi) * 16u, dsum[gi]);
+            }
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int gi = 0; gi < kHalf; ++gi) {
+            if ((uint32_t)(h0 + gi) < pend_cnt) {
+              const uint32_t mi = (pend_ws + h0 + gi) * MT;
+#pragma unroll
+              for (int r = 0; r < MT; ++r) {
+                const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
+                acc[r] = fmaf((float)val, sc_pend[h0 + gi] * X.mscale()[mi + r], acc[r]);
+              }
+            }
+          }
+        }
+        tc_fence_before_sync();
+        dirty = true;
+      }
+      have_pending = false;
+    };
+    // packed weights of ring stage s (the warpgroup's k-th) -> A buffer k & 1; the slot is released; the issuer is told.
+    // Returns the stage's record.
+    auto expand = [&](uint32_t s, uint32_t k) -> uint2 {
+      const uint32_t slot = s % kSlots;
+      X.wait(&X.sh->b.full[slot], (s / kSlots) & 1u, 11);
+      if (tracer) PS_TRACE_STAGE(X, s, 6);
+      const uint2 rc = X.sh->rec[slot];
+      const uint32_t cnt = rc.y >> 16;
+      // the MMAs that read this A buffer last (this warpgroup's stage before the previous one) are done
+      if (k >= 2u) X.wait(&X.sh->b.mma_done[g][k & 1u], ((k - 2u) >> 1) & 1u, 12);
+      if (tracer) PS_TRACE_STAGE(X, s, 1);
+      const unsigned char* src = X.smem + kOffSlots + (size_t)slot * kSlotBytes;
+      unsigned char* dst = X.abuf_ptr(g, k);
+      if (!X.aborted()) {
+  #pragma unroll
+        for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi) {
+          if (gi < cnt) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(src + gi * kStreamRec4 + col * 16u);
+            sc_cur[gi] = *reinterpret_cast<const float*>(src + gi * kStreamRec4 + 2048u + col * 4u);
+            uint4 lo, hi;
+            lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
+            lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
+            lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
+            lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
+            unsigned char* d = dst + gi * 4096u + col * 16u;
+            *reinterpret_cast<uint4*>(d) = lo;           // rows 0..15 of the group: first k-half
+            *reinterpret_cast<uint4*>(d + 2048) = hi;    // rows 16..31: second k-half
+          }
+        }
+      }
+      if (tracer) PS_TRACE_STAGE(X, s, 5);
+      fence_proxy_async_smem();
+      if (tracer) PS_TRACE_STAGE(X, s, 7);
+      __syncwarp();
+      if (X.lane == 0) {
+        if (quarter == 0) X.sh->wgrec[g][k & 1u] = rc.y;  // what the issuer needs: window slot and blocks
+        mbar_arrive(&X.sh->b.empty[slot]);   // packed weights and scales are out of the slot
+        mbar_arrive(&X.sh->b.a_ready[g][k & 1u]);
+      }
+      if (tracer) PS_TRACE_STAGE(X, s, 2);
+      return rc;
+    };
+
+
+    if (is4) {
+      if (worker) {
+        uint32_t k = g == 0 ? X.mc0 : (g == 1 ? X.mc1 : X.mc2);
+        for (uint32_t s = first_of(base, (uint32_t)g); s < end; s += 3u, ++k) {
+          if (tracer && first_round && s < base + 3u) PS_TRACE_ISSUE(X, p, 5);
+          const uint2 rc = expand(s, k);
+          if (have_pending) {
+            drain();  // while the MMAs of this stage are issued and run
+            if (pend_tile != rc.x) flush(pend_tile);
+          }
+          pend_tile = rc.x; pend_ws = rc.y & 0xFFFFu; pend_cnt = rc.y >> 16; pend_k = k;
+#pragma unroll
+          for (int i = 0; i < kStage4; ++i) sc_pend[i] = sc_cur[i];
+          have_pending = true;
+        }
+        if (have_pending) { drain(); flush(pend_tile); }  // the round ends: every warpgroup's part goes out
+      } else if (issuer) {
+        const uint32_t f0 = first_of(base, 0u), f1 = first_of(base, 1u), f2 = first_of(base, 2u);
+        if (first_round) PS_TRACE_ISSUE(X, p, issuer_idx ? 2 : 0);
+        for (uint32_t s = base + ((base ^ (uint32_t)issuer_idx) & 1u); s < end; s += 2u) {
+          const uint32_t sg = s % 3u;
+          const uint32_t k = sg == 0u ? X.mc0 + (s - f0) / 3u : (sg == 1u ? X.mc1 + (s - f1) / 3u : X.mc2 + (s - f2) / 3u);
+          X.wait(&X.sh->b.a_ready[sg][k & 1u], (k >> 1) & 1u, 13);
+          if (first_round && s < base + 2u) PS_TRACE_ISSUE(X, p, issuer_idx ? 3 : 1);
+          PS_TRACE_STAGE(X, s, 3);
+          if (!X.aborted()) {
+            const uint32_t rc = X.sh->wgrec[sg][k & 1u];
+            const uint32_t ws = rc & 0xFFFFu, cnt = rc >> 16;
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_i8(16, false);
+            const uint64_t ad = umma_desc_kmajor(smem_u32(X.abuf_ptr(sg, k)), 2048, 128);
+            const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)ws * kBRec), 128, 0);
+            const uint32_t d0 = X.tmem + sg * 128u + (k & 1u) * 64u;
+            if (cnt == (uint32_t)kStage4) {
+#pragma unroll
+              for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi)
+                umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
+            } else {
+              for (uint32_t gi = 0; gi < cnt; ++gi)
+                umma_i8(d0 + gi * 16u, umma_desc_advance(ad, gi * 4096u), umma_desc_advance(bd, gi * kBRec), idesc, 0u);
+            }
+            umma_commit(&X.sh->b.mma_done[sg][k & 1u]);
+          }
+          PS_TRACE_STAGE(X, s, 4);
+        }
+      }
+      // every consumer thread keeps the three warpgroups' stage counts
+      {
+        const uint32_t b3 = base % 3u;
+        const uint32_t o0 = (3u - b3) % 3u, o1 = (4u - b3) % 3u, o2 = (5u - b3) % 3u;  // offset of the first stage of warpgroup 0 / 1 / 2
+        X.mc0 += nst > o0 ? (nst - o0 + 2u) / 3u : 0u;
+        X.mc1 += nst > o1 ? (nst - o1 + 2u) / 3u : 0u;
+        X.mc2 += nst > o2 ? (nst - o2 + 2u) / 3u : 0u;
       }
     } else {
-      const uint32_t ii = X.s & 1u;  // issuer of this stage; warpgroup ii reads its sums out
-      if (issuer && ii == (uint32_t)issuer_idx) {
-        if (seg_mmas == 0 && X.sgc >= 1u) X.wait(&X.sh->b.seg_free[ii], (X.sgc - 1u) & 1u, 17);  // the previous run's sums are read out
-        X.wait(&X.sh->b.full[slot], (X.s / kSlots) & 1u, 18);
-        PS_TRACE_STAGE(X, X.s, 3);
-        if (!X.aborted()) {
-          tc_fence_after_sync();
-          constexpr uint32_t idesc = umma_idesc_i8(16, true);
-          const uint64_t ad = umma_desc_kmajor(smem_u32(X.slot_ptr(X.s)), 2048, 128);
-          const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)st.ws * kBRec), 128, 0);
-          const uint32_t d0 = X.tmem + ii * 128u;
-          // consecutive MMAs go to kAcc8 different accumulators: one accumulator would make every MMA wait for the
-          // one before it, and a 128 x 16 x 32 MMA is all latency
-          for (uint32_t bi = 0; bi < st.cnt; ++bi) {
-            const uint32_t j = seg_mmas + bi;
-            umma_i8(d0 + (j & (kAcc8 - 1u)) * 16u, umma_desc_advance(ad, bi * 4096u), umma_desc_advance(bd, bi * kBRec), idesc, j >= kAcc8 ? 1u : 0u);
+      // ---- int8 ----
+      if (issuer) {
+        const uint32_t ii = (uint32_t)issuer_idx;
+        uint32_t nm = 0, run_tile = 0;
+        bool open = false;
+        auto close_run = [&](uint32_t last) {
+          const uint32_t b = X.sgc & 1u;
+          X.sh->segrec[ii][b] = make_uint4(run_tile, nm, last, 0u);
+          // two arrivals complete the barrier: this thread's (which publishes the record: the arrival a commit makes is
+          // not ordered after the thread's own stores) and the commit's (the run's MMAs are done)
+          mbar_arrive(&X.sh->b.seg_done[ii][b]);
+          if (!X.aborted()) umma_commit(&X.sh->b.seg_done[ii][b]);
+          ++X.sgc; nm = 0; open = false;
+        };
+        auto open_run = [&](uint32_t tile) {
+          // the sums of the run that used this accumulator set before are read out
+          if (X.sgc >= 2u) X.wait(&X.sh->b.seg_free[ii][X.sgc & 1u], ((X.sgc >> 1) - 1u) & 1u, 17);
+          run_tile = tile; nm = 0; open = true;
+        };
+        for (uint32_t s = base + ((base ^ ii) & 1u); s < end; s += 2u) {
+          const uint32_t slot = s % kSlots;
+          X.wait(&X.sh->b.full[slot], (s / kSlots) & 1u, 18);
+          const uint2 rc = X.sh->rec[slot];
+          if (open && rc.x != run_tile) close_run(0u);
+          if (!open) open_run(rc.x);
+          PS_TRACE_STAGE(X, s, 3);
+          const uint32_t ws = rc.y & 0xFFFFu, cnt = rc.y >> 16;
+          if (!X.aborted()) {
+            tc_fence_after_sync();
+            constexpr uint32_t idesc = umma_idesc_i8(16, true);
+            const uint64_t ad = umma_desc_kmajor(smem_u32(X.smem + kOffSlots + (size_t)slot * kSlotBytes), 2048, 128);
+            const uint64_t bd = umma_desc_kmajor(smem_u32(X.bwin() + (size_t)ws * kBRec), 128, 0);
+            const uint32_t d0 = X.tmem + ii * 256u + (X.sgc & 1u) * 128u;
+            // consecutive MMAs go to kAcc8 different accumulators: one accumulator would make every MMA wait for the
+            // one before it, and a 128 x 16 x 32 MMA is all latency
+            for (uint32_t bi = 0; bi < cnt; ++bi) {
+              const uint32_t j = nm + bi;
+              umma_i8(d0 + (j & (kAcc8 - 1u)) * 16u, umma_desc_advance(ad, bi * 4096u), umma_desc_advance(bd, bi * kBRec), idesc, j >= kAcc8 ? 1u : 0u);
+            }
+            umma_commit(&X.sh->b.empty[slot]);  // the slot is free once these MMAs have read it
+            mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]);
           }
-          umma_commit(&X.sh->b.empty[slot]);  // the slot is free once these MMAs have read it
-          mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]); mbar_arrive(&X.sh->b.empty[slot]);
+          nm += cnt;
+          PS_TRACE_STAGE(X, s, 4);
         }
-        PS_TRACE_STAGE(X, X.s, 4);
-      }
-      // issuer ii and warpgroup ii count the MMAs of issuer ii's part of the run
-      const bool counts = (issuer_idx == (int)ii) || (worker && g == (int)ii);
-      if (counts) seg_mmas += st.cnt;
-    }
-    ++X.s;
-    if (!is4 && st.seg_end) {
-      // ---- int8: the run inside this tile ends ----
-      if (issuer_idx >= 0) {
-        if (seg_mmas > 0) {
-          if (issuer && !X.aborted()) umma_commit(&X.sh->b.seg_done[issuer_idx]);
-          ++X.sgc;
-        }
-        seg_mmas = 0;
+        if (!open) open_run(0u);
+        close_run(1u);  // always: the warpgroup that reads this issuer's sums learns that the round is over
+      } else if (issuer_idx >= 0) {
+        // the other lanes of an issuer warp have nothing to do in this round
       } else if (worker && g < 2) {
-        if (seg_mmas > 0) {
-          X.wait(&X.sh->b.seg_done[g], X.sgc & 1u, 19);
+        for (;;) {
+          const uint32_t b = X.sgc & 1u;
+          if (!X.wait(&X.sh->b.seg_done[g][b], (X.sgc >> 1) & 1u, 19)) break;
+          const uint4 sr = X.sh->segrec[g][b];
           ++X.sgc;
           tc_fence_after_sync();
           int32_t dg[4 * MT];
 #pragma unroll
           for (int t = 0; t < 4 * MT; ++t) dg[t] = 0;
-          if (!X.aborted()) {
-            const uint32_t nacc = min(seg_mmas, kAcc8);
-            constexpr int kBatch = MT == 1 ? (int)kAcc8 : (int)kAcc8 / 2;  // accumulators in registers at once
+          const uint32_t nacc = min(sr.y, kAcc8);
+          constexpr int kBatch = 2;  // accumulators in registers at once (more would spill)
+          const uint32_t t0 = X.tmem + lane_base + (uint32_t)g * 256u + b * 128u;
 #pragma unroll
-            for (int a0 = 0; a0 < (int)kAcc8; a0 += kBatch) {
-              if ((uint32_t)a0 < nacc) {
-                int32_t part[kBatch][MT == 1 ? 4 : 8];
+          for (int a0 = 0; a0 < (int)kAcc8; a0 += kBatch) {
+            if ((uint32_t)a0 < nacc) {
+              int32_t part[kBatch][MT == 1 ? 4 : 8];
 #pragma unroll
-                for (int a = 0; a < kBatch; ++a) {
-                  if ((uint32_t)(a0 + a) < nacc) {
-                    if constexpr (MT == 1) tmem_ld4(X.tmem + lane_base + (uint32_t)g * 128u + (a0 + a) * 16u, part[a]);
-                    else tmem_ld8(X.tmem + lane_base + (uint32_t)g * 128u + (a0 + a) * 16u, part[a]);
-                  }
+              for (int a = 0; a < kBatch; ++a) {
+                if ((uint32_t)(a0 + a) < nacc) {
+                  if constexpr (MT == 1) tmem_ld4(t0 + (a0 + a) * 16u, part[a]);
+                  else tmem_ld8(t0 + (a0 + a) * 16u, part[a]);
                 }
-                tmem_ld_wait();
-#pragma unroll
-                for (int a = 0; a < kBatch; ++a)
-                  if ((uint32_t)(a0 + a) < nacc) {
-#pragma unroll
-                    for (int t = 0; t < 4 * MT; ++t) dg[t] += part[a][t];  // integer sums: exact
-                  }
               }
+              tmem_ld_wait();
+#pragma unroll
+              for (int a = 0; a < kBatch; ++a)
+                if ((uint32_t)(a0 + a) < nacc) {
+#pragma unroll
+                  for (int t = 0; t < 4 * MT; ++t) dg[t] += part[a][t];  // integer sums: exact
+                }
             }
           }
           tc_fence_before_sync();
           __syncwarp();
-          if (X.lane == 0) mbar_arrive(&X.sh->b.seg_free[g]);  // the issuer may start its next run
-          if (!X.aborted()) {
+          if (X.lane == 0) mbar_arrive(&X.sh->b.seg_free[g][b]);  // the issuer may use this accumulator set again
+          if (sr.y > 0u) {
 #pragma unroll
             for (int r = 0; r < MT; ++r) {
               float v = (float)dg[4 * r];
@@ -1006,24 +1108,31 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
               acc[r] = v * X.sh->xscale[r];
             }
             dirty = true;
+            flush(sr.x);
           }
-          flush(st.tile);
+          if (sr.z) break;
         }
-        seg_mmas = 0;
       }
     }
+    X.s = end;
+    ru = rend;
   }
   if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 3);
 }
 
 // ---- attention phase ----------------------------------------------------------------------------------
 
+// One (sequence, KV head, key split) item per CTA turn.  Its keys and values come through the ring in stages of
+// keys_per_stage rows; up to kAttnBatch stages are worked at once: scores of all their keys (a warp per key), one
+// running-softmax update, the value sums.  The split that finishes an item last merges all its splits (in split order,
+// so the result does not depend on which CTA that is) into the f32 attention output the o_proj phase reads.
+constexpr uint32_t kAttnBatch = kSlots - 1;
+
 template <int MT>
 __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t len) {
   const StepParams* P = X.c.sp;
   if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 0);
   if (p > 0) {
-    bar_sync(1, kConsumers);
     if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
     bar_sync(1, kConsumers);
   }
@@ -1033,63 +1142,93 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
   phase_duties<MT>(X, D);
   const int ct = X.tid - kWarpLeader * 32, cw = X.warp - kWarpLeader, lane = X.lane;
   const uint32_t hd = P->hd, half = hd / 2, rep = P->rep, nq4 = hd / 4, pos = len;
+  const uint32_t scld = kAttnBatch * ap.KS + 1u;      // scores per head: the batch's keys, then the new key
   float* qs = reinterpret_cast<float*>(X.bwin());   // [rep][hd]
   float* knew = qs + rep * hd;
   float* vnew = knew + hd;
-  float* sc = vnew + hd;                              // [rep][KS]
-  float* snew = sc + rep * ap.KS;                     // [rep]
+  float* sc = vnew + hd;                              // [rep][scld]
+  float* wm = sc + rep * scld;                        // merge: [rep][S] maxima, then [rep][S] sums
   const float2* table = P->rope + (size_t)pos * half;
+  // this thread's outputs in the value step: head vr, elements 4 vc .. 4 vc + 3
+  const bool vact = (uint32_t)ct < rep * nq4;
+  const uint32_t vr = vact ? ct / nq4 : 0, vc = vact ? ct - vr * nq4 : 0;
+  float rsv[MT];
+  bool have_rs = false;
+  constexpr int kQPer = 2;  // elements of q a thread has in flight
   for (uint32_t item = blockIdx.x; item < ap.n_items; item += gridDim.x) {
     const uint32_t split = item % ap.S, bk = item / ap.S, b = bk / P->KVl, kvh = bk - b * P->KVl;
     uint32_t k0, k1;
     ap.range(item, k0, k1);
     const bool owns_new = split == ap.S - 1;
-    const float rs = X.sh->rstd[b];
     const long long* arow = D.acc_in + (size_t)b * D.in_ld;
+    // apply_rope (functional.rs:197-204) on the finished q (and k) sums times 1/rms.  All loads first (one trip to L2):
+    // the two halves of every element pair this thread rotates, the table entry, and for the split that owns the new
+    // position the key and value sums as well.
+    long long kx1 = 0, kx2 = 0, vx = 0;
+    float2 kcs = make_float2(0.f, 0.f);
+    if (owns_new && (uint32_t)ct < hd) {
+      const uint32_t e = ct, f = e < half ? e : e - half, base = P->nq + kvh * hd;
+      kcs = table[f];
+      kx1 = __ldcg(arow + base + f); kx2 = __ldcg(arow + base + f + half);
+      vx = __ldcg(arow + P->nq + P->nkv + kvh * hd + e);
+    }
     const bool poisoned = __ldcg(D.poison_in + b) != 0;
-    // apply_rope (functional.rs:197-204) on the finished q (and k) sums times 1/rms
-    auto rotated = [&](uint32_t base, uint32_t e) {
-      const uint32_t f = e < half ? e : e - half;
-      const float2 cs = table[f];
-      const float x1 = unfix(__ldcg(arow + base + f)) * rs, x2 = unfix(__ldcg(arow + base + f + half)) * rs;
-      const float o = e < half ? x1 * cs.x + (-x2) * cs.y : x2 * cs.x + x1 * cs.y;
+    float rs = 0.0f;
+    auto rotate = [&](long long a1, long long a2, float2 cs, bool low) {
+      const float x1 = unfix(a1) * rs, x2 = unfix(a2) * rs;
+      const float o = low ? x1 * cs.x + (-x2) * cs.y : x2 * cs.x + x1 * cs.y;
       return poisoned ? __int_as_float(0x7fc00000) : o;
     };
-    for (uint32_t i = ct; i < rep * hd; i += kConsumers) {
-      const uint32_t r = i / hd, e = i - r * hd;
-      qs[i] = rotated((kvh * rep + r) * hd, e);
+#pragma unroll 1
+    for (uint32_t i0 = 0; i0 < rep * hd; i0 += kQPer * kConsumers) {
+      long long q1[kQPer], q2[kQPer];
+      float2 qcs[kQPer];
+#pragma unroll
+      for (int u = 0; u < kQPer; ++u) {
+        const uint32_t i = i0 + (uint32_t)ct + (uint32_t)u * kConsumers;
+        q1[u] = 0; q2[u] = 0; qcs[u] = make_float2(0.f, 0.f);
+        if (i < rep * hd) {
+          const uint32_t r = i / hd, e = i - r * hd, f = e < half ? e : e - half, base = (kvh * rep + r) * hd;
+          qcs[u] = table[f];
+          q1[u] = __ldcg(arow + base + f); q2[u] = __ldcg(arow + base + f + half);
+        }
+      }
+      if (!have_rs) { warp_rstd<MT>(X, D, rsv); have_rs = true; }
+      rs = rsv[0];
+#pragma unroll
+      for (int r = 1; r < MT; ++r) rs = b == (uint32_t)r ? rsv[r] : rs;
+#pragma unroll
+      for (int u = 0; u < kQPer; ++u) {
+        const uint32_t i = i0 + (uint32_t)ct + (uint32_t)u * kConsumers;
+        if (i < rep * hd) qs[i] = rotate(q1[u], q2[u], qcs[u], (i % hd) < half);
+      }
     }
-    if (owns_new) {  // KvBuf::append (transformer.rs:27-53): the new key (rotated) and value at position len
+    if (owns_new && (uint32_t)ct < hd) {  // KvBuf::append (transformer.rs:27-53): the new key (rotated) and value at position len
       const bool room = pos < P->cap;  // the host grows the cache before the step; never write past it
       if (!room && ct == 0) atomicCAS(X.c.status, 0, 5);
-      float* kd = D.kc + ((size_t)bk * P->cap + pos) * hd;
-      float* vd = D.vc + ((size_t)bk * P->cap + pos) * hd;
-      for (uint32_t e = ct; e < hd; e += kConsumers) {
-        const float kv = rotated(P->nq + kvh * hd, e);
-        float vv = unfix(__ldcg(arow + P->nq + P->nkv + kvh * hd + e)) * rs;
-        if (poisoned) vv = __int_as_float(0x7fc00000);
-        knew[e] = kv; vnew[e] = vv;
-        if (room) { kd[e] = kv; vd[e] = vv; }
+      const float kv = rotate(kx1, kx2, kcs, (uint32_t)ct < half);
+      const float vv = poisoned ? __int_as_float(0x7fc00000) : unfix(vx) * rs;
+      knew[ct] = kv; vnew[ct] = vv;
+      if (room) {
+        D.kc[((size_t)bk * P->cap + pos) * hd + ct] = kv;
+        D.vc[((size_t)bk * P->cap + pos) * hd + ct] = vv;
       }
     }
     bar_sync(1, kConsumers);
-    // this thread's outputs in the value step: head vr, elements 4 vc .. 4 vc + 3
-    const bool vact = (uint32_t)ct < rep * nq4;
-    const uint32_t vr = vact ? ct / nq4 : 0, vc = vact ? ct - vr * nq4 : 0;
     float run_m = -INFINITY, run_l = 0.0f;
     float4 run_o = make_float4(0.f, 0.f, 0.f, 0.f);
     const uint32_t nst = (k1 - k0 + ap.KS - 1) / ap.KS;
-    for (uint32_t j = 0; j < nst || (j == 0 && owns_new); ++j) {
-      const bool have = j < nst;
-      const uint32_t nk = have ? min(ap.KS, k1 - (k0 + j * ap.KS)) : 0;
-      const float* ks = reinterpret_cast<const float*>(X.slot_ptr(X.s));
-      const float* vs = reinterpret_cast<const float*>(X.slot_ptr(X.s) + kSlotBytes / 2);
-      if (have) X.wait(&X.sh->b.full[X.s % kSlots], (X.s / kSlots) & 1u, 20);
+    for (uint32_t j0 = 0; j0 < nst || (j0 == 0 && owns_new); j0 += kAttnBatch) {
+      const uint32_t nb = min(kAttnBatch, nst - min(nst, j0));            // stages of this batch
+      const uint32_t nk = nb ? min(nb * ap.KS, k1 - (k0 + j0 * ap.KS)) : 0u;  // their keys
+      const bool with_new = j0 == 0 && owns_new;
+      for (uint32_t j = 0; j < nb; ++j) X.wait(&X.sh->b.full[(X.s + j) % kSlots], ((X.s + j) / kSlots) & 1u, 20);
       // scores: a warp per key, the lanes share the head dimension, all heads of the group at once
       if (!X.aborted()) {
-        for (uint32_t kk = cw; kk < nk + ((j == 0 && owns_new) ? 1u : 0u); kk += kConvWarps) {
+        for (uint32_t kk = cw; kk < nk + (with_new ? 1u : 0u); kk += kConvWarps) {
           const bool is_new = kk >= nk;
-          const float4* krow = reinterpret_cast<const float4*>(is_new ? knew : ks + (size_t)kk * hd);
+          const uint32_t st = kk / ap.KS, row = kk - st * ap.KS;
+          const float4* krow = reinterpret_cast<const float4*>(is_new ? knew : reinterpret_cast<const float*>(X.slot_ptr(X.s + st)) + (size_t)row * hd);
           float a[8];
 #pragma unroll
           for (int r = 0; r < 8; ++r) a[r] = 0.0f;
@@ -1108,28 +1247,40 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
             if ((uint32_t)r < rep) {
 #pragma unroll
               for (int off = 16; off > 0; off >>= 1) a[r] += __shfl_xor_sync(0xFFFFFFFFu, a[r], off);
-              if (lane == 0) { if (is_new) snew[r] = a[r] * P->attn_scale; else sc[r * ap.KS + kk] = a[r] * P->attn_scale; }
+              if (lane == 0) sc[r * scld + (is_new ? scld - 1u : kk)] = a[r] * P->attn_scale;
             }
           }
         }
       }
       bar_sync(1, kConsumers);
+      // the new maximum of every head (each of its threads works it out), then the weights exp(score - max), shared out
+      float M = run_m;
       if (vact && !X.aborted()) {
-        const bool with_new = j == 0 && owns_new;
-        float M = run_m;
-        for (uint32_t kk = 0; kk < nk; ++kk) M = fmaxf(M, sc[vr * ap.KS + kk]);
-        if (with_new) M = fmaxf(M, snew[vr]);
+        for (uint32_t kk = 0; kk < nk; ++kk) M = fmaxf(M, sc[vr * scld + kk]);
+        if (with_new) M = fmaxf(M, sc[vr * scld + scld - 1u]);
+      }
+      bar_sync(1, kConsumers);   // every thread has read the scores it needs for the maximum
+      if (vact && !X.aborted()) {
+        for (uint32_t kk = vc; kk < nk; kk += nq4) sc[vr * scld + kk] = expf(sc[vr * scld + kk] - M);
+        if (with_new && vc == 0) sc[vr * scld + scld - 1u] = expf(sc[vr * scld + scld - 1u] - M);
+      }
+      bar_sync(1, kConsumers);
+      if (vact && !X.aborted()) {
         const float cr = run_m == -INFINITY ? 0.0f : expf(run_m - M);
         float Ls = run_l * cr;
         float4 O = make_float4(run_o.x * cr, run_o.y * cr, run_o.z * cr, run_o.w * cr);
-        for (uint32_t kk = 0; kk < nk; ++kk) {
-          const float pr = expf(sc[vr * ap.KS + kk] - M);
-          const float4 vv = reinterpret_cast<const float4*>(vs + (size_t)kk * hd)[vc];
-          Ls += pr;
-          O.x = fmaf(pr, vv.x, O.x); O.y = fmaf(pr, vv.y, O.y); O.z = fmaf(pr, vv.z, O.z); O.w = fmaf(pr, vv.w, O.w);
+        for (uint32_t st = 0, kk = 0; st < nb; ++st) {
+          const float* vs = reinterpret_cast<const float*>(X.slot_ptr(X.s + st) + kSlotBytes / 2);
+          const uint32_t rows = min(ap.KS, nk - kk);
+          for (uint32_t row = 0; row < rows; ++row, ++kk) {
+            const float pr = sc[vr * scld + kk];
+            const float4 vv = reinterpret_cast<const float4*>(vs + (size_t)row * hd)[vc];
+            Ls += pr;
+            O.x = fmaf(pr, vv.x, O.x); O.y = fmaf(pr, vv.y, O.y); O.z = fmaf(pr, vv.z, O.z); O.w = fmaf(pr, vv.w, O.w);
+          }
         }
         if (with_new) {
-          const float pr = expf(snew[vr] - M);
+          const float pr = sc[vr * scld + scld - 1u];
           const float4 vv = reinterpret_cast<const float4*>(vnew)[vc];
           Ls += pr;
           O.x = fmaf(pr, vv.x, O.x); O.y = fmaf(pr, vv.y, O.y); O.z = fmaf(pr, vv.z, O.z); O.w = fmaf(pr, vv.w, O.w);
@@ -1137,17 +1288,66 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
         run_m = M; run_l = Ls; run_o = O;
       }
       bar_sync(1, kConsumers);
-      if (have) {
-        if (cw < 4 && lane == 0) mbar_arrive(&X.sh->b.empty[X.s % kSlots]);  // count 4
-        ++X.s;
-      }
+      if (cw < 4 && lane == 0)
+        for (uint32_t j = 0; j < nb; ++j) mbar_arrive(&X.sh->b.empty[(X.s + j) % kSlots]);  // count 4
+      X.s += nb;
     }
+    // the split's part goes out; whoever completes the item merges
     if (vact) {
       float* rec = P->att_part + ((size_t)item * rep + vr) * (hd + 4u);
       *reinterpret_cast<float4*>(rec + 4u * vc) = run_o;
       if (vc == 0) { rec[hd] = run_m; rec[hd + 1] = run_l; }
     }
-    bar_sync(1, kConsumers);  // qs / knew are rewritten by the next item
+    bar_sync(1, kConsumers);
+    if (ct == 0) {
+      // release: the CTA's partial (ordered before by the barrier); acquire: the other splits' partials
+      unsigned old;
+      asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(P->att_cnt + bk) : "memory");
+      X.sh->att_last = old == ap.S - 1u;
+      if (old == ap.S - 1u) P->att_cnt[bk] = 0;  // for the next layer (ordered before it by the grid barriers in between)
+    }
+    bar_sync(1, kConsumers);  // also: qs / knew are rewritten by the next item
+    if (X.sh->att_last && !X.aborted()) {
+      const uint32_t stride = hd + 4u, S = ap.S;
+      const float* base0 = P->att_part + (size_t)(bk * S) * rep * stride;
+      // the splits' softmax statistics into shared memory (one load each), then every output thread merges in split order
+      for (uint32_t i = ct; i < rep * S; i += kConsumers) {
+        const uint32_t r = i / S, s2 = i - r * S;
+        const float* rec = base0 + ((size_t)s2 * rep + r) * stride;
+        wm[i] = __ldcg(rec + hd);
+        wm[rep * S + i] = __ldcg(rec + hd + 1);
+      }
+      bar_sync(1, kConsumers);
+      if (vact) {
+        const float* base = base0 + (size_t)vr * stride + 4u * vc;
+        float M = -INFINITY;
+        for (uint32_t s2 = 0; s2 < S; ++s2) M = fmaxf(M, wm[vr * S + s2]);
+        float Lsum = 0.0f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        constexpr uint32_t kB = 4;  // partial outputs in flight at once
+        for (uint32_t s0 = 0; s0 < S; s0 += kB) {
+          float4 ov[kB];
+#pragma unroll
+          for (uint32_t u = 0; u < kB; ++u)
+            if (s0 + u < S) ov[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(s0 + u) * rep * stride));
+#pragma unroll
+          for (uint32_t u = 0; u < kB; ++u) {
+            if (s0 + u < S) {
+              const float ms = wm[vr * S + s0 + u];
+              if (ms != -INFINITY) {
+                const float wgt = expf(ms - M);
+                Lsum = fmaf(wm[rep * S + vr * S + s0 + u], wgt, Lsum);
+                o.x = fmaf(ov[u].x, wgt, o.x); o.y = fmaf(ov[u].y, wgt, o.y); o.z = fmaf(ov[u].z, wgt, o.z); o.w = fmaf(ov[u].w, wgt, o.w);
+              }
+            }
+          }
+        }
+        const float inv = 1.0f / Lsum;
+        o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+        *reinterpret_cast<float4*>(P->att_out + (size_t)b * P->nq + (kvh * rep + vr) * hd + 4u * vc) = o;
+      }
+      bar_sync(1, kConsumers);  // wm is reused by the next item
+    }
   }
   if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 3);
 }
@@ -1157,15 +1357,18 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
 template <int MT>
 __device__ void final_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   const StepParams* P = X.c.sp;
-  bar_sync(1, kConsumers);
   if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
   bar_sync(1, kConsumers);
   phase_duties<MT>(X, D);
+  float rsv[MT];
+  warp_rstd<MT>(X, D, rsv);
   const int ct = X.tid - kWarpLeader * 32, cw = X.warp - kWarpLeader;
   const uint32_t n = P->Vl;
   const uint32_t a = (uint32_t)((uint64_t)n * blockIdx.x / gridDim.x), b = (uint32_t)((uint64_t)n * (blockIdx.x + 1) / gridDim.x);
-  for (uint32_t r = 0; r < X.c.m; ++r) {
-    const float rs = X.sh->rstd[r];
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    if ((uint32_t)r >= X.c.m) break;
+    const float rs = rsv[r];
     const bool poisoned = __ldcg(D.poison_in + r) != 0;
     int32_t bv = INT32_MIN, bj = -1;
     for (uint32_t j = a + ct; j < b; j += kConsumers) {
@@ -1196,7 +1399,6 @@ __device__ void final_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
 template <int MT>
 __device__ void pick_phase(Ctx<MT>& X, uint32_t p) {
   const StepParams* P = X.c.sp;
-  bar_sync(1, kConsumers);
   if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, blockIdx.x == 0);
   bar_sync(1, kConsumers);
   if (blockIdx.x != 0 || X.aborted()) return;
@@ -1220,7 +1422,6 @@ __device__ void pick_phase(Ctx<MT>& X, uint32_t p) {
 // f32 out of the accumulator, which is left zero (test program).
 template <int MT>
 __device__ void out_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
-  bar_sync(1, kConsumers);
   if (X.tid == kLeaderTid) grid_barrier<MT>(X, p, true);
   bar_sync(1, kConsumers);
   const int ct = X.tid - kWarpLeader * 32;
@@ -1235,15 +1436,17 @@ __device__ void out_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
 }
 
 template <int MT, typename Prog>
-__device__ void run_program(const Prog& prog, const Common& cm, unsigned char* smem, Shared* sh, uint32_t len) {
-  Ctx<MT> X;
-  X.smem = smem; X.sh = sh; X.c = cm;
+__device__ void run_program(const Prog& prog, unsigned char* smem, Shared* sh, uint32_t len) {
+  Ctx<MT> X(smem, sh);
   X.tid = threadIdx.x; X.lane = X.tid & 31; X.warp = X.tid >> 5;
   X.s = 0; X.mc0 = 0; X.mc1 = 0; X.mc2 = 0; X.sgc = 0; X.cur_phase = 0;
   if (X.tid == 0) {
     for (int i = 0; i < kSlots; ++i) { mbar_init(&sh->b.full[i], 1); mbar_init(&sh->b.empty[i], 4); }
     for (int i = 0; i < kGroups; ++i) { mbar_init(&sh->b.a_ready[i][0], 4); mbar_init(&sh->b.a_ready[i][1], 4); mbar_init(&sh->b.mma_done[i][0], 1); mbar_init(&sh->b.mma_done[i][1], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh->b.seg_done[i], 1); mbar_init(&sh->b.seg_free[i], 4); mbar_init(&sh->b.fin[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      for (int j = 0; j < 2; ++j) { mbar_init(&sh->b.seg_done[i][j], 2); mbar_init(&sh->b.seg_free[i][j], 4); }
+      mbar_init(&sh->b.fin[i], 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     sh->abort = 0;
   }
@@ -1263,9 +1466,16 @@ __device__ void run_program(const Prog& prog, const Common& cm, unsigned char* s
       for (uint32_t i = issued > (uint32_t)kSlots ? issued - kSlots : 0u; i < issued; ++i) mbar_wait(&sh->b.full[i % kSlots], (i / kSlots) & 1u);
     }
   } else {
+    const bool scribe = X.warp == kWarpIssuer1 && X.lane == 1;  // a lane with no role of its own writes the descriptors
+    if (scribe) prog.get(0, sh->D[0]);
+    bar_sync(1, kConsumers);
     for (uint32_t p = 0; p < np; ++p) {
-      PhaseDesc D;
-      prog.get(p, D);
+      // Between the phases: every warp of this CTA is done with phase p - 1 (the leader then joins the grid barrier
+      // inside the phase), and the descriptor of phase p, written during phase p - 1, is visible.  Phase p + 1's goes
+      // into a slot nobody reads any more, while the grid barrier is waited for.
+      if (p > 0) bar_sync(1, kConsumers);
+      if (scribe && p + 1 < np) prog.get(p + 1, sh->D[(p + 1) % 3u]);
+      const PhaseDesc& D = sh->D[p % 3u];
       switch (D.type) {
         case PH_GEMV: gemv_phase<MT>(X, D, p); break;
         case PH_ATTN: attn_phase<MT>(X, D, p, len); break;
@@ -1301,11 +1511,13 @@ __global__ void __launch_bounds__(kThreads, 1) pstep_kernel(const StepParams Pin
     reinterpret_cast<unsigned long long*>(lay)[i] = reinterpret_cast<const unsigned long long*>(P.layers)[i];
   const uint32_t len = (uint32_t)*P.len;
   __syncthreads();
-  Common cm;
-  cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
-  cm.sp = &P; cm.out = nullptr; cm.trace = P.trace;
+  if (threadIdx.x == 0) {
+    Common& cm = sh.c;
+    cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
+    cm.sp = &P; cm.out = nullptr; cm.trace = P.trace;
+  }
   StepProgram prog{P, lay};
-  run_program<MT>(prog, cm, smem, &sh, len);
+  run_program<MT>(prog, smem, &sh, len);
 }
 
 template <int MT>
@@ -1315,11 +1527,13 @@ __global__ void __launch_bounds__(kThreads, 1) pgemv_kernel(const GemvTestParams
   __shared__ GemvTestParams P;
   if (threadIdx.x == 0) P = Pin;
   __syncthreads();
-  Common cm;
-  cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
-  cm.sp = nullptr; cm.out = P.out; cm.trace = P.trace;
+  if (threadIdx.x == 0) {
+    Common& cm = sh.c;
+    cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
+    cm.sp = nullptr; cm.out = P.out; cm.trace = P.trace;
+  }
   TestProgram prog{P};
-  run_program<MT>(prog, cm, smem, &sh, 0u);
+  run_program<MT>(prog, smem, &sh, 0u);
 }
 
 template <typename K>

@@ -62,6 +62,8 @@ struct StepParams {
   long long* acc_qkv; long long* acc_o; long long* acc_gu; long long* acc_dn; long long* acc_logits;
   int* poison;              // [5][kMaxRows]: non-finite partial sums seen for an accumulator row
   float* att_part;          // attention partials [m*KVl*splits][rep][hd + 4]
+  float* att_out;           // merged attention output [m][nq], f32
+  unsigned* att_cnt;        // [m*KVl] splits that have finished an item; back to zero when the item is merged
   float* logits;            // f32 [m][Vl]
   int2* arg_slots;          // [gridDim][kMaxRows] best (ordered value, column) per CTA
   unsigned* bar;            // grid barrier counter (monotonic)
