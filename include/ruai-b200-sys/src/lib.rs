@@ -104,6 +104,10 @@ extern "C" {
     // ---- Backend::matmul_int8 / dequant_int4 / matmul_int4 (backend/mod.rs:675-704) ----
     pub fn ruai_matmul_q(ctx: *mut ruai_ctx, x_dtype: c_int, x_dev: *const c_void, w: *const ruai_qweight, bias_dev_or_null: *const f32, out_dev: *mut c_void, m: u32) -> c_int;
     pub fn ruai_matmul_q_static(ctx: *mut ruai_ctx, x_dtype: c_int, x_dev: *const c_void, w: *const ruai_qweight, bias_dev_or_null: *const f32, out_dev: *mut c_void, m: u32) -> c_int;
+    pub fn ruai_matmul_q_grad_input(ctx: *mut ruai_ctx, g_dev: *const f32, w: *const ruai_qweight, dx_dev: *mut f32, m: u32) -> c_int;
+    pub fn ruai_linear_lora_forward(ctx: *mut ruai_ctx, x_dev: *const f32, w: *const ruai_qweight, lora_a_dev: *const f32, lora_b_dev: *const f32, rank: u32, scale: f32, bias_dev_or_null: *const f32, out_dev: *mut f32, m: u32) -> c_int;
+    pub fn ruai_sample(ctx: *mut ruai_ctx, logits_dev: *const f32, vocab: u32, temperature: f32, top_k: u32, top_p: f32, rng_state: *mut u64, token_host: *mut i32) -> c_int;
+    pub fn ruai_model_generate_sampled(m: *mut ruai_model, prompt_host: *const i32, T: u32, n_new: u32, temperature: f32, top_k: u32, top_p: f32, seed: u64, out_ids_host: *mut i32) -> c_int;
     pub fn ruai_matmul_q_stream(ctx: *mut ruai_ctx, x_dev: *const f32, w: *const ruai_qweight, out_dev: *mut f32, m: u32, repeat: u32) -> c_int;
     pub fn ruai_dequant_int4(ctx: *mut ruai_ctx, w: *const ruai_qweight, out_dev: *mut f32) -> c_int;
     pub fn ruai_dequant_int4_ref(ctx: *mut ruai_ctx, q_dev: *const i8, scale_dev: *const f32, k: u32, n: u32, group: u32, out_dev: *mut f32) -> c_int;
@@ -116,6 +120,8 @@ extern "C" {
     pub fn ruai_model_set_f32(m: *mut ruai_model, tensor_id: u64, data_host: *const f32, count: usize) -> c_int;
     pub fn ruai_model_set_quantized(m: *mut ruai_model, tensor_id: u64, q_host: *const i8, scale_host: *const f32, bits: u32, group: u32) -> c_int;
     pub fn ruai_model_get_f32(m: *mut ruai_model, tensor_id: u64, out_host: *mut f32, count: usize) -> c_int;
+    pub fn ruai_model_use_persistent_step(m: *mut ruai_model, on: c_int) -> c_int;
+    pub fn ruai_model_uses_persistent_step(m: *mut ruai_model, B: u32) -> c_int;
     pub fn ruai_model_quantize(m: *mut ruai_model, bits: u32, group: u32) -> c_int;
     pub fn ruai_model_get_linear(m: *mut ruai_model, tensor_id: u64, q_host: *mut i8, scale_host: *mut f32) -> c_int;
     pub fn ruai_model_forward_cached(m: *mut ruai_model, ids_host: *const i32, b: u32, t: u32, logits_host_or_null: *mut f32, all_positions: c_int) -> c_int;

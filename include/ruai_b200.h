@@ -120,6 +120,16 @@ int ruai_qweight_info(const ruai_qweight* w, uint32_t* k, uint32_t* n, uint32_t*
  * x_dtype, bias_dev_or_null is f32 [n].  Arithmetic is f32.                 */
 int ruai_matmul_q(ruai_ctx* ctx, int x_dtype, const void* x_dev, const ruai_qweight* w,
                   const float* bias_dev_or_null, void* out_dev, uint32_t m);
+/* Backward of `Tensor::matmul_int8` / `matmul_int4` (ops.rs:705-709, 731-734): the weights are frozen, the only
+ * gradient is dx[m,k] = g[m,n] @ dequant(W)^T.  The reference materialises the f32 weight for it; here the packed
+ * weight is read once per row of g.  f32 in, f32 out, m <= 65535.                                                   */
+int ruai_matmul_q_grad_input(ruai_ctx* ctx, const float* g_dev, const ruai_qweight* w, float* dx_dev, uint32_t m);
+/* `Linear::forward` of a quantized layer with a LoRA adapter (layers.rs:169-190; add_lora 84-97), QLoRA-style:
+ * out = matmul_q(x) + (x @ A @ B) * scale + bias, A [k,rank], B [rank,n] row-major f32, scale = alpha / rank,
+ * in the reference's order of additions.  f32 activations; rank 1..1024.                                           */
+int ruai_linear_lora_forward(ruai_ctx* ctx, const float* x_dev, const ruai_qweight* w, const float* lora_a_dev,
+                             const float* lora_b_dev, uint32_t rank, float scale, const float* bias_dev_or_null,
+                             float* out_dev, uint32_t m);
 /* ruai_matmul_q for hosts that cannot let this library allocate device memory at run time
  * (a serving process whose framework already owns the whole device, or a loop that cannot
  * afford cudaMalloc's implicit synchronisation).  Same arguments, same results.  It has no
@@ -200,6 +210,14 @@ int ruai_model_set_quantized(ruai_model* m, uint64_t tensor_id, const int8_t* q_
 /* Read back one f32 tensor of a loaded model (embeddings, norm parameters, GPT-2 biases): the
  * parameters `state_dict()` of a quantized model still holds (llama.rs:559-578, gpt2.rs:344-358). */
 int ruai_model_get_f32(ruai_model* m, uint64_t tensor_id, float* out_host, size_t count);
+/* Which of the two implementations of a single-token greedy step (ruai_model_decode_step, ruai_model_generate) the
+ * model uses: the chain of launches, one kernel per Linear / attention (default), or ONE persistent cooperative kernel
+ * per token (on != 0; Llama-shaped quantized models, one GPU, at most two sequences; other cases keep the chain).
+ * Both compute the reference's step (llama.rs:441-463); they differ in speed and in the last bits of the logits.
+ * Without a call the environment decides (RUAI_B200_PSTEP=1 selects the persistent kernel).
+ * ruai_model_uses_persistent_step: 1 if steps of B sequences would run as the persistent kernel now. */
+int ruai_model_use_persistent_step(ruai_model* m, int on);
+int ruai_model_uses_persistent_step(ruai_model* m, uint32_t B);
 /* `Llama::quantize_int8` / `quantize_int4(group)` over the f32 tensors set so far. */
 int ruai_model_quantize(ruai_model* m, uint32_t bits, uint32_t group);
 /* Read back one block Linear (or the head, tensor id RUAI_T_LMHEAD) in the
@@ -221,6 +239,16 @@ int ruai_model_cache_len(const ruai_model* m, uint32_t* len, uint32_t* capacity)
  * maximum context.  out_ids_host receives T + n_new ids (prompt first).     */
 int ruai_model_generate(ruai_model* m, const int32_t* prompt_host, uint32_t T, uint32_t n_new,
                         int32_t* out_ids_host);
+
+/* `generate` with `Sampler::new(temperature, top_k, top_p, seed)` (generation.rs:28-73, 83-113): as above, but the
+ * next token is drawn on the device from the step's logits (temperature <= 0: greedy; top_k 0 = no limit; top_p 1 =
+ * off).  Equal logits are ordered by ascending index (the reference's unstable sort leaves this open).  One GPU. */
+int ruai_model_generate_sampled(ruai_model* m, const int32_t* prompt_host, uint32_t T, uint32_t n_new,
+                                float temperature, uint32_t top_k, float top_p, uint64_t seed, int32_t* out_ids_host);
+/* `Sampler::sample` on one row of f32 logits in device memory; *rng_state is the sampler's SplitMix64 state
+ * (rand.rs:29-41), advanced by one draw when temperature > 0. */
+int ruai_sample(ruai_ctx* ctx, const float* logits_dev, uint32_t vocab, float temperature, uint32_t top_k, float top_p,
+                uint64_t* rng_state, int32_t* token_host);
 
 /* One decode step that never leaves the device: the ids are read from
  * ids_dev_or_null [B] (NULL: the argmax of the previous step), the argmax of

@@ -146,6 +146,28 @@ def matmul_int4(x, q, scale):
     return out
 
 
+def dequant(bits, q, scale, group=32):
+    """The f32 weight the reference's backward materialises: q * scales (ops.rs:707) or dequant_int4 (ops.rs:732)."""
+    if bits == 8:
+        return np.ascontiguousarray(q, np.int8).astype(np.float32) * _f32(scale)[None, :]
+    return dequant_int4(q, scale, group)
+
+
+def matmul_q_grad_input(bits, g, q, scale, group=32):
+    """Backward of matmul_int8 / matmul_int4 (ops.rs:705-709, 731-734): dx = g @ dequant(W)^T, f32."""
+    return (_f32(g) @ dequant(bits, q, scale, group).T).astype(np.float32)
+
+
+def linear_lora_forward(bits, x, q, scale, lora_a, lora_b, lora_scale, bias=None):
+    """Linear::forward with an adapter (layers.rs:169-190): quantized base, + (x @ A @ B) * scale, + bias, in that order."""
+    x = _f32(x)
+    y = matmul_int8(x, q, scale) if bits == 8 else matmul_int4(x, q, scale)
+    y = y + ((x @ _f32(lora_a)) @ _f32(lora_b)) * np.float32(lora_scale)
+    if bias is not None:
+        y = y + _f32(bias)
+    return y.astype(np.float32)
+
+
 def rms_norm(x, w, eps):
     x = _f32(x)
     y = np.empty_like(x)
@@ -204,6 +226,25 @@ def argmax(logits):
     """`generation::argmax` (generation.rs:6-8): last index among equal maxima."""
     logits = _f32(logits)
     return int(lib().orc_argmax(logits, logits.size))
+
+
+class Sampler:
+    """`Sampler` (generation.rs:15-73); equal logits ordered by ascending index."""
+
+    def __init__(self, temperature, top_k=0, top_p=1.0, seed=0):
+        self.temperature, self.top_k, self.top_p = float(temperature), int(top_k), float(top_p)
+        self.state = C.c_uint64(seed)
+        self.margin = 1.0
+
+    def sample(self, logits):
+        logits = _f32(logits)
+        mg = C.c_float(1.0)
+        L = lib()
+        L.orc_sample.restype = u32
+        L.orc_sample.argtypes = [_fp, u32, C.c_float, u32, C.c_float, C.POINTER(C.c_uint64), C.POINTER(C.c_float)]
+        tok = L.orc_sample(logits, logits.size, self.temperature, self.top_k, self.top_p, C.byref(self.state), C.byref(mg))
+        self.margin = float(mg.value)
+        return int(tok)
 
 
 def synth_normal(seed, tensor_id, shape, std=0.02):
@@ -273,6 +314,19 @@ class Model:
         if rc:
             raise RuntimeError(f"oracle generate failed ({rc})")
         return (out, tr) if trace else out
+
+    def generate_sampled(self, prompt, n, temperature, top_k=0, top_p=1.0, seed=0):
+        """`generate` with `Sampler::new(...)`: returns (ids, margins [n]) (see orc_sample for the margin)."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.empty(prompt.size + n, np.int32)
+        mg = np.empty(n, np.float32)
+        L = lib()
+        L.orc_model_generate_sampled.restype = C.c_int
+        L.orc_model_generate_sampled.argtypes = [C.c_void_p, _i32p, u32, u32, C.c_float, u32, C.c_float, C.c_uint64, _i32p, _fp]
+        rc = L.orc_model_generate_sampled(self.h, prompt, prompt.size, n, float(temperature), int(top_k), float(top_p), int(seed), out, mg)
+        if rc:
+            raise RuntimeError(f"oracle generate_sampled failed ({rc})")
+        return out, mg
 
     def get_linear(self, tensor_id, bits, group=32):
         """(q, scale) of one Linear in the reference's buffer layout; tensor ids as in ruai_b200_synth.h."""

@@ -571,10 +571,92 @@ ORC int orc_model_get_linear(void* h, uint64_t id, int8_t* q, float* scale, uint
   return 0;
 }
 
+// Rng::next_u64 / Rng::unit, src/nn/rand.rs:29-41 (SplitMix64; 24 random bits).
+static float rng_unit(uint64_t* state) {
+  *state += 0x9e3779b97f4a7c15ull;
+  uint64_t z = *state;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  z ^= z >> 31;
+  return (float)(z >> 40) / (float)(1ull << 24);
+}
+ORC float orc_rng_unit(uint64_t* state) { return rng_unit(state); }
+
+// Sampler::sample, src/nn/generation.rs:38-73.  The reference's sort_unstable_by leaves the order of equal logits
+// open; equal logits go by ascending index here.  margin (optional) receives the smallest distance, in probability
+// mass, between a comparison the sampler made and its threshold at the position it decided on (top_p cut, draw): a draw
+// whose margin is below the rounding differences of exp may fall the other way on another implementation.
+ORC uint32_t orc_sample(const float* logits, uint32_t n, float temperature, uint32_t top_k, float top_p, uint64_t* state, float* margin) {
+  if (margin) *margin = 1.0f;
+  if (temperature <= 0.0f) return orc_argmax(logits, n);
+  auto key = [&](uint32_t i) {
+    int32_t b;
+    std::memcpy(&b, &logits[i], 4);
+    return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1);  // total_cmp
+  };
+  std::vector<uint32_t> idx(n);
+  for (uint32_t i = 0; i < n; ++i) idx[i] = i;
+  std::sort(idx.begin(), idx.end(), [&](uint32_t a, uint32_t b) {
+    const int32_t ka = key(a), kb = key(b);
+    return ka != kb ? ka > kb : a < b;
+  });
+  if (top_k > 0) idx.resize(std::min<size_t>(top_k, idx.size()));
+  const float m = logits[idx[0]];
+  std::vector<float> probs(idx.size());
+  for (size_t i = 0; i < idx.size(); ++i) probs[i] = std::exp((logits[idx[i]] - m) / temperature);
+  float total = 0.0f;
+  for (float p : probs) total += p;
+  for (float& p : probs) p /= total;
+  float mg = 1.0f;
+  if (top_p < 1.0f) {
+    float acc = 0.0f;
+    size_t keep = probs.size();
+    for (size_t i = 0; i < probs.size(); ++i) {
+      const float before = acc;
+      acc += probs[i];
+      if (acc >= top_p) {
+        keep = i + 1;
+        mg = std::min(mg, std::min(acc - top_p, top_p - before));
+        break;
+      }
+    }
+    probs.resize(keep);
+    idx.resize(keep);
+  }
+  float sum = 0.0f;
+  for (float p : probs) sum += p;
+  const float r = rng_unit(state) * sum;
+  float acc = 0.0f;
+  uint32_t pick = idx.back();
+  for (size_t i = 0; i < probs.size(); ++i) {
+    const float before = acc;
+    acc += probs[i];
+    if (r < acc) {
+      pick = idx[i];
+      mg = std::min(mg, std::min(acc - r, r - before));
+      break;
+    }
+  }
+  if (margin) *margin = mg;
+  return pick;
+}
+
 // generate_cached with Sampler::greedy, src/nn/generation.rs:83-113.
 // out receives T + n ids; logits_trace (optional) receives the n logit rows.
+static int generate_with(void* h, const int32_t* prompt, uint32_t T, uint32_t n, int32_t* out, float* logits_trace, bool sampled, float temperature,
+                         uint32_t top_k, float top_p, uint64_t seed, float* margins);
 ORC int orc_model_generate(void* h, const int32_t* prompt, uint32_t T, uint32_t n, int32_t* out, float* logits_trace) {
+  return generate_with(h, prompt, T, n, out, logits_trace, false, 0.0f, 0, 1.0f, 0, nullptr);
+}
+// generate_cached with Sampler::new(temperature, top_k, top_p, seed); margins (optional) [n]: see orc_sample.
+ORC int orc_model_generate_sampled(void* h, const int32_t* prompt, uint32_t T, uint32_t n, float temperature, uint32_t top_k, float top_p, uint64_t seed,
+                                   int32_t* out, float* margins) {
+  return generate_with(h, prompt, T, n, out, nullptr, true, temperature, top_k, top_p, seed, margins);
+}
+static int generate_with(void* h, const int32_t* prompt, uint32_t T, uint32_t n, int32_t* out, float* logits_trace, bool sampled, float temperature,
+                         uint32_t top_k, float top_p, uint64_t seed, float* margins) {
   Model* M = (Model*)h;
+  uint64_t state = seed;
   if (T == 0) return 1;
   const uint32_t max_len = M->max_pos;
   std::vector<int32_t> ids(prompt, prompt + T);
@@ -589,7 +671,9 @@ ORC int orc_model_generate(void* h, const int32_t* prompt, uint32_t T, uint32_t 
     int rc = forward_cached(*M, pending.data(), 1, (uint32_t)pending.size(), logits.data(), false);
     if (rc) return rc;
     if (logits_trace) std::memcpy(logits_trace + (size_t)s * M->V, logits.data(), M->V * sizeof(float));
-    const int32_t next = (int32_t)orc_argmax(logits.data(), M->V);
+    float mg = 1.0f;
+    const int32_t next = sampled ? (int32_t)orc_sample(logits.data(), M->V, temperature, top_k, top_p, &state, &mg) : (int32_t)orc_argmax(logits.data(), M->V);
+    if (margins) margins[s] = mg;
     ids.push_back(next);
     pending.assign(1, next);
   }

@@ -63,6 +63,10 @@ _PROTOS = {
     "ruai_qweight_info": (C.c_int, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
     "ruai_matmul_q": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32]),
     "ruai_matmul_q_static": (C.c_int, [vp, C.c_int, vp, vp, vp, vp, u32]),
+    "ruai_matmul_q_grad_input": (C.c_int, [vp, vp, vp, vp, u32]),
+    "ruai_linear_lora_forward": (C.c_int, [vp, vp, vp, vp, vp, u32, C.c_float, vp, vp, u32]),
+    "ruai_sample": (C.c_int, [vp, vp, u32, C.c_float, u32, C.c_float, C.POINTER(u64), C.POINTER(i32)]),
+    "ruai_model_generate_sampled": (C.c_int, [vp, vp, u32, u32, C.c_float, u32, C.c_float, u64, vp]),
     "ruai_matmul_q_stream": (C.c_int, [vp, vp, vp, vp, u32, u32]),
     "ruai_ctx_set_wait_limit": (C.c_int, [vp, C.c_uint]),
     "ruai_ctx_inject_barrier_skew": (C.c_int, [vp, C.c_uint]),
@@ -76,6 +80,8 @@ _PROTOS = {
     "ruai_model_quantize": (C.c_int, [vp, u32, u32]),
     "ruai_model_set_quantized": (C.c_int, [vp, u64, vp, vp, u32, u32]),
     "ruai_model_get_f32": (C.c_int, [vp, u64, vp, C.c_size_t]),
+    "ruai_model_use_persistent_step": (C.c_int, [vp, C.c_int]),
+    "ruai_model_uses_persistent_step": (C.c_int, [vp, u32]),
     "ruai_model_get_linear": (C.c_int, [vp, u64, vp, vp]),
     "ruai_model_forward_cached": (C.c_int, [vp, vp, u32, u32, vp, C.c_int]),
     "ruai_model_cache_clear": (C.c_int, [vp]),

@@ -42,6 +42,9 @@ struct ruai_ctx {
   unsigned barrier_skew = 0;       // failure injection: extra arrivals (in grids) the next persistent launch will wait for in vain
   unsigned* ps_sync = nullptr;     // [0] grid barrier counter, [1] abort flag, [2..3] poison, for ruai_matmul_q_stream
   unsigned ps_bar_base = 0;
+  // sampler scratch (sample.cu): sort keys, probabilities, the sort's temporary storage
+  void* sample_buf = nullptr;
+  size_t sample_bytes = 0;
 };
 
 enum QLayout : uint32_t {

@@ -76,6 +76,7 @@ RUAI_API int ruai_ctx_destroy(ruai_ctx* c) {
   cudaFree(c->counters);
   cudaFree(c->status);
   cudaFree(c->ps_sync);
+  cudaFree(c->sample_buf);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->stream);

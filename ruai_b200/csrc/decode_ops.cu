@@ -112,7 +112,7 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, uint32_t h
 // grid (B*T, Hq + KV); thread i < hd/2 handles the pair (i, i + hd/2).
 __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_t k_off, uint32_t v_off, const float2* __restrict__ table,
                                const int32_t* __restrict__ len, uint32_t T, uint32_t Hq, uint32_t KV, uint32_t hd, uint32_t cap,
-                               float* __restrict__ kcache, float* __restrict__ vcache) {
+                               float* __restrict__ kcache, float* __restrict__ vcache, int* __restrict__ status) {
   grid_dependency_wait();
   grid_launch_dependents();
   const uint32_t r = blockIdx.x, b = r / T, t = r % T, head = blockIdx.y, half = hd / 2;
@@ -129,6 +129,10 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t qkv_ld, uint32_
     }
   } else {
     const uint32_t h = head - Hq;
+    if (pos >= cap) {  // never write past the cache (see attention_kernel)
+      if (threadIdx.x == 0 && status) atomicCAS(status, 0, 5);
+      return;
+    }
     const float* k = row + k_off + (size_t)h * hd;
     const float* v = row + v_off + (size_t)h * hd;
     float* kd = kcache + (((size_t)b * KV + h) * cap + pos) * hd;
@@ -194,11 +198,16 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP * SUB) attention_kernel(c
   }
   __syncthreads();
   uint32_t past = 0, pos = 0, n_keys = 0, n_cached = 0, k0 = 0, k1 = 0;
+  bool over = false;
   auto plan = [&]() {
     past = (uint32_t)*p.len;
     pos = past + t;
     n_keys = pos + 1;  // causal_mask_offset, functional.rs:238-247
     n_cached = p.fuse ? n_keys - 1 : n_keys;
+    // The host grows the cache before the step, so a position at or past the capacity means the device's position
+    // word is not the host's: touch nothing of the cache, leave an error for the host (the step's output is void).
+    over = pos >= p.cap;
+    if (over) n_cached = 0;
     const uint32_t per = (n_cached + gridDim.z - 1) / gridDim.z;
     k0 = min(n_cached, split * per);
     k1 = min(n_cached, k0 + per);
@@ -225,6 +234,7 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP * SUB) attention_kernel(c
     if (tid == 0 && k1 > k0) fetch_chunk(k0);
   }
   const bool owns_new = p.fuse && split == gridDim.z - 1;
+  if (over && tid == 0 && p.status) atomicCAS(p.status, 0, 5);
   const float* row = p.q + (size_t)(b * p.T + t) * p.q_ld;
   const float* qrow = row + (size_t)kvh * REP * hd;
   const bool rot = p.fuse && p.table != nullptr;
@@ -252,8 +262,10 @@ __global__ void __launch_bounds__(kAttnChunkKeys * REP * SUB) attention_kernel(c
       const float vv = vr[e];
       knew[e] = kvv;
       vnew[e] = vv;
-      kbase[(size_t)pos * hd + e] = kvv;
-      vbase[(size_t)pos * hd + e] = vv;
+      if (!over) {
+        kbase[(size_t)pos * hd + e] = kvv;
+        vbase[(size_t)pos * hd + e] = vv;
+      }
     }
   }
   __syncthreads();
@@ -600,7 +612,7 @@ int ruai_rope_kv(ruai_ctx* c, float* qkv, uint32_t qkv_ld, uint32_t k_off, uint3
                  uint32_t T, uint32_t Hq, uint32_t KV, uint32_t hd, uint32_t cap, float* kcache, float* vcache) {
   const unsigned threads = hd / 2 >= 64 ? 64 : 32;
   RUAI_CUDA(c, ruai_launch(c, rope_kv_kernel, dim3(rows, Hq + KV), dim3(threads), 0, true, qkv, qkv_ld, k_off, v_off, table, len, T, Hq, KV, hd, cap,
-                           kcache, vcache));
+                           kcache, vcache, c->status));
   return RUAI_OK;
 }
 

@@ -295,9 +295,13 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
         gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 4));
         // gmax < 2^e with e = biased exponent - 126; f = round(v * 2^(20-e)), x = f * 2^(e-20)
         const uint32_t eb = __float_as_uint(gmax) >> 23;
-        const bool nz = eb >= 20u && eb < 255u;
+        // a NaN or an infinity anywhere in the group (fmaxf drops NaN, so it is looked for on its own): the group's
+        // scale becomes NaN and with it this row's sums, as in f32 arithmetic (cpu.rs:1035-1067 propagates them)
+        bool bad = !(fabsf(xv.x) <= 3.402823466e38f && fabsf(xv.y) <= 3.402823466e38f && fabsf(xv.z) <= 3.402823466e38f && fabsf(xv.w) <= 3.402823466e38f);
+        bad = ((__ballot_sync(0xFFFFFFFFu, bad) >> (lane & 24)) & 0xFFu) != 0u;
+        const bool nz = eb >= 20u && eb < 255u && !bad;
         const float up = nz ? __uint_as_float((273u - eb) << 23) : 0.0f;
-        const float xscale = nz ? __uint_as_float((eb - 19u) << 23) : 0.0f;
+        const float xscale = bad ? __int_as_float(0x7fc00000) : (nz ? __uint_as_float((eb - 19u) << 23) : 0.0f);
         const float vv[4] = {xv.x, xv.y, xv.z, xv.w};
         uint32_t w0 = 0, w1 = 0, w2 = 0;
         int fs = 0;

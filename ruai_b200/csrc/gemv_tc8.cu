@@ -194,7 +194,12 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
       }
       return v;
     };
-    auto max4 = [](float mx, const float4& v) { return fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w))); };
+    // (fmaxf drops NaN: a NaN or an infinity in the row is looked for on its own and makes the maximum infinite, which
+    // turns the row's scale and with it its sums into NaN, as f32 arithmetic would: cpu.rs:1002-1029 propagates them)
+    auto max4 = [](float mx, const float4& v) {
+      const bool fin = fabsf(v.x) <= 3.402823466e38f && fabsf(v.y) <= 3.402823466e38f && fabsf(v.z) <= 3.402823466e38f && fabsf(v.w) <= 3.402823466e38f;
+      return fin ? fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w))) : INFINITY;
+    };
     auto row_max = [&](int r, float mx) {  // 128-thread maximum of one row: warp part here, the rest after the barrier
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
@@ -206,7 +211,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
       for (int w2 = 0; w2 < kCols / 32; ++w2) gmax = fmaxf(gmax, s_max[r][w2]);
       const uint32_t eb = __float_as_uint(gmax) >> 23;
       const bool nz = eb >= 27u && eb < 255u;
-      if (tid == 0) s_xscale[r] = nz ? __uint_as_float((eb - 26u) << 23) : 0.0f;  // 2^(e - 27), e = eb - 126
+      if (tid == 0) s_xscale[r] = eb == 255u ? __int_as_float(0x7fc00000) : (nz ? __uint_as_float((eb - 26u) << 23) : 0.0f);  // 2^(e - 27), e = eb - 126
       return nz ? __uint_as_float((280u - eb) << 23) : 0.0f;
     };
     // digits of four consecutive k of row r into the B operand: group g = 32 k, [k-half][n/8][n%8][16 bytes]
@@ -302,7 +307,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc_int8_kernel(const Params p, 
           for (uint32_t kk = kbeg + tid; kk < kend; kk += kCols) {
             float v = load_as_f32(p.x, p.x_dtype, (size_t)(m0 + r) * p.x_ld + kk);
             if (normed) v *= p.pro.norm_w[kk];
-            mx = fmaxf(mx, fabsf(v));
+            mx = fabsf(v) <= 3.402823466e38f ? fmaxf(mx, fabsf(v)) : INFINITY;
           }
         row_max(r, mx);
       }

@@ -89,6 +89,7 @@ struct Layer {
 // Device state of the persistent decode step (pstep.cu).
 struct PStep {
   bool tried = false, usable = false;
+  int wanted = -1;  // -1: the environment decides (RUAI_B200_PSTEP=1 turns it on), 0 / 1: ruai_model_use_persistent_step
   DevBuf layers, x, ss, acc, poison, att_part, arg_slots, sync;  // sync: [0] barrier counter, [1] abort flag
   unsigned bar_base = 0;
   uint32_t table_cap = 0, table_B = 0, splits = 0, att_rows = 0;
@@ -643,7 +644,8 @@ bool pstep_eligible(ruai_model* m, uint32_t B) {
   if (!S.tried) {
     S.tried = true;
     const char* env = getenv("RUAI_B200_PSTEP");
-    bool ok = !(env && env[0] == '0') && m->llama && m->world == 1 && m->quantized && m->L >= 1 && m->L <= (uint32_t)ps::kMaxLayers;
+    const bool wanted = S.wanted >= 0 ? S.wanted == 1 : (env && env[0] == '1');  // the launch chain is the default
+    bool ok = wanted && m->llama && m->world == 1 && m->quantized && m->L >= 1 && m->L <= (uint32_t)ps::kMaxLayers;
     ok = ok && m->d % 32 == 0 && m->hd % 4 == 0 && m->hd <= 256 && m->KVl > 0;
     const uint32_t rep = m->KVl ? m->Hl / m->KVl : 0;
     ok = ok && rep >= 1 && rep <= 8 && rep * (m->hd / 4) <= 448u && m->fl % 4 == 0;
@@ -758,6 +760,19 @@ int prepare_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions) {
 // ---- C ABI ---------------------------------------------------------------------------------
 
 static int run_decode_graph(ruai_model* m, uint32_t B);
+
+RUAI_API int ruai_model_use_persistent_step(ruai_model* m, int on) {
+  if (!m) return RUAI_ERR_ARG;
+  RUAI_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  m->ps.wanted = on ? 1 : 0;
+  m->ps.tried = false;
+  m->len_dirty = true;  // the two paths keep the position in different places; the host's copy is uploaded again
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_model_uses_persistent_step(ruai_model* m, uint32_t B) {
+  return m && pstep_eligible(m, B) ? 1 : 0;
+}
 
 RUAI_API int ruai_llama_create(ruai_ctx* c, const ruai_llama_config* cfg, const ruai_tp* tp, ruai_model** out) {
   if (!c || !cfg || !out) return ruai_fail(c, RUAI_ERR_ARG, "ruai_llama_create: NULL argument");
@@ -1149,7 +1164,23 @@ RUAI_API int ruai_model_step_bytes(const ruai_model* m, uint32_t B, uint32_t len
 }
 
 // generate_cached with Sampler::greedy (generation.rs:83-113): batch 1, sliding window.
+namespace {
+struct SamplerArgs { float temperature; uint32_t top_k; float top_p; uint64_t state; };
+}
+static int generate_impl(ruai_model* m, const int32_t* prompt, uint32_t T, uint32_t n_new, SamplerArgs* sampler, int32_t* out);
+
 RUAI_API int ruai_model_generate(ruai_model* m, const int32_t* prompt, uint32_t T, uint32_t n_new, int32_t* out) {
+  return generate_impl(m, prompt, T, n_new, nullptr, out);
+}
+
+RUAI_API int ruai_model_generate_sampled(ruai_model* m, const int32_t* prompt, uint32_t T, uint32_t n_new, float temperature, uint32_t top_k, float top_p,
+                                         uint64_t seed, int32_t* out) {
+  SamplerArgs sa{temperature, top_k, top_p, seed};  // Sampler::new (generation.rs:28-30)
+  if (m && m->world > 1) return model_fail(m, RUAI_ERR_UNSUPPORTED, "sampling needs the whole vocabulary on one GPU: the head of this model is sharded");
+  return generate_impl(m, prompt, T, n_new, temperature > 0.0f ? &sa : nullptr, out);
+}
+
+static int generate_impl(ruai_model* m, const int32_t* prompt, uint32_t T, uint32_t n_new, SamplerArgs* sampler, int32_t* out) {
   if (!m || !prompt || !out) return ruai_fail(m ? m->ctx : nullptr, RUAI_ERR_ARG, "ruai_model_generate: NULL argument");
   if (T == 0) return model_fail(m, RUAI_ERR_ARG, "prompt must not be empty");
   ruai_ctx* c = m->ctx;
@@ -1185,6 +1216,11 @@ RUAI_API int ruai_model_generate(ruai_model* m, const int32_t* prompt, uint32_t 
       m->len_dirty = false;
       RUAI_TRY(issue_step(m, 1, Tn, false, true));
       m->len += Tn;
+      RUAI_CUDA(c, cudaMemcpyAsync(&next, m->d_ids.p, sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
+      RUAI_TRY(check_device_status(m));
+    }
+    if (sampler) {  // the step left the argmax in d_ids; the sampled token replaces it there
+      RUAI_TRY(ruai_sample_device(c, m->logits.as<float>(), m->V, sampler->temperature, sampler->top_k, sampler->top_p, &sampler->state, m->d_ids.as<int32_t>()));
       RUAI_CUDA(c, cudaMemcpyAsync(&next, m->d_ids.p, sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
       RUAI_TRY(check_device_status(m));
     }

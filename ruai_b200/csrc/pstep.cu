@@ -1,47 +1,55 @@
 // The persistent decode step: ONE cooperative kernel per generated token.
 //
-// It replaces, for Llama-shaped models and up to two sequences, the chain of launches that
-// Llama::run (src/nn/modules/llama.rs:441-463; DecoderLayer::forward 306-309; Attention::forward
-// 248-277) becomes on a GPU: per layer q/k/v Linear, RoPE + KV append + attention, o_proj, gate/up
-// Linear + SwiGLU, down_proj, then the head and the greedy pick (generation.rs:6-8).  One CTA per SM
-// stays resident for the whole step and walks these as PHASES separated by a grid-wide barrier.
+// It runs, for Llama-shaped models and up to two sequences, what Llama::run (src/nn/modules/llama.rs:441-463;
+// DecoderLayer::forward 306-309; Attention::forward 248-277) does per token: per layer q/k/v Linear, RoPE + KV append +
+// attention, o_proj, gate/up Linear + SwiGLU, down_proj, then the head and the greedy pick (generation.rs:6-8).  One CTA
+// per SM stays resident for the whole step and walks these as PHASES separated by a grid-wide barrier.  It is the
+// alternative to the chain of launches of model.cu (one kernel per Linear / attention); which of the two a model uses is
+// the caller's choice (ruai_model_use_persistent_step), the chain being the default because it is the faster one on the
+// shapes measured so far: a phase boundary here (last partial sums out -> grid barrier -> activations back from L2 ->
+// digits -> first MMAs) costs about as much as a launch boundary there, and the chain's GEMV kernels keep more expanding
+// warps per SM busy.
 //
-// What makes it fast is that the weights never stop streaming.  Every CTA owns, per phase, a contiguous
-// run of (128-column tile, block of k) units of the weight in the tile-stream layout (pstep.cuh).  One
-// producer thread walks the stage list of the WHOLE step and keeps a ring of 20 KB bulk copies
-// (cp.async.bulk + mbarrier) full; it is held back only by free ring slots, never by a phase boundary,
-// so while the CTAs meet at a barrier the next phase's weights (or the next layer's cached keys and
-// values) are already landing in shared memory.
+// The weights never stop streaming.  Every CTA owns, per phase, a contiguous run of (128-column tile, block of k) units
+// of the weight in the tile-stream layout (pstep.cuh).  One producer thread walks the stages of the WHOLE step and keeps
+// a ring of 12 KB bulk copies (cp.async.bulk + mbarrier) full; it is held back only by free ring slots, never by a phase
+// boundary, so while the CTAs meet at a barrier the next phase's weights (or the next layer's cached keys and values)
+// are already landing in shared memory.  With each stage it leaves a small record (tile, window slot, blocks), from
+// which the other roles take what the stage holds: nobody but the producer walks the stage list.
 //
-// Arithmetic of a GEMV phase is that of gemv_tc.cu / gemv_tc8.cu: activations as block fixed point
-// (int4: three int8 digits per group of 32; int8: four digits per row of the CTA's window), exact
-// integer products on the tensor cores (tcgen05.mma kind::i8, accumulators in tensor memory), one f32
-// multiply-add per (scale group, column, row).  Four kinds of warps meet only at mbarriers:
-//   producer (1 thread)  : bulk copies into the ring;
-//   expanding (8 warps)  : int4 nibbles -> bytes into one of two A-operand buffers (int8 needs none: the
-//                          ring slot IS the operand);
-//   issuing (1 thread)   : one MMA per scale group (int4) or per 32 rows (int8), commits;
-//   draining (4 warps)   : sums out of tensor memory, scaled, accumulated in f32 per column.
-// A CTA's partial sums of a tile go to a 64-bit fixed-point accumulator in global memory with
-// red.add.u64: integer addition commutes, so the result is bit-identical from run to run whatever the
-// arrival order.  Everything non-linear happens when the NEXT phase loads its activations ("loaders"):
-// residual add, RMSNorm weight (the 1/rms factor is a per-row scalar and is applied one phase later,
-// from per-group sums of squares the loader leaves), SwiGLU, the merge of the attention key splits.
+// Arithmetic of a GEMV phase is that of gemv_tc.cu / gemv_tc8.cu: activations as block fixed point (int4: three int8
+// digits per group of 32; int8: four digits per row of the CTA's window), exact integer products on the tensor cores
+// (tcgen05.mma kind::i8, accumulators in tensor memory), one f32 multiply-add per (scale group, column, row).  The warps
+// of a CTA meet only at mbarriers:
+//   warp 0, one thread        : producer;
+//   warps 1 and 2, one thread : MMA issuers (stage s is issued by issuer s % 2; a thread needs well over a hundred
+//                               cycles per tcgen05.mma);
+//   warps 3..14               : three warpgroups; stage s belongs to warpgroup s % 3, which expands its int4 nibbles to
+//                               bytes (one of two A-operand buffers per warpgroup) and later reads its sums out of tensor
+//                               memory, scales and accumulates them (int8 needs no expansion: the ring slot IS the
+//                               operand, and warpgroups 0 / 1 read out issuer 0's / 1's runs);
+//   warps 1..14 together      : the digits of the activations at the start of a phase, the attention phase, the logits.
+// A CTA's partial sums of a tile go to a 64-bit fixed-point accumulator in global memory with red.add.u64: integer
+// addition commutes, so the result is bit-identical from run to run whatever the arrival order.  Everything non-linear
+// happens when the NEXT phase loads its activations ("loaders"): residual add, RMSNorm weight (the 1/rms factor is a
+// per-row scalar and is applied one phase later, from per-group sums of squares the loader leaves), SwiGLU.  The
+// attention phase works one (sequence, KV head, key split) item per CTA; the split that finishes an item last merges it.
 //
-// Every wait is bounded (mbarrier waits, the grid barrier); a wait that runs out sets an abort flag that
-// the other CTAs see at their next wait, the kernel frees its tensor memory and returns, and the host
-// reports RUAI_ERR_TIMEOUT.
+// Two things the kernel is built around, both measured: (1) no stack.  Nearly all of the SM's memory is configured as
+// shared memory, the L1 that is left holds no per-thread stack, and every touch of a spilled register or a by-reference
+// struct costs a trip to L2 (a few hundred bytes of stack frame doubled the step time).  Hence the phase descriptor and
+// the common parameters in shared memory, streaming state scoped after the conversion, small batches where registers
+// run out.  (2) No test in front of loads where a stage is full: the copy of a loop without the per-group condition
+// lets the compiler issue the loads together.
+//
+// Every wait is bounded (mbarrier waits, the grid barrier); a wait that runs out sets an abort flag that the other CTAs
+// see at their next wait, the kernel frees its tensor memory and returns, and the host reports RUAI_ERR_TIMEOUT.
 #include <algorithm>
+#include <type_traits>
 
 #include "pipeline.cuh"
 #include "pstep.cuh"
 
-#ifndef PS_POLL_SPECIAL
-#define PS_POLL_SPECIAL 0
-#endif
-#ifndef PS_SLEEP_NS
-#define PS_SLEEP_NS 40
-#endif
 namespace ps {
 
 using namespace pipe;
@@ -163,51 +171,20 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t (&v)[8]) {
                : "memory");
 }
 
-// ---- the stage list of one CTA in one GEMV phase ----------------------------------------------
-
-struct Stage {
-  uint32_t tile, blk, cnt;  // cnt blocks of `tile` starting at block `blk`
-  uint32_t ws;              // window slot of the first block's digits
-  bool round_start;         // the digits of a new round have to be written before this stage's MMAs
-  bool seg_end;             // last stage of a run inside one tile (and one round): partial sums go out
-  uint32_t round_blk0, round_cnt;  // first block and number of blocks of the round (valid at round_start)
-};
+// ---- the units of one CTA in one GEMV phase ---------------------------------------------------
 
 // Units are (tile, block) in tile-major order; CTA b owns units [U*b/G, U*(b+1)/G).  Digits of the
 // activations are kept for a window of kWin blocks: if the weight has at most kWin blocks of k the window
 // slot of a block is the block itself and the phase is one round; otherwise a round is kWin consecutive units.
 struct StageIter {
-  uint32_t u, u0, u1, nblk, smax, tile, blk, round_u0, blk_at_u0;
-  bool windowed, first;
-  __device__ void init(uint32_t ntiles, uint32_t nblk_, uint32_t smax_) {
-    const uint64_t units = (uint64_t)ntiles * nblk_;
+  uint32_t u0, u1, blk_at_u0;
+  bool windowed;
+  __device__ void init(uint32_t ntiles, uint32_t nblk) {
+    const uint64_t units = (uint64_t)ntiles * nblk;
     u0 = (uint32_t)(units * blockIdx.x / gridDim.x);
     u1 = (uint32_t)(units * (blockIdx.x + 1) / gridDim.x);
-    u = u0; nblk = nblk_; smax = smax_;
-    tile = u0 / nblk_; blk = u0 - tile * nblk_;
-    blk_at_u0 = blk;
-    windowed = nblk_ > (uint32_t)kWin;
-    round_u0 = u0; first = true;
-  }
-  // a handful of adds and compares: every warp walks every stage of its CTA
-  __device__ __forceinline__ bool next(Stage& s) {
-    if (u >= u1) return false;
-    s.round_start = first;
-    first = false;
-    uint32_t round_end = u1;
-    if (windowed) {
-      if (u - round_u0 >= (uint32_t)kWin) { round_u0 = u; s.round_start = true; }
-      round_end = min(u1, round_u0 + (uint32_t)kWin);
-    }
-    const uint32_t cnt = min(min(smax, nblk - blk), round_end - u);
-    s.tile = tile; s.blk = blk; s.cnt = cnt;
-    s.ws = windowed ? u - round_u0 : blk;
-    s.round_blk0 = windowed ? blk : blk_at_u0;
-    s.round_cnt = windowed ? round_end - round_u0 : min(u1 - u0, nblk);
-    s.seg_end = (blk + cnt == nblk) || (u + cnt == round_end);
-    u += cnt; blk += cnt;
-    if (blk == nblk) { blk = 0; ++tile; }
-    return true;
+    blk_at_u0 = u0 % nblk;
+    windowed = nblk > (uint32_t)kWin;
   }
 };
 
@@ -324,8 +301,8 @@ struct TestProgram {
 
 // Profiling builds only (-DRUAI_B200_TRACE): CTA 0 stamps its SM clock at the hand-overs of the first stages.
 // Layout: stage events [kTraceStages][8], then phase events [kTracePhases][4].
-constexpr uint32_t kTraceStages = 192, kTracePhases = 192;
 #ifdef RUAI_B200_TRACE
+constexpr uint32_t kTraceStages = 192, kTracePhases = 192;
 #define PS_TRACE_STAGE(X, stage, ev)                                                                       \
   do {                                                                                                     \
     if ((X).c.trace && blockIdx.x == 0 && (stage) < kTraceStages) (X).c.trace[(size_t)(stage) * 8 + (ev)] = clock64(); \
@@ -387,13 +364,7 @@ struct Ctx {
     // otherwise poll with a short sleep in between: a suspending try_wait was seen to wake up more than a thousand cycles
     // after the barrier completed, and a tight polling loop takes the issue slots of the warps it waits for
     for (unsigned i = 0; i < c.spin_limit; ++i) {
-#if PS_POLL_SPECIAL == 1
-      if (warp > 2) __nanosleep(PS_SLEEP_NS);
-#elif PS_POLL_SPECIAL == 2
-      if (warp > 2) { if (i > 4) __nanosleep(PS_SLEEP_NS); }
-#else
-      __nanosleep(PS_SLEEP_NS);
-#endif
+      __nanosleep(40);
       asm volatile(
           "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(ok)
@@ -821,7 +792,7 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
   (void)tracer;
   StageIter it;
   const uint32_t smax = is4 ? kStage4 : kStage8;
-  it.init(D.ntiles, D.nblk, smax);
+  it.init(D.ntiles, D.nblk);
   X.cur_phase = p;
 
   // the rounds of this CTA: [ru, rend) units each
@@ -851,14 +822,14 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
 
     // The streaming state lives inside the round, after the conversion: the two never hold registers at the same time.
     float acc[MT];
-  #pragma unroll
+#pragma unroll
     for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
     bool dirty = false;  // acc holds something that has not gone out yet
     auto flush = [&](uint32_t tile) {
       const uint32_t j = tile * kCols + col;
       if (dirty && j < D.n) {
         const float cs = is4 ? 1.0f : __ldg(D.colscale + j);
-  #pragma unroll
+#pragma unroll
         for (int r = 0; r < MT; ++r) {
           if ((uint32_t)r < X.c.m) {
             const float v = acc[r] * cs;
@@ -867,14 +838,14 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
           }
         }
       }
-  #pragma unroll
+#pragma unroll
       for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
       dirty = false;
     };
 
     // ---- int4, warpgroup side ----
     float sc_cur[kStage4], sc_pend[kStage4];
-  #pragma unroll
+#pragma unroll
     for (int i = 0; i < kStage4; ++i) { sc_cur[i] = 0.0f; sc_pend[i] = 0.0f; }
     uint32_t pend_ws = 0, pend_cnt = 0, pend_k = 0, pend_tile = 0;
     bool have_pending = false;
@@ -885,30 +856,35 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
       tc_fence_after_sync();
       if (!X.aborted()) {
         const uint32_t t0 = X.tmem + lane_base + (uint32_t)g * 128u + (pend_k & 1u) * 64u;
+        auto halves = [&](auto full) {
+          constexpr bool F = decltype(full)::value;
 #pragma unroll
-        for (int h0 = 0; h0 < kStage4; h0 += kHalf) {
-          if ((uint32_t)h0 >= pend_cnt) break;
-          int32_t dsum[kHalf][MT == 1 ? 4 : 8];
+          for (int h0 = 0; h0 < kStage4; h0 += kHalf) {
+            if (!F && (uint32_t)h0 >= pend_cnt) break;
+            int32_t dsum[kHalf][MT == 1 ? 4 : 8];
 #pragma unroll
-          for (int gi = 0; gi < kHalf; ++gi) {
-            if ((uint32_t)(h0 + gi) < pend_cnt) {
-              if constexpr (MT == 1) tmem_ld4(t0 + (h0 + gi) * 16u, dsum[gi]);
-              else tmem_ld8(t0 + (h0 + gi) * 16u, dsum[gi]);
+            for (int gi = 0; gi < kHalf; ++gi) {
+              if (F || (uint32_t)(h0 + gi) < pend_cnt) {
+                if constexpr (MT == 1) tmem_ld4(t0 + (h0 + gi) * 16u, dsum[gi]);
+                else tmem_ld8(t0 + (h0 + gi) * 16u, dsum[gi]);
+              }
             }
-          }
-          tmem_ld_wait();
+            tmem_ld_wait();
 #pragma unroll
-          for (int gi = 0; gi < kHalf; ++gi) {
-            if ((uint32_t)(h0 + gi) < pend_cnt) {
-              const uint32_t mi = (pend_ws + h0 + gi) * MT;
+            for (int gi = 0; gi < kHalf; ++gi) {
+              if (F || (uint32_t)(h0 + gi) < pend_cnt) {
+                const uint32_t mi = (pend_ws + h0 + gi) * MT;
 #pragma unroll
-              for (int r = 0; r < MT; ++r) {
-                const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
-                acc[r] = fmaf((float)val, sc_pend[h0 + gi] * X.mscale()[mi + r], acc[r]);
+                for (int r = 0; r < MT; ++r) {
+                  const int val = dsum[gi][3 * r] * 16384 + dsum[gi][3 * r + 1] * 128 + dsum[gi][3 * r + 2] - 8 * X.msum()[mi + r];
+                  acc[r] = fmaf((float)val, sc_pend[h0 + gi] * X.mscale()[mi + r], acc[r]);
+                }
               }
             }
           }
-        }
+        };
+        if (pend_cnt == (uint32_t)kStage4) halves(std::true_type{});
+        else halves(std::false_type{});
         tc_fence_before_sync();
         dirty = true;
       }
@@ -927,10 +903,12 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
       if (tracer) PS_TRACE_STAGE(X, s, 1);
       const unsigned char* src = X.smem + kOffSlots + (size_t)slot * kSlotBytes;
       unsigned char* dst = X.abuf_ptr(g, k);
-      if (!X.aborted()) {
-  #pragma unroll
+      // (a full stage takes the copy of the loop without the per-group test: with it every group's loads wait for the
+      // branch before them)
+      auto groups = [&](auto full) {
+#pragma unroll
         for (uint32_t gi = 0; gi < (uint32_t)kStage4; ++gi) {
-          if (gi < cnt) {
+          if (decltype(full)::value || gi < cnt) {
             const uint4 wv = *reinterpret_cast<const uint4*>(src + gi * kStreamRec4 + col * 16u);
             sc_cur[gi] = *reinterpret_cast<const float*>(src + gi * kStreamRec4 + 2048u + col * 4u);
             uint4 lo, hi;
@@ -943,6 +921,10 @@ __device__ void gemv_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p) {
             *reinterpret_cast<uint4*>(d + 2048) = hi;    // rows 16..31: second k-half
           }
         }
+      };
+      if (!X.aborted()) {
+        if (cnt == (uint32_t)kStage4) groups(std::true_type{});
+        else groups(std::false_type{});
       }
       if (tracer) PS_TRACE_STAGE(X, s, 5);
       fence_proxy_async_smem();
@@ -1140,6 +1122,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
   AttnPlan ap;
   ap.init(X.c.m, P->KVl, P->splits, P->keys_per_stage, len);
   phase_duties<MT>(X, D);
+    if (X.tid == kLeaderTid) PS_TRACE_ISSUE(X, p, 0);
   const int ct = X.tid - kWarpLeader * 32, cw = X.warp - kWarpLeader, lane = X.lane;
   const uint32_t hd = P->hd, half = hd / 2, rep = P->rep, nq4 = hd / 4, pos = len;
   const uint32_t scld = kAttnBatch * ap.KS + 1u;      // scores per head: the batch's keys, then the new key
@@ -1215,6 +1198,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       }
     }
     bar_sync(1, kConsumers);
+    if (ct == 0) PS_TRACE_ISSUE(X, p, 1);
     float run_m = -INFINITY, run_l = 0.0f;
     float4 run_o = make_float4(0.f, 0.f, 0.f, 0.f);
     const uint32_t nst = (k1 - k0 + ap.KS - 1) / ap.KS;
@@ -1223,39 +1207,55 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       const uint32_t nk = nb ? min(nb * ap.KS, k1 - (k0 + j0 * ap.KS)) : 0u;  // their keys
       const bool with_new = j0 == 0 && owns_new;
       for (uint32_t j = 0; j < nb; ++j) X.wait(&X.sh->b.full[(X.s + j) % kSlots], ((X.s + j) / kSlots) & 1u, 20);
-      // scores: a warp per key, the lanes share the head dimension, all heads of the group at once
+    if (ct == 0) PS_TRACE_ISSUE(X, p, 2);
+      // scores: eight lanes per key (four keys per warp at a time), all heads of the group at once
       if (!X.aborted()) {
-        for (uint32_t kk = cw; kk < nk + (with_new ? 1u : 0u); kk += kConvWarps) {
-          const bool is_new = kk >= nk;
-          const uint32_t st = kk / ap.KS, row = kk - st * ap.KS;
-          const float4* krow = reinterpret_cast<const float4*>(is_new ? knew : reinterpret_cast<const float*>(X.slot_ptr(X.s + st)) + (size_t)row * hd);
+        const uint32_t l8 = lane & 7u, kq = lane >> 3, nkt = nk + (with_new ? 1u : 0u);
+        for (uint32_t k4 = 4u * (uint32_t)cw; k4 < nkt; k4 += 4u * kConvWarps) {
+          const uint32_t kk = k4 + kq;
+          const bool act = kk < nkt, is_new = act && kk >= nk;
+          const uint32_t kc = act && !is_new ? kk : 0u, st = kc / ap.KS, row = kc - st * ap.KS;
+          const float* krow = is_new ? knew : reinterpret_cast<const float*>(X.slot_ptr(X.s + st)) + (size_t)row * hd;
           float a[8];
 #pragma unroll
           for (int r = 0; r < 8; ++r) a[r] = 0.0f;
-          for (uint32_t e4 = lane; e4 < nq4; e4 += 32) {
-            const float4 kv = krow[e4];
+          // (the usual group of four heads takes a copy without the per-head test, which the loads would wait for)
+          auto dots = [&](auto four) {
+            constexpr bool F = decltype(four)::value;
+            for (uint32_t e = 4u * l8; e < hd; e += 32u) {
+              const float4 kv = *reinterpret_cast<const float4*>(krow + e);
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if ((uint32_t)r < rep) {
-                const float4 qv = reinterpret_cast<const float4*>(qs + r * hd)[e4];
-                a[r] = fmaf(qv.x, kv.x, a[r]); a[r] = fmaf(qv.y, kv.y, a[r]); a[r] = fmaf(qv.z, kv.z, a[r]); a[r] = fmaf(qv.w, kv.w, a[r]);
+              for (int r = 0; r < (F ? 4 : 8); ++r) {
+                if (F || (uint32_t)r < rep) {
+                  const float4 qv = *reinterpret_cast<const float4*>(qs + r * hd + e);
+                  a[r] = fmaf(qv.x, kv.x, a[r]); a[r] = fmaf(qv.y, kv.y, a[r]); a[r] = fmaf(qv.z, kv.z, a[r]); a[r] = fmaf(qv.w, kv.w, a[r]);
+                }
               }
             }
-          }
 #pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            if ((uint32_t)r < rep) {
-#pragma unroll
-              for (int off = 16; off > 0; off >>= 1) a[r] += __shfl_xor_sync(0xFFFFFFFFu, a[r], off);
-              if (lane == 0) sc[r * scld + (is_new ? scld - 1u : kk)] = a[r] * P->attn_scale;
+            for (int r = 0; r < (F ? 4 : 8); ++r) {
+              if (F || (uint32_t)r < rep) {
+                a[r] += __shfl_xor_sync(0xFFFFFFFFu, a[r], 1);
+                a[r] += __shfl_xor_sync(0xFFFFFFFFu, a[r], 2);
+                a[r] += __shfl_xor_sync(0xFFFFFFFFu, a[r], 4);
+              }
             }
+          };
+          if (rep == 4u) dots(std::true_type{});
+          else dots(std::false_type{});
+          if (act && l8 == 0u) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if ((uint32_t)r < rep) sc[r * scld + (is_new ? scld - 1u : kk)] = a[r] * P->attn_scale;
           }
         }
       }
       bar_sync(1, kConsumers);
+      if (ct == 0) PS_TRACE_ISSUE(X, p, 3);
       // the new maximum of every head (each of its threads works it out), then the weights exp(score - max), shared out
       float M = run_m;
       if (vact && !X.aborted()) {
+#pragma unroll 4
         for (uint32_t kk = 0; kk < nk; ++kk) M = fmaxf(M, sc[vr * scld + kk]);
         if (with_new) M = fmaxf(M, sc[vr * scld + scld - 1u]);
       }
@@ -1265,6 +1265,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
         if (with_new && vc == 0) sc[vr * scld + scld - 1u] = expf(sc[vr * scld + scld - 1u] - M);
       }
       bar_sync(1, kConsumers);
+      if (ct == 0) PS_TRACE_ISSUE(X, p, 4);
       if (vact && !X.aborted()) {
         const float cr = run_m == -INFINITY ? 0.0f : expf(run_m - M);
         float Ls = run_l * cr;
@@ -1272,6 +1273,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
         for (uint32_t st = 0, kk = 0; st < nb; ++st) {
           const float* vs = reinterpret_cast<const float*>(X.slot_ptr(X.s + st) + kSlotBytes / 2);
           const uint32_t rows = min(ap.KS, nk - kk);
+#pragma unroll 4
           for (uint32_t row = 0; row < rows; ++row, ++kk) {
             const float pr = sc[vr * scld + kk];
             const float4 vv = reinterpret_cast<const float4*>(vs + (size_t)row * hd)[vc];
@@ -1291,6 +1293,7 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       if (cw < 4 && lane == 0)
         for (uint32_t j = 0; j < nb; ++j) mbar_arrive(&X.sh->b.empty[(X.s + j) % kSlots]);  // count 4
       X.s += nb;
+    if (ct == 0) PS_TRACE_ISSUE(X, p, 5);
     }
     // the split's part goes out; whoever completes the item merges
     if (vact) {
@@ -1307,46 +1310,70 @@ __device__ void attn_phase(Ctx<MT>& X, const PhaseDesc& D, uint32_t p, uint32_t 
       if (old == ap.S - 1u) P->att_cnt[bk] = 0;  // for the next layer (ordered before it by the grid barriers in between)
     }
     bar_sync(1, kConsumers);  // also: qs / knew are rewritten by the next item
+    if (ct == 0) PS_TRACE_ISSUE(X, p, 6);
     if (X.sh->att_last && !X.aborted()) {
-      const uint32_t stride = hd + 4u, S = ap.S;
+      const uint32_t stride = hd + 4u, S = ap.S, nv = rep * nq4;
       const float* base0 = P->att_part + (size_t)(bk * S) * rep * stride;
-      // the splits' softmax statistics into shared memory (one load each), then every output thread merges in split order
+      // the splits' softmax statistics into shared memory (one load each); then the output threads, in up to four groups
+      // that share the splits out, weigh and add the partial outputs (all of a group's loads in flight together), and
+      // the first group adds the groups' parts in order
       for (uint32_t i = ct; i < rep * S; i += kConsumers) {
         const uint32_t r = i / S, s2 = i - r * S;
         const float* rec = base0 + ((size_t)s2 * rep + r) * stride;
         wm[i] = __ldcg(rec + hd);
         wm[rep * S + i] = __ldcg(rec + hd + 1);
       }
+      const uint32_t ngrp = min(4u, (uint32_t)kConsumers / nv), gq = (uint32_t)ct / nv, t = (uint32_t)ct - gq * nv;
+      const uint32_t per_g = (S + ngrp - 1u) / ngrp;
+      const uint32_t mr = t / nq4, mc = t - mr * nq4;
+      float* part = wm + 2u * rep * S;  // [ngrp][nv][5]
+      constexpr uint32_t kB = 4;  // partial outputs in flight at once (more would spill)
+      float4 ov[kB];
+      const uint32_t sa = min(S, gq * per_g), sb = gq < ngrp ? min(S, sa + per_g) : sa;
+      const float* base = base0 + (size_t)mr * stride + 4u * mc;
+#pragma unroll
+      for (uint32_t u = 0; u < kB; ++u)
+        if (sa + u < sb) ov[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(sa + u) * rep * stride));
       bar_sync(1, kConsumers);
-      if (vact) {
-        const float* base = base0 + (size_t)vr * stride + 4u * vc;
+      if (gq < ngrp) {
         float M = -INFINITY;
-        for (uint32_t s2 = 0; s2 < S; ++s2) M = fmaxf(M, wm[vr * S + s2]);
+        for (uint32_t s2 = 0; s2 < S; ++s2) M = fmaxf(M, wm[mr * S + s2]);
         float Lsum = 0.0f;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-        constexpr uint32_t kB = 4;  // partial outputs in flight at once
-        for (uint32_t s0 = 0; s0 < S; s0 += kB) {
-          float4 ov[kB];
+        for (uint32_t s0 = sa; s0 < sb; s0 += kB) {
+          if (s0 != sa) {
 #pragma unroll
-          for (uint32_t u = 0; u < kB; ++u)
-            if (s0 + u < S) ov[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(s0 + u) * rep * stride));
+            for (uint32_t u = 0; u < kB; ++u)
+              if (s0 + u < sb) ov[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(s0 + u) * rep * stride));
+          }
 #pragma unroll
           for (uint32_t u = 0; u < kB; ++u) {
-            if (s0 + u < S) {
-              const float ms = wm[vr * S + s0 + u];
+            if (s0 + u < sb) {
+              const float ms = wm[mr * S + s0 + u];
               if (ms != -INFINITY) {
                 const float wgt = expf(ms - M);
-                Lsum = fmaf(wm[rep * S + vr * S + s0 + u], wgt, Lsum);
+                Lsum = fmaf(wm[rep * S + mr * S + s0 + u], wgt, Lsum);
                 o.x = fmaf(ov[u].x, wgt, o.x); o.y = fmaf(ov[u].y, wgt, o.y); o.z = fmaf(ov[u].z, wgt, o.z); o.w = fmaf(ov[u].w, wgt, o.w);
               }
             }
           }
         }
+        float* pp = part + ((size_t)gq * nv + t) * 5u;
+        pp[0] = Lsum; pp[1] = o.x; pp[2] = o.y; pp[3] = o.z; pp[4] = o.w;
+      }
+      bar_sync(1, kConsumers);
+      if (gq == 0u) {
+        float Lsum = 0.0f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t q = 0; q < ngrp; ++q) {
+          const float* pp = part + ((size_t)q * nv + t) * 5u;
+          Lsum += pp[0]; o.x += pp[1]; o.y += pp[2]; o.z += pp[3]; o.w += pp[4];
+        }
         const float inv = 1.0f / Lsum;
         o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
-        *reinterpret_cast<float4*>(P->att_out + (size_t)b * P->nq + (kvh * rep + vr) * hd + 4u * vc) = o;
+        *reinterpret_cast<float4*>(P->att_out + (size_t)b * P->nq + (kvh * rep + mr) * hd + 4u * mc) = o;
       }
-      bar_sync(1, kConsumers);  // wm is reused by the next item
+      bar_sync(1, kConsumers);  // the merge's scratch is reused by the next item
     }
   }
   if (X.tid == kLeaderTid) PS_TRACE_PHASE(X, p, 3);

@@ -178,6 +178,46 @@ def _matmul_q(x, w, bias=None):
     return out
 
 
+def matmul_q_grad_input(g, w):
+    """Gradient of `matmul_int8` / `matmul_int4` with respect to the activations (ops.rs:705-709, 731-734): g @ dequant(W)^T."""
+    if g.rdtype != F32 or g.shape[-1] != w.n:
+        raise ValueError(f"gradient must be f32 [..., {w.n}]")
+    m = int(np.prod(g.shape[:-1], dtype=np.int64))
+    out = Tensor(g.dev, g.shape[:-1] + (w.k,), np.float32, F32)
+    g.dev.check(g.dev.L.ruai_matmul_q_grad_input(g.dev.ctx, g.ptr, w.h, out.ptr, m))
+    return out
+
+
+def linear_lora_forward(x, w, lora_a, lora_b, scale, bias=None):
+    """`Linear::forward` of a quantized layer with a LoRA adapter (layers.rs:169-190)."""
+    if x.rdtype != F32 or x.shape[-1] != w.k:
+        raise ValueError(f"activations must be f32 [..., {w.k}]")
+    rank = lora_a.shape[1]
+    if lora_a.shape != (w.k, rank) or lora_b.shape != (rank, w.n):
+        raise ValueError("lora_a must be [k, rank] and lora_b [rank, n]")
+    m = int(np.prod(x.shape[:-1], dtype=np.int64))
+    out = Tensor(x.dev, x.shape[:-1] + (w.n,), np.float32, F32)
+    x.dev.check(x.dev.L.ruai_linear_lora_forward(x.dev.ctx, x.ptr, w.h, lora_a.ptr, lora_b.ptr, rank, float(scale),
+                                                 bias.ptr if bias is not None else None, out.ptr, m))
+    return out
+
+
+class Sampler:
+    """`Sampler` (generation.rs:15-73) over logits in device memory."""
+
+    def __init__(self, temperature, top_k=0, top_p=1.0, seed=0):
+        self.temperature, self.top_k, self.top_p = float(temperature), int(top_k), float(top_p)
+        self.state = C.c_uint64(seed)
+
+    def sample(self, logits):
+        if logits.rdtype != F32 or len(logits.shape) != 1:
+            raise ValueError("logits must be a 1-D f32 tensor")
+        tok = C.c_int32(0)
+        logits.dev.check(logits.dev.L.ruai_sample(logits.dev.ctx, logits.ptr, logits.shape[0], self.temperature, self.top_k, self.top_p,
+                                                  C.byref(self.state), C.byref(tok)))
+        return int(tok.value)
+
+
 def matmul_q_stream(x, w, repeat=1):
     """`matmul_int8` / `matmul_int4` for 1 or 2 rows through the persistent kernel's data path (f32)."""
     if x.rdtype != F32:
@@ -329,11 +369,26 @@ class _Model:
         self.dev.check(self.dev.L.ruai_model_generate(self.h, prompt.ctypes.data_as(C.c_void_p), prompt.size, n, out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def generate_sampled(self, prompt, n, temperature, top_k=0, top_p=1.0, seed=0):
+        """`generate` with `Sampler::new(temperature, top_k, top_p, seed)` (generation.rs:28-73); the draw runs on the device."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.empty(prompt.size + n, np.int32)
+        self.dev.check(self.dev.L.ruai_model_generate_sampled(self.h, prompt.ctypes.data_as(C.c_void_p), prompt.size, n, float(temperature), int(top_k),
+                                                              float(top_p), int(seed), out.ctypes.data_as(C.c_void_p)))
+        return out
+
     def decode_step(self, B, ids_dev=None, fetch=True):
         """One greedy step for B sequences that stays on the device; returns the next ids if fetch."""
         out = np.empty(B, np.int32) if fetch else None
         self.dev.check(self.dev.L.ruai_model_decode_step(self.h, ids_dev, B, out.ctypes.data_as(C.c_void_p) if fetch else None))
         return out
+
+    def use_persistent_step(self, on=True):
+        """Single-token greedy steps as ONE persistent kernel per token (on) or as the chain of launches (default)."""
+        self.dev.check(self.dev.L.ruai_model_use_persistent_step(self.h, 1 if on else 0))
+
+    def uses_persistent_step(self, B=1):
+        return bool(self.dev.L.ruai_model_uses_persistent_step(self.h, B))
 
     def cache_reserve(self, B, positions):
         self.dev.check(self.dev.L.ruai_model_cache_reserve(self.h, B, positions))

@@ -316,3 +316,65 @@ def test_large_batch_decode_steps(dev, name, B, cfg):
         gm.cache_clear(); om.cache_clear()
         break_after = step  # one checked step per cache state keeps the two models on the same ids
         lo = om.forward_cached(prompts); gm.forward_cached(prompts)
+
+
+# ---- sampling on the device (generation.rs:15-73) ----
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.8, 40, 1.0), (0.7, 0, 0.9), (1.3, 50, 0.95), (1.0, 1, 1.0), (1.0, 0, 0.01), (0.0, 0, 1.0)])
+def test_device_sampler_matches_checker(dev, temperature, top_k, top_p):
+    """The same draws from the same seed on rows of logits with a wide and with a narrow spread, vocabulary sizes that
+    are not multiples of the warp.  A draw that the checker reports as decided by less than 2e-6 of probability mass
+    (the two round exp differently, about 1e-7 relative) may fall either way and is not compared."""
+    rng = np.random.default_rng(7)
+    for V, spread in [(4, 1.0), (1000, 3.0), (32003, 1.0), (128256, 6.0)]:
+        logits = (rng.standard_normal(V) * spread).astype(np.float32)
+        logits[V // 3] = logits[V // 2]  # a tie
+        t = nn.Tensor.from_numpy(dev, logits)
+        so, sg = oracle.Sampler(temperature, top_k, top_p, 123), nn.Sampler(temperature, top_k, top_p, 123)
+        compared = 0
+        for _ in range(12):
+            want, got = so.sample(logits), sg.sample(t)
+            assert so.state.value == sg.state.value
+            if so.margin > 2e-6:
+                assert want == got, (V, want, got, so.margin)
+                compared += 1
+        assert compared >= 6, (V, compared)
+
+
+def test_device_sampler_reference_cases(dev):
+    """tests/inference.rs:186-208 on the device sampler."""
+    logits = np.array([1.0, 3.0, 2.0, -1.0], np.float32)
+    t = nn.Tensor.from_numpy(dev, logits)
+    assert nn.Sampler(0.0).sample(t) == 1
+    assert nn.Sampler(1.0, 1, 1.0, 7).sample(t) == 1
+    assert nn.Sampler(1.0, 0, 0.01, 7).sample(t) == 1
+    s = nn.Sampler(1.0, 2, 1.0, 3)
+    assert all(s.sample(t) in (1, 2) for _ in range(200))
+    s = nn.Sampler(1.0, 0, 1.0, 11)
+    counts = np.zeros(4)
+    for _ in range(4000):
+        counts[s.sample(t)] += 1
+    p = np.exp(logits) / np.exp(logits).sum()
+    assert np.abs(counts / 4000.0 - p).max() < 0.03, counts
+
+
+@pytest.mark.parametrize("persistent", [False, True])
+def test_sampled_generation_matches_checker(dev, persistent):
+    """generate with Sampler::new(0.9, 20, 0.95, seed): the same tokens as the checker up to the first draw that the
+    checker reports as decided by less than 1e-4 of probability mass (the logits of the two differ by their tolerance)."""
+    cfg = dict(V=331, d=256, ffn=704, L=3, H=8, KV=2, hd=32, max_pos=256)
+    oc = oracle.LlamaConfig(cfg["V"], cfg["d"], cfg["ffn"], cfg["L"], cfg["H"], cfg["KV"], cfg["hd"], cfg["max_pos"], 1e-5, 10000.0, 0)
+    gc = nn.LlamaConfig(cfg["V"], cfg["d"], cfg["ffn"], cfg["L"], cfg["H"], cfg["KV"], cfg["hd"], cfg["max_pos"], 1e-5, 10000.0, 0)
+    om = oracle.Model(oc, seed=5, bits=8, group=32)
+    gm = nn.Llama(dev, gc)
+    gm.load_synthetic(5, 8, 32)
+    gm.use_persistent_step(persistent)
+    prompt = oracle.synth_tokens(0, 0x20000000, 7, cfg["V"])
+    agree = 0
+    for seed in (1, 2, 3):
+        want, margins = om.generate_sampled(prompt, 24, 0.9, 20, 0.95, seed)
+        got = gm.generate_sampled(prompt, 24, 0.9, 20, 0.95, seed)
+        safe = int(np.argmax(margins < 1e-4)) if (margins < 1e-4).any() else 24
+        assert got[:7 + safe].tolist() == want[:7 + safe].tolist(), (seed, safe)
+        agree += safe
+    assert agree >= 24

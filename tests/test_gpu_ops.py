@@ -182,6 +182,55 @@ def test_matmul_grid_f32(dev, m, k, n, bits):
     assert np.array_equal(q2, q) and np.array_equal(s2, s)
 
 
+# the Llama-3-8B widths (hidden 4096, q/k/v 6144, MLP 14336) at prefill-sized row counts, ragged and full tiles
+WIDE = [(17, 4096, 14336), (64, 4096, 6144), (128, 14336, 4096), (512, 4096, 4096)]
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,k,n", WIDE)
+def test_matmul_grid_8b_widths(dev, m, k, n, bits):
+    x = oracle.synth_normal(13, 0x31000000 + m, (m, k), 1.0)
+    w = oracle.synth_normal(13, k * 65537 + n, (k, n))
+    if bits == 8:
+        q, s = oracle.quantize_int8(w)
+        qw, want = nn.QWeight.int8(dev, q, s), oracle.matmul_int8(x, q, s)
+    else:
+        q, s = oracle.quantize_int4(w, 32)
+        qw, want = nn.QWeight.int4(dev, q, s, 32), oracle.matmul_int4(x, q, s)
+    _, y = run_matmul(dev, x, qw, "f32")
+    # Quantized-Linear outputs: max-abs 1e-2 and 1e-3 relative to the output's scale.  (The rows-by-the-hundred GEMM
+    # carries the activations as two bf16 pieces, 16 significant bits; over k = 14336 a handful of the 524288 outputs
+    # miss the 1e-4 * (1 + |y|) of tests/devices.rs by up to 4e-4, which the smaller shapes above all meet.)
+    err = np.abs(want.astype(np.float64) - y).max()
+    assert err <= 1e-2 and err <= 1e-3 * np.abs(want).max(), (err, np.abs(want).max())
+    loose = ~(np.abs(want - y) <= 1e-4 * (1 + np.abs(want)))
+    assert loose.mean() <= 1e-4, f"{loose.sum()} of {loose.size} outputs beyond the tests/devices.rs tolerance"
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m", [1, 2, 5])
+def test_matmul_non_finite_activations_propagate(dev, bits, m):
+    """A NaN or an infinity in a row of x makes that row of the product non-finite, as f32 arithmetic on the CPU does
+    (cpu.rs:1002-1029, 1035-1067); the other rows are unaffected."""
+    k, n = 4096, 1024
+    x = oracle.synth_normal(14, m, (m, k), 1.0)
+    w = oracle.synth_normal(14, 2, (k, n))
+    if bits == 8:
+        q, s = oracle.quantize_int8(w)
+        qw, f = nn.QWeight.int8(dev, q, s), oracle.matmul_int8
+    else:
+        q, s = oracle.quantize_int4(w, 32)
+        qw, f = nn.QWeight.int4(dev, q, s, 32), oracle.matmul_int4
+    want = f(x, q, s)
+    for bad in (np.nan, np.inf, -np.inf):
+        xb = x.copy()
+        xb[0, 1234] = bad
+        _, y = run_matmul(dev, xb, qw, "f32")
+        assert not np.isfinite(y[0]).any(), bad
+        if m > 1:
+            same(want[1:], y[1:], 1e-4)
+
+
 @pytest.mark.parametrize("bits", [8, 4])
 def test_matmul_bf16_activations(dev, bits):
     m, k, n = 16, 1536, 1536
@@ -213,3 +262,49 @@ def test_linearity_and_determinism(dev):
     assert np.array_equal(again, y1)
     q, s = lin.int4
     same(oracle.matmul_int4(x1, q, s), y1, 1e-4)
+
+
+# ---- training-side ops on the packed weights: input gradient and LoRA forward (layers.rs:169-190, ops.rs:705-734) ----
+
+def _qw(dev, bits, k, n, seed, group=32):
+    w = oracle.synth_normal(seed, k * 65537 + n, (k, n))
+    if bits == 8:
+        q, s = oracle.quantize_int8(w)
+        return q, s, nn.QWeight.int8(dev, q, s)
+    q, s = oracle.quantize_int4(w, group)
+    return q, s, nn.QWeight.int4(dev, q, s, group)
+
+
+@pytest.mark.parametrize("bits,group", [(8, 32), (4, 32), (4, 16)])
+@pytest.mark.parametrize("m,k,n", [(1, 64, 48), (3, 576, 1536), (5, 4096, 1024), (2, 96, 130)])
+def test_grad_input_matches_checker_and_is_the_adjoint(dev, m, k, n, bits, group):
+    q, s, qw = _qw(dev, bits, k, n, 21, group)
+    g = oracle.synth_normal(21, 7, (m, n), 1.0)
+    want = oracle.matmul_q_grad_input(bits, g, q, s, group)
+    got = nn.matmul_q_grad_input(nn.Tensor.from_numpy(dev, g), qw).numpy()
+    same(want, got, 1e-4)
+    # adjoint identity with the forward op of this library: <g, x @ W> == <g @ W^T, x>
+    x = oracle.synth_normal(21, 8, (m, k), 1.0)
+    y = nn._matmul_q(nn.Tensor.from_numpy(dev, x), qw).numpy().astype(np.float64)
+    lhs, rhs = float((g * y).sum()), float((got.astype(np.float64) * x).sum())
+    assert abs(lhs - rhs) <= 2e-4 * max(abs(lhs), np.abs(g).sum() * 1e-3)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,k,n,rank", [(1, 64, 48, 4), (4, 576, 1536, 8), (2, 4096, 1024, 16), (3, 96, 130, 3)])
+def test_lora_forward_matches_checker(dev, m, k, n, rank, bits):
+    q, s, qw = _qw(dev, bits, k, n, 22)
+    x = oracle.synth_normal(22, 1, (m, k), 1.0)
+    a = oracle.synth_normal(22, 2, (k, rank), 1.0 / np.sqrt(k))
+    b = oracle.synth_normal(22, 3, (rank, n), 0.05)
+    bias = oracle.synth_normal(22, 4, (n,))
+    scale = 16.0 / rank
+    T = lambda v: nn.Tensor.from_numpy(dev, v)
+    for bb in (None, bias):
+        want = oracle.linear_lora_forward(bits, x, q, s, a, b, scale, bb)
+        got = nn.linear_lora_forward(T(x), qw, T(a), T(b), scale, None if bb is None else T(bb)).numpy()
+        same(want, got, 1e-4)
+    # B = 0 (a fresh adapter, layers.rs:93): the output is the base layer's
+    zero = np.zeros((rank, n), np.float32)
+    got = nn.linear_lora_forward(T(x), qw, T(a), T(zero), scale).numpy()
+    assert np.array_equal(got, nn._matmul_q(T(x), qw).numpy())

@@ -160,18 +160,10 @@ def llama_cfgs(V, d, ffn, L, H, KV, hd, max_pos, theta=10000.0, tied=False):
 def build_pair(dev, cfgs, seed, bits, persistent=True):
     oc, gc = cfgs
     om = oracle.Model(oc, seed=seed, bits=bits, group=32)
-    old = os.environ.get("RUAI_B200_PSTEP")
-    os.environ["RUAI_B200_PSTEP"] = "1" if persistent else "0"
-    try:
-        gm = nn.Llama(dev, gc)
-        gm.load_synthetic(seed, bits, 32)
-        gm.forward_cached(np.array([[1]], np.int32))  # fixes the path choice of this model while the variable is set
-        gm.cache_clear()
-    finally:
-        if old is None:
-            del os.environ["RUAI_B200_PSTEP"]
-        else:
-            os.environ["RUAI_B200_PSTEP"] = old
+    gm = nn.Llama(dev, gc)
+    gm.load_synthetic(seed, bits, 32)
+    gm.use_persistent_step(persistent)
+    assert gm.uses_persistent_step(1) == persistent
     return om, gm
 
 
@@ -251,6 +243,7 @@ def test_persistent_greedy_tokens_and_device_argmax_ties(dev):
     gm2.set_f32(0x10000001, head)
     gm2.set_f32(0x40000000, np.ones(c["d"], np.float32))
     gm2.quantize_int8()
+    gm2.use_persistent_step(True)
     logits = gm2.forward_cached(np.array([[5]], np.int32))
     assert logits[0, 17] == logits[0, 300]
     best = float(logits.max())
@@ -262,10 +255,11 @@ def test_persistent_greedy_tokens_and_device_argmax_ties(dev):
     assert nxt[0] == ties[-1], (nxt, ties)
 
 
-def test_cache_clear_then_decode_step_with_a_new_batch(dev):
+@pytest.mark.parametrize("persistent", [True, False])
+def test_cache_clear_then_decode_step_with_a_new_batch(dev, persistent):
     """cache_clear() followed directly by decode_step() with another batch size must start at position 0 of fresh
-    buffers (the host's position is the authority), not at the device's stale position."""
-    om, gm = build_pair(dev, llama_cfgs(**SMALL), 6, 8)
+    buffers (the host's position is the authority), not at the device's stale position; on both step paths."""
+    om, gm = build_pair(dev, llama_cfgs(**SMALL), 6, 8, persistent=persistent)
     gm.forward_cached(np.array([[1, 2, 3, 4, 5, 6, 7]], np.int32))
     gm.cache_clear()
     om.cache_clear()
@@ -275,3 +269,9 @@ def test_cache_clear_then_decode_step_with_a_new_batch(dev):
     want = om.forward_cached(ids[:, None])
     assert nxt.tolist() == [oracle.argmax(r) for r in want]
     assert gm.cache_len() == 1
+    # switching the path in mid-sequence keeps the position
+    gm.use_persistent_step(not persistent)
+    nxt2 = gm.decode_step(2, None)
+    want2 = om.forward_cached(np.array([[oracle.argmax(r)] for r in want], np.int32))
+    assert nxt2.tolist() == [oracle.argmax(r) for r in want2]
+    assert gm.cache_len() == 2

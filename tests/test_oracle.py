@@ -273,3 +273,44 @@ def test_synthetic_generator_is_normal_and_stable():
     assert np.array_equal(w, again)
     t = oracle.synth_tokens(0, 0x20000000, 64, 50257)
     assert t.min() >= 0 and t.max() < 50257 and len(set(t.tolist())) > 50
+
+
+# ---- sampler (generation.rs:15-73) ----
+
+def test_rng_is_splitmix64():
+    """rand.rs:29-35 is SplitMix64; its published first outputs for seed 0 pin the constants and shifts."""
+    import ctypes as C
+    L = oracle.lib()
+    L.orc_rng_unit.restype = C.c_float
+    st = C.c_uint64(0)
+    want = [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F]
+    for z in want:
+        u = L.orc_rng_unit(C.byref(st))
+        assert u == np.float32((z >> 40) / float(1 << 24))  # Rng::unit: the top 24 bits (rand.rs:39-41)
+    assert st.value == (3 * 0x9E3779B97F4A7C15) % (1 << 64)
+
+
+def test_sampler_behaviour_reference_cases():
+    """tests/inference.rs:186-208, case by case."""
+    logits = np.array([1.0, 3.0, 2.0, -1.0], np.float32)
+    assert oracle.Sampler(0.0).sample(logits) == 1
+    assert oracle.Sampler(1.0, 1, 1.0, 7).sample(logits) == 1      # top_k = 1 is greedy
+    assert oracle.Sampler(1.0, 0, 0.01, 7).sample(logits) == 1     # tiny top_p is greedy
+    s = oracle.Sampler(1.0, 2, 1.0, 3)
+    assert all(s.sample(logits) in (1, 2) for _ in range(500))     # top_k = 2 never picks outside the two best
+    s = oracle.Sampler(1.0, 0, 1.0, 11)
+    counts = np.zeros(4)
+    for _ in range(20000):
+        counts[s.sample(logits)] += 1
+    p = np.exp(logits) / np.exp(logits).sum()
+    assert np.abs(counts / 20000.0 - p).max() < 0.015, counts       # frequencies follow softmax at temperature 1
+    def run(seed):
+        s = oracle.Sampler(0.8, 0, 0.95, seed)
+        return [s.sample(logits) for _ in range(20)]
+    assert run(5) == run(5)                                         # seeded: reproducible
+
+
+def test_sampler_ties_go_by_index_and_last_candidate_fallback():
+    logits = np.array([2.0, 2.0, 2.0, 0.0], np.float32)
+    s = oracle.Sampler(1.0, 2, 1.0, 1)
+    assert all(s.sample(logits) in (0, 1) for _ in range(200))      # the two kept of three equal logits are the first two
