@@ -3,8 +3,9 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-A step is one greedy decode step (one new token for each of the B sequences): the persistent
-cooperative kernel for up to two sequences, the captured launch chain beyond.  The default workload
+A step is one greedy decode step (one new token for each of the B sequences), run as the captured chain of
+launches (the default of the library; the faster of its two implementations on the shapes measured); the headline
+line also carries the same measurement through the one-launch persistent kernel (`persistent_step`).  The default workload
 is the one the headline target is quoted on: the Llama-3-8B-shaped model, int4 (group 32) weights with
 an int8 head, batch 1, 1024 cached positions.  Weights are seeded synthetic N(0, 0.02^2) generated and
 quantized on the device; nothing is read from disk.  With N > 1 (launched by torch.distributed.run, one
@@ -410,6 +411,30 @@ def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local
                            "note": "the quantized Linears of one step timed back to back (zero activations, no norm prologue: the bytes are the same)",
                            "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak, "bytes_per_step_per_gpu": step_bytes,
                                           "frac_of_nominal_8TBs": step_gbs / 8000.0}}
+    # ---- the same steps as ONE persistent cooperative kernel per token (opt-in implementation of the step) ----
+    if headline and world == 1 and kind == "llama" and B <= 2:
+        m.use_persistent_step(True)
+        if m.uses_persistent_step(B):
+            par2 = greedy_check(nn, m, model, bits, None)
+            m.cache_reserve(B, min(max_pos, ctx + K + W + 8))
+            m.cache_assume(B, ctx)
+            m.decode_step(B, ids_dev.ptr, fetch=True)
+            for _ in range(W - 1):
+                m.decode_step(B, None, fetch=False)
+            ms2 = []
+            for _ in range(max(3, min(regions, 6))):
+                region()
+                barrier()
+                dev.timer_start()
+                for _ in range(K):
+                    m.decode_step(B, None, fetch=False)
+                ms2.append(dev.timer_stop_ms())
+            med2 = float(np.median(ms2))
+            gbs2 = step_bytes / (med2 / K / 1000.0) / 1e9
+            res["persistent_step"] = {"value": B * K / (med2 / 1000.0), "unit": "tokens/s", "ms_per_step": med2 / K, "launches_per_step": m.step_launches(),
+                                      "regions": len(ms2), "achieved_gbs": gbs2, "frac": gbs2 / peak, "parity": par2,
+                                      "kernel": "pstep_kernel (the whole step as one cooperative launch; ruai_model_use_persistent_step)"}
+        m.use_persistent_step(False)
     m.close()
     return res
 
@@ -484,6 +509,8 @@ def main():
             "launches_per_step": r.get("launches_per_step"), "roofline": r.get("roofline"), "load_seconds": r["load_seconds"]}
     if r.get("parity") is not None:
         line["tp_parity" if world > 1 else "parity"] = r["parity"]
+    if r.get("persistent_step") is not None:
+        line["persistent_step"] = r["persistent_step"]
     if others:
         line["other_workloads"] = others
     if world == 1 and not args.no_cpu_baseline and not prefill:

@@ -137,5 +137,6 @@ extern "C" {
 
     // ---- tensor parallel ----
     pub fn ruai_tp_export(m: *mut ruai_model, handle_out: *mut c_void) -> c_int;
+    pub fn ruai_tp_resync(m: *mut ruai_model) -> c_int;
     pub fn ruai_tp_connect(m: *mut ruai_model, handles: *const c_void) -> c_int;
 }

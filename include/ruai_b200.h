@@ -284,6 +284,10 @@ int ruai_model_time_linears(ruai_model* m, uint32_t B, uint32_t iters, float* ms
 #define RUAI_IPC_HANDLE_BYTES 64
 int ruai_tp_export(ruai_model* m, void* handle_out /* RUAI_IPC_HANDLE_BYTES */);
 int ruai_tp_connect(ruai_model* m, const void* handles /* world * RUAI_IPC_HANDLE_BYTES */);
+/* After a step that failed with RUAI_ERR_TIMEOUT on any rank (a peer did not take part): once every rank has
+ * stopped stepping (the caller synchronises the ranks), each calls this to clear its side of the exchange; after a
+ * second synchronisation of the ranks, and a cache clear, stepping can resume.                                   */
+int ruai_tp_resync(ruai_model* m);
 
 #ifdef __cplusplus
 }

@@ -94,6 +94,7 @@ _PROTOS = {
     "ruai_model_step_launches": (C.c_int, [vp, C.POINTER(u32)]),
     "ruai_model_time_linears": (C.c_int, [vp, u32, u32, C.POINTER(C.c_float), C.POINTER(u32), C.POINTER(C.c_double)]),
     "ruai_tp_export": (C.c_int, [vp, vp]),
+    "ruai_tp_resync": (C.c_int, [vp]),
     "ruai_tp_connect": (C.c_int, [vp, vp]),
 }
 

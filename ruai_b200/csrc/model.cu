@@ -1239,6 +1239,16 @@ RUAI_API int ruai_tp_export(ruai_model* m, void* handle_out) {
   return ruai_tp_export_handle(m->ctx, &m->tp, handle_out);
 }
 
+RUAI_API int ruai_tp_resync(ruai_model* m) {
+  if (!m) return ruai_fail(nullptr, RUAI_ERR_ARG, "NULL argument");
+  if (m->world <= 1) return model_fail(m, RUAI_ERR_UNSUPPORTED, "the model is not sharded");
+  DeviceGuard g(m->ctx->ordinal);
+  RUAI_TRY(ruai_tp_resync_state(m->ctx, &m->tp));
+  RUAI_CUDA(m->ctx, cudaMemset(m->d_err.p, 0, sizeof(int32_t)));
+  (void)ruai_ctx_check_status(m->ctx);  // clears a pending status word
+  return RUAI_OK;
+}
+
 RUAI_API int ruai_tp_connect(ruai_model* m, const void* handles) {
   if (!m || !handles) return ruai_fail(nullptr, RUAI_ERR_ARG, "NULL argument");
   if (m->world <= 1) return model_fail(m, RUAI_ERR_UNSUPPORTED, "the model is not sharded");

@@ -14,7 +14,6 @@
 
 namespace {
 
-constexpr unsigned kSpinLimit = 1u << 22;  // x ~100 ns sleeps: about half a second
 
 struct TpDev {
   uint32_t rank, world;
@@ -24,15 +23,17 @@ struct TpDev {
   int2* aslots[kTpMaxWorld];      // per rank: [2][world][kTpArgmaxRows]
   float* data[kTpMaxWorld];       // per rank: [2][world][slot_floats]
   unsigned* seq;
+  unsigned spin_limit;            // polls (about 100 ns apart) a wait for a peer may take: by default about half a second
 };
 
 size_t flags_bytes() { return 2ull * kTpMaxWorld * kTpMaxCtas * sizeof(unsigned); }
 size_t aflags_bytes() { return 2ull * kTpMaxWorld * kTpArgmaxRows * sizeof(unsigned); }
 size_t aslots_bytes() { return 2ull * kTpMaxWorld * kTpArgmaxRows * sizeof(int2); }
 
-TpDev make_dev(const ruai_tp_state* t) {
+TpDev make_dev(const ruai_ctx* c, const ruai_tp_state* t) {
   TpDev d;
   d.rank = t->rank; d.world = t->world; d.slot_floats = t->slot_floats; d.seq = t->seq;
+  d.spin_limit = c->spin_limit < (1u << 30) ? c->spin_limit << 2 : 0xFFFFFFFFu;  // ruai_ctx_set_wait_limit scales both kinds of waits
   for (uint32_t p = 0; p < kTpMaxWorld; ++p) {
     char* base = (char*)t->peer[p];
     d.flags[p] = (unsigned*)base;
@@ -53,8 +54,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 
 // Returns false when the flag did not reach `want` within the limit.
-__device__ bool bounded_wait(const unsigned* flag, unsigned want) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
+__device__ bool bounded_wait(const unsigned* flag, unsigned want, unsigned limit) {
+  for (unsigned i = 0; i < limit; ++i) {
     if (ld_acquire_sys(flag) == want) return true;
     __nanosleep(100);
   }
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(TpDev t, const floa
   if (threadIdx.x < t.world && threadIdx.x != t.rank)
     st_release_sys(&t.flags[threadIdx.x][((size_t)par * t.world + t.rank) * kTpMaxCtas + blockIdx.x], seq);
   if (threadIdx.x < t.world && threadIdx.x != t.rank) {
-    if (!bounded_wait(&t.flags[t.rank][((size_t)par * t.world + threadIdx.x) * kTpMaxCtas + blockIdx.x], seq)) s_ok = 0;
+    if (!bounded_wait(&t.flags[t.rank][((size_t)par * t.world + threadIdx.x) * kTpMaxCtas + blockIdx.x], seq, t.spin_limit)) s_ok = 0;
   }
   __syncthreads();
   if (!s_ok) {
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(TpDev t, const float* _
     __threadfence_system();
     st_release_sys(&t.aflags[threadIdx.x][slot], seq);
     const size_t theirs = ((size_t)par * t.world + threadIdx.x) * kTpArgmaxRows + row;
-    if (!bounded_wait(&t.aflags[t.rank][theirs], seq)) s_ok = 0;
+    if (!bounded_wait(&t.aflags[t.rank][theirs], seq, t.spin_limit)) s_ok = 0;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -225,6 +226,17 @@ void ruai_tp_destroy(ruai_tp_state* t) {
   *t = ruai_tp_state();
 }
 
+// After an exchange that timed out the ranks' sequence numbers no longer agree.  Every rank, with none of its kernels in
+// flight and after all ranks have stopped stepping (the caller's barrier), clears its own flags and counts; after a
+// second barrier of the caller's the exchange starts again from sequence 0.
+int ruai_tp_resync_state(ruai_ctx* c, ruai_tp_state* t) {
+  RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+  RUAI_CUDA(c, cudaMemset(t->region, 0, flags_bytes() + aflags_bytes() + aslots_bytes()));
+  RUAI_CUDA(c, cudaMemset(t->seq, 0, 4 * sizeof(unsigned)));
+  RUAI_CUDA(c, cudaDeviceSynchronize());
+  return RUAI_OK;
+}
+
 int ruai_tp_export_handle(ruai_ctx* c, ruai_tp_state* t, void* handle_out) {
   static_assert(sizeof(cudaIpcMemHandle_t) == RUAI_IPC_HANDLE_BYTES, "IPC handle size");
   cudaIpcMemHandle_t h;
@@ -258,12 +270,12 @@ int ruai_tp_allreduce_add(ruai_ctx* c, ruai_tp_state* t, float* x, uint32_t rows
   uint32_t ctas = (count4 + 1023) / 1024;  // 4 float4 per thread
   ctas = ctas < 1 ? 1 : (ctas > kTpMaxCtas ? kTpMaxCtas : ctas);
   if (sumsq && !(ctas == 1 && rows == 1)) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "the exchange gives the sum of squares only for one row in one CTA");
-  RUAI_CUDA(c, ruai_launch(c, allreduce_push_kernel, dim3(ctas), dim3(256), 0, true, make_dev(t), (const float*)t->partial, x, count4, err, sumsq));
+  RUAI_CUDA(c, ruai_launch(c, allreduce_push_kernel, dim3(ctas), dim3(256), 0, true, make_dev(c, t), (const float*)t->partial, x, count4, err, sumsq));
   return RUAI_OK;
 }
 
 int ruai_tp_argmax(ruai_ctx* c, ruai_tp_state* t, const float* logits, uint32_t n_local, uint32_t rows, uint32_t col_offset, int32_t* out, int* err) {
   if (rows > kTpArgmaxRows) return ruai_fail(c, RUAI_ERR_UNSUPPORTED, "argmax over %u rows exceeds %u", rows, kTpArgmaxRows);
-  RUAI_CUDA(c, ruai_launch(c, tp_argmax_kernel, dim3(rows), dim3(1024), 0, true, make_dev(t), logits, n_local, col_offset, out, err));
+  RUAI_CUDA(c, ruai_launch(c, tp_argmax_kernel, dim3(rows), dim3(1024), 0, true, make_dev(c, t), logits, n_local, col_offset, out, err));
   return RUAI_OK;
 }

@@ -22,6 +22,7 @@ int ruai_tp_init(ruai_ctx* c, ruai_tp_state* t, uint32_t rank, uint32_t world, u
 void ruai_tp_destroy(ruai_tp_state* t);
 int ruai_tp_export_handle(ruai_ctx* c, ruai_tp_state* t, void* handle_out);
 int ruai_tp_connect_handles(ruai_ctx* c, ruai_tp_state* t, const void* handles);
+int ruai_tp_resync_state(ruai_ctx* c, ruai_tp_state* t);
 int ruai_tp_check_ready(ruai_ctx* c, ruai_tp_state* t, uint32_t rows, uint32_t d);
 // x[rows, d] += sum over ranks of partial[rows, d], the same bits on every rank.
 // With `sumsq` (one row, d <= 4096 only) it also leaves sum(x^2) of the new row there, as one tile.

@@ -417,6 +417,10 @@ class _Model:
         self.dev.check(self.dev.L.ruai_tp_export(self.h, buf))
         return bytes(buf.raw)
 
+    def tp_resync(self):
+        """Clear this rank's side of the exchange after a timed-out step (see ruai_tp_resync for the protocol)."""
+        self.dev.check(self.dev.L.ruai_tp_resync(self.h))
+
     def tp_connect(self, handles):
         blob = b"".join(handles)
         self.dev.check(self.dev.L.ruai_tp_connect(self.h, blob))

@@ -264,23 +264,27 @@ FULL = {
 }
 
 
+@pytest.mark.parametrize("persistent", [False, True])
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("name", ["tinyllama-1.1b", "llama3-8b"])
-def test_full_depth_greedy_tokens_and_logits(dev, greedy_golden, name, bits):
+def test_full_depth_greedy_tokens_and_logits(dev, greedy_golden, name, bits, persistent):
     """All 22 / 32 layers, prompt 16, 32 greedy tokens: identical ids, and the logits of every step within max-abs 1e-2
-    and 1e-3 of the row's largest magnitude.  The expected values come from tests/golden/make_greedy_golden.py (the CPU
-    checker run on the full model); the top-2 margins stored there show every pick is decisive (>= 7e-3)."""
+    and 1e-3 of the row's largest magnitude, on both implementations of the single-token step (chain of launches,
+    persistent kernel).  The expected values come from tests/golden/make_greedy_golden.py (the CPU checker run on the
+    full model); the top-2 margins stored there show every pick is decisive (>= 7e-3)."""
     key = f"{name}-int{bits}"
     ids, margin = greedy_golden[key + "/ids"], greedy_golden[key + "/margin"]
     want, absmax = greedy_golden[key + "/logits"], greedy_golden[key + "/absmax"]
     _, gc = llama_cfg(**FULL[name])
     gm = nn.Llama(dev, gc)
     gm.load_synthetic(0, bits, 32)
+    gm.use_persistent_step(persistent)
+    assert gm.uses_persistent_step(1) == persistent
     prompt = oracle.synth_tokens(0, 0x20000000, 16, FULL[name]["V"])
     assert prompt.tolist() == ids[:16].tolist()
     got = gm.generate(prompt, 32)
     assert got.tolist() == ids.tolist(), f"first difference at {int(np.argmax(got != ids)) - 16}; margins {margin[:4]}"
-    # teacher-forced logits of every step (persistent single-token steps after the prompt)
+    # teacher-forced logits of every step (single-token steps after the prompt)
     gm.cache_clear()
     rows = [gm.forward_cached(prompt[None, :])[0]]
     for t in ids[16:-1]:
@@ -305,17 +309,18 @@ def test_large_batch_decode_steps(dev, name, B, cfg):
     nxt = np.array([oracle.argmax(r) for r in lo], np.int32)
     ids_dev = nn.Tensor.from_numpy(dev, nxt)
     for step in range(2):
+        # both models are fed the checker's ids, so that a near-tie in one step does not send them down different paths
         lo = om.forward_cached(nxt[:, None])
         want_next = np.array([oracle.argmax(r) for r in lo], np.int32)
-        got_next = gm.decode_step(B, ids_dev.ptr if step == 0 else None)
+        got_next = gm.decode_step(B, ids_dev.ptr)
         srt = np.sort(lo, axis=1)
         decisive = (srt[:, -1] - srt[:, -2]) > 1e-4
         assert (got_next[decisive] == want_next[decisive]).all(), f"{name}: step {step}"
+        assert gm.cache_len() == om.cache_len() == 3 + step + 1
         nxt = want_next
         ids_dev = nn.Tensor.from_numpy(dev, nxt)
-        gm.cache_clear(); om.cache_clear()
-        break_after = step  # one checked step per cache state keeps the two models on the same ids
-        lo = om.forward_cached(prompts); gm.forward_cached(prompts)
+    # the logits of one more step, all B rows
+    close(om.forward_cached(nxt[:, None]), gm.forward_cached(nxt[:, None]), name + " step logits")
 
 
 # ---- sampling on the device (generation.rs:15-73) ----

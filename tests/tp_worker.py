@@ -12,10 +12,23 @@ import numpy as np
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def barrier(d, rank, world, name):
+    """All ranks have reached `name` (files in DIR)."""
+    open(os.path.join(d, f"{name}.{rank}"), "w").close()
+    t0 = time.time()
+    while not all(os.path.exists(os.path.join(d, f"{name}.{r}")) for r in range(world)):
+        if time.time() - t0 > 120:
+            raise SystemExit(f"rank {rank}: barrier {name} timed out")
+        time.sleep(0.02)
+
+
 def main():
     rank, world, d, bits = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4])
+    scenario = sys.argv[5] if len(sys.argv) > 5 else "generate"
     from ruai_b200 import nn
     dev = nn.Device.cuda(rank)
+    if scenario == "peer_skips_a_step":
+        dev.set_wait_limit(250000)  # about 0.1 s per wait for a peer instead of half a second; before the first step
     cfg = nn.LlamaConfig(1024, 512, 1536, 3, 8, 4, 64, 256, 1e-5, 10000.0, 0)
     m = nn.Llama(dev, cfg, nn.TP(rank, world))
     m.load_synthetic(3, bits, 32)
@@ -33,6 +46,27 @@ def main():
         handles.append(open(p, "rb").read())
     m.tp_connect(handles)
     prompt = np.array([(i * 37 + 11) % 1024 for i in range(12)], np.int32)
+    if scenario == "peer_skips_a_step":
+        # Failure made on the host: rank 1 leaves out one step (between steps, nothing of its own in flight).  Rank 0's
+        # waits for the peer run out, its call reports RUAI_ERR_TIMEOUT, nothing hangs.  Then both resynchronise.
+        barrier(d, rank, world, "start")  # the ranks begin within the (shortened) wait of each other
+        m.forward_cached(prompt[None, :], want_logits=False)
+        tok = nn.Tensor.from_numpy(dev, np.array([5], np.int32))
+        m.decode_step(1, tok.ptr)
+        barrier(d, rank, world, "before")
+        outcome = "ok"
+        if rank == 0:
+            try:
+                m.decode_step(1, None)
+            except nn.RuaiError as e:
+                outcome = "timeout" if e.code == 4 and "timed out" in str(e) else f"other: {e}"
+        barrier(d, rank, world, "after")
+        m.tp_resync()
+        barrier(d, rank, world, "resynced")
+        m.cache_clear()
+        ids = m.generate(prompt, 24)
+        np.savez(os.path.join(d, f"out{rank}.npz"), ids=ids, steps=np.zeros((1, 1), np.int32), outcome=np.array(outcome))
+        return
     ids = m.generate(prompt, 24)
     # batched device-resident steps as well
     B = 4
