@@ -236,15 +236,17 @@ def time_regions(dev, run_region, barrier, regions):
     return out
 
 
-def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local_rank=0, headline=False):
+def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local_rank=0, headline=False, layers=None, persistent=False):
     """Loads the model of `name`, times it; returns the fields of its result."""
     model, bits, B, ctx, prefill = parse_workload(name)
     kind, dims = MODELS[model]
     peak, peak_tf, peak_src = measured_peaks()
     t0 = time.time()
-    cfg = make_cfg(nn, model)
+    cfg = make_cfg(nn, model, layers=layers)
     m = nn.Llama(dev, cfg, nn.TP(rank, world) if world > 1 else None) if kind == "llama" else nn.GPT2(dev, cfg)
     m.load_synthetic(0, bits, 32)
+    if persistent:
+        m.use_persistent_step(True)
     if world > 1:
         handles = [None] * world
         dist.all_gather_object(handles, m.tp_export())
@@ -295,7 +297,7 @@ def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local
         return res
 
     parity = None
-    if headline and kind == "llama":
+    if headline and kind == "llama" and not layers:
         gather = None
         if dist is not None:
             def gather(x):
@@ -412,7 +414,7 @@ def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local
                            "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak, "bytes_per_step_per_gpu": step_bytes,
                                           "frac_of_nominal_8TBs": step_gbs / 8000.0}}
     # ---- the same steps as ONE persistent cooperative kernel per token (opt-in implementation of the step) ----
-    if headline and world == 1 and kind == "llama" and B <= 2:
+    if headline and world == 1 and kind == "llama" and B <= 2 and not layers and not persistent:
         m.use_persistent_step(True)
         if m.uses_persistent_step(B):
             par2 = greedy_check(nn, m, model, bits, None)
@@ -449,6 +451,10 @@ def main():
     ap.add_argument("--regions", type=int, default=12, help="timed regions of exactly --steps steps; the median is reported")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the other workloads measured alongside the default one")
+    ap.add_argument("--profile-layers", type=int, default=0,
+                    help="profiling aid (not a benchmark configuration): build the model with this many layers so that a profiler's capture stays small; "
+                         "the line says so in config.layers and skips the golden-token check")
+    ap.add_argument("--persistent", action="store_true", help="profiling aid: time the persistent one-launch step as the main measurement")
     args = ap.parse_args()
     model, bits, B, ctx, prefill = parse_workload(args.workload)
     kind, dims = MODELS[model]
@@ -486,7 +492,11 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = nn.Device.cuda(local_rank)
-    r = run_workload(nn, dev, args.workload, K, W, max(args.regions, 1), rank, world, dist, local_rank, headline=True)
+    if args.profile_layers:
+        config["layers"] = args.profile_layers
+        config["note"] = "reduced layer count for a profiler capture: not a benchmark configuration"
+    r = run_workload(nn, dev, args.workload, K, W, max(args.regions, 1), rank, world, dist, local_rank, headline=True,
+                     layers=args.profile_layers or None, persistent=args.persistent)
     others = []
     if world == 1 and not args.no_others and args.workload == "llama3-8b-int4-b1":
         for name in OTHER_WORKLOADS:
