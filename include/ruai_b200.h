@@ -132,7 +132,9 @@ int ruai_linear_lora_forward(ruai_ctx* ctx, const float* x_dev, const ruai_qweig
                              float* out_dev, uint32_t m);
 /* ruai_matmul_q for hosts that cannot let this library allocate device memory at run time
  * (a serving process whose framework already owns the whole device, or a loop that cannot
- * afford cudaMalloc's implicit synchronisation).  Same arguments, same results.  It has no
+ * afford cudaMalloc's implicit synchronisation).  Same arguments; results within the same
+ * tolerance of the reference's CPU path (it always runs the first-generation f32 kernel, so the
+ * bits equal ruai_matmul_q's only with RUAI_B200_TC=0 and RUAI_B200_BULK=0).  It has no
  * counterpart in the reference.  The split-K scratch lives in a fixed 8 MiB + 16 KiB array
  * inside the loaded module (held on every GPU that loads the library until exit); a call
  * whose split plan needs more fails with RUAI_ERR_UNSUPPORTED and says so.  The first call

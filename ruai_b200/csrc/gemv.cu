@@ -479,7 +479,9 @@ RUAI_API int ruai_matmul_q_static(ruai_ctx* c, int x_dtype, const void* x, const
     g_static_scratch_addr[c->ordinal] = p;
   }
   unsigned char* base = (unsigned char*)g_static_scratch_addr[c->ordinal];
-  // the same work split as ruai_matmul_q, so both give the same bits
+  // the work split of the first-generation kernel: the same bits as ruai_matmul_q gives when the tensor-core and bulk-copy
+  // kernels are off (RUAI_B200_TC=0, RUAI_B200_BULK=0); against the default dispatch the results agree within the
+  // GPU-vs-CPU tolerance (other activation rounding, other order of the partial sums)
   const int mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16;
   const uint32_t row_tiles = (m + mt - 1) / mt;
   const uint32_t col_tiles = (w->n + kThreads - 1) / kThreads;

@@ -432,22 +432,36 @@ int ensure_cache(ruai_model* m, uint32_t B, uint32_t need) {
   const uint32_t cap = std::max(std::max(need, 2 * m->cap), 16u);
   const size_t per = (size_t)B * m->KVl * cap * m->hd * sizeof(float);
   RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
-  for (Layer& L : m->layers) {
+  // Layer by layer (at most one layer's old and new buffers exist together).  If an allocation or copy fails half way
+  // the layers would disagree about their capacity: the whole cache is dropped then (as after cache_clear, contents
+  // lost) and the error says so, so that the model stays usable.
+  auto grow_layer = [&](Layer& L) -> int {
     DevBuf nk, nv;
-    RUAI_TRY(nk.alloc(c, per));
-    RUAI_TRY(nv.alloc(c, per));
-    RUAI_CUDA(c, cudaMemsetAsync(nk.p, 0, per, c->stream));
-    RUAI_CUDA(c, cudaMemsetAsync(nv.p, 0, per, c->stream));
-    if (m->len > 0 && L.kc.p) {
+    auto bail = [&](int rc) { nk.release(); nv.release(); return rc; };
+    if (nk.alloc(c, per) != RUAI_OK || nv.alloc(c, per) != RUAI_OK) return bail(RUAI_ERR_CUDA);
+    cudaError_t e = cudaMemsetAsync(nk.p, 0, per, c->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(nv.p, 0, per, c->stream);
+    if (e == cudaSuccess && m->len > 0 && L.kc.p) {
       const size_t row = (size_t)m->hd * sizeof(float);
-      RUAI_CUDA(c, cudaMemcpy2DAsync(nk.p, (size_t)cap * row, L.kc.p, (size_t)m->cap * row, (size_t)m->len * row, (size_t)B * m->KVl,
-                                     cudaMemcpyDeviceToDevice, c->stream));
-      RUAI_CUDA(c, cudaMemcpy2DAsync(nv.p, (size_t)cap * row, L.vc.p, (size_t)m->cap * row, (size_t)m->len * row, (size_t)B * m->KVl,
-                                     cudaMemcpyDeviceToDevice, c->stream));
+      e = cudaMemcpy2DAsync(nk.p, (size_t)cap * row, L.kc.p, (size_t)m->cap * row, (size_t)m->len * row, (size_t)B * m->KVl, cudaMemcpyDeviceToDevice, c->stream);
+      if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(nv.p, (size_t)cap * row, L.vc.p, (size_t)m->cap * row, (size_t)m->len * row, (size_t)B * m->KVl, cudaMemcpyDeviceToDevice, c->stream);
     }
-    RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) return bail(ruai_fail(c, RUAI_ERR_CUDA, "KV cache growth: %s", cudaGetErrorString(e)));
     L.kc.release(); L.vc.release();
     L.kc = nk; L.vc = nv;
+    return RUAI_OK;
+  };
+  for (Layer& L : m->layers) {
+    if (grow_layer(L) != RUAI_OK) {
+      (void)cudaGetLastError();  // an allocation failure is not sticky; later launch checks must not see it
+      for (Layer& L2 : m->layers) { L2.kc.release(); L2.vc.release(); }
+      m->cap = 0; m->len = 0; m->len_dirty = true; m->B = 0;
+      drop_graph(m);
+      m->ps.table_cap = 0;
+      return model_fail(m, RUAI_ERR_CUDA, "KV cache: growing to %u positions for batch %u failed (%zu bytes per layer and tensor); the cache was dropped", cap, B, per);
+    }
   }
   m->cap = cap;
   drop_graph(m);

@@ -383,3 +383,20 @@ def test_sampled_generation_matches_checker(dev, persistent):
         assert got[:7 + safe].tolist() == want[:7 + safe].tolist(), (seed, safe)
         agree += safe
     assert agree >= 24
+
+
+def test_failed_cache_growth_leaves_the_model_usable(dev):
+    """A cache the device cannot hold (one allocation of terabytes, refused by the driver at once: nothing is consumed)
+    fails with an error that says the cache was dropped; the model then answers as after cache_clear."""
+    cfg = dict(V=331, d=256, ffn=704, L=3, H=8, KV=2, hd=32, max_pos=256)
+    om, gm = build(dev, llama_cfg(**cfg), 2, 8, 32)
+    prompt = oracle.synth_tokens(0, 0x20000000, 9, cfg["V"])[None, :]
+    close(om.forward_cached(prompt), gm.forward_cached(prompt), "before")
+    gm.cache_clear()
+    om.cache_clear()
+    with pytest.raises(nn.RuaiError, match="cache was dropped"):
+        gm.cache_reserve(1 << 26, 256)
+    assert gm.cache_len() == 0
+    close(om.forward_cached(prompt), gm.forward_cached(prompt), "after the failed growth")
+    tok = np.array([[7]], np.int32)
+    close(om.forward_cached(tok), gm.forward_cached(tok), "a step after it")
