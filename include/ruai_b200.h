@@ -73,6 +73,9 @@ int ruai_ctx_set_wait_limit(ruai_ctx* ctx, unsigned polls);
  * more grid-wide arrivals precede it than really do, so its first grid barrier can never
  * complete and its bounded wait runs out.  Nothing faults; used by the timeout tests. */
 int ruai_ctx_inject_barrier_skew(ruai_ctx* ctx, unsigned grids);
+/* The same for a shared-memory barrier: the first bulk copy of the next persistent launch is announced `bytes` larger
+ * than it is, so the barrier it signals never completes and the consumers' bounded wait for that stage runs out. */
+int ruai_ctx_inject_copy_shortfall(ruai_ctx* ctx, unsigned bytes);
 
 /* Device memory for callers without their own allocator (cuda.rs:288-300). */
 int ruai_malloc(ruai_ctx* ctx, size_t bytes, void** out_dev);

@@ -1,6 +1,6 @@
 """Build recipe of the CPU checker (test infrastructure, not the product).
 
-`build()` compiles oracle/oracle.cpp into oracle/_ref/liboracle.so with
+`build()` compiles oracle/oracle.cpp into oracle/_build/liboracle.so with
 `g++ -O2 -ffp-contract=off -fopenmp`.  The reference implementation itself is
 Rust and no Rust toolchain exists where this runs, so there is no reference
 binary to build; the checker is the restatement in oracle.cpp.
@@ -9,7 +9,7 @@ import os
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-OUT_DIR = os.path.join(HERE, "_ref")
+OUT_DIR = os.path.join(HERE, "_build")  # the restatement compiled here: not a build of the reference itself
 LIB = os.path.join(OUT_DIR, "liboracle.so")
 SRC = os.path.join(HERE, "oracle.cpp")
 DEPS = [SRC, os.path.join(HERE, "..", "include", "ruai_b200.h"), os.path.join(HERE, "..", "include", "ruai_b200_synth.h")]

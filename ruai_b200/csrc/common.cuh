@@ -40,6 +40,7 @@ struct ruai_ctx {
   // persistent kernels (pstep.cu)
   unsigned spin_limit = 1u << 20;  // polls of a bounded device-side wait (about a second)
   unsigned barrier_skew = 0;       // failure injection: extra arrivals (in grids) the next persistent launch will wait for in vain
+  unsigned tx_shortfall = 0;       // failure injection: bytes the first bulk copy of the next persistent launch is announced too large by
   unsigned* ps_sync = nullptr;     // [0] grid barrier counter, [1] abort flag, [2..3] poison, for ruai_matmul_q_stream
   unsigned ps_bar_base = 0;
   // sampler scratch (sample.cu): sort keys, probabilities, the sort's temporary storage

@@ -747,6 +747,8 @@ int pstep_run(ruai_model* m, uint32_t B) {
   P.arg_slots = S.arg_slots.as<int2>();
   P.bar = S.sync.as<unsigned>(); P.bar_base = S.bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status; P.abort_flag = S.sync.as<int>() + 1;
   P.spin_limit = c->spin_limit;
+  P.tx_shortfall = c->tx_shortfall;
+  c->tx_shortfall = 0;
   P.want_argmax = 1;
   P.trace = c->trace;
   c->barrier_skew = 0;

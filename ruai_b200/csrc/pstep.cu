@@ -104,6 +104,7 @@ struct PhaseDesc {
 struct Common {
   uint32_t m;
   unsigned* bar; unsigned bar_base; int* status; int* abort_flag; unsigned spin_limit;
+  unsigned tx_shortfall;  // failure injection: see StepParams
   // attention / final (step program only)
   const StepParams* sp;
   float* out;  // test program: f32 [m][n]
@@ -724,7 +725,7 @@ __device__ bool produce_gemv(Ctx<MT>& X, const PhaseDesc& D) {
         PS_TRACE_STAGE(X, X.s, 0);
         X.sh->rec[slot] = make_uint2(tile, (windowed ? u - ru : blk) | (cnt << 16));
         const uint32_t bytes = cnt * rec;
-        mbar_expect_tx(&X.sh->b.full[slot], bytes);
+        mbar_expect_tx(&X.sh->b.full[slot], bytes + (X.s == 0u ? X.c.tx_shortfall : 0u));
         bulk_load(X.smem + kOffSlots + (size_t)slot * kSlotBytes, src, bytes, &X.sh->b.full[slot]);
         src += bytes; u += cnt; blk += cnt; ++X.s;
         if (++slot == (uint32_t)kSlots) { slot = 0; ++use; }
@@ -1490,7 +1491,17 @@ __device__ void run_program(const Prog& prog, unsigned char* smem, Shared* sh, u
       producer_loop<MT>(X, prog, len);
       // no copy may be in flight when the CTA leaves
       const uint32_t issued = X.s;
-      for (uint32_t i = issued > (uint32_t)kSlots ? issued - kSlots : 0u; i < issued; ++i) mbar_wait(&sh->b.full[i % kSlots], (i / kSlots) & 1u);
+      for (uint32_t i = issued > (uint32_t)kSlots ? issued - kSlots : 0u; i < issued; ++i) {
+        // bounded like every wait, but not cut short by the abort flag: the point is to outlast the copies
+        const uint32_t a = smem_u32(&sh->b.full[i % kSlots]), parity = (i / kSlots) & 1u;
+        for (unsigned poll = 0; poll < X.c.spin_limit; ++poll) {
+          uint32_t ok;
+          asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                       : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+          if (ok) break;
+          __nanosleep(100);
+        }
+      }
     }
   } else {
     const bool scribe = X.warp == kWarpIssuer1 && X.lane == 1;  // a lane with no role of its own writes the descriptors
@@ -1540,7 +1551,7 @@ __global__ void __launch_bounds__(kThreads, 1) pstep_kernel(const StepParams Pin
   __syncthreads();
   if (threadIdx.x == 0) {
     Common& cm = sh.c;
-    cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
+    cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit; cm.tx_shortfall = P.tx_shortfall;
     cm.sp = &P; cm.out = nullptr; cm.trace = P.trace;
   }
   StepProgram prog{P, lay};
@@ -1556,7 +1567,7 @@ __global__ void __launch_bounds__(kThreads, 1) pgemv_kernel(const GemvTestParams
   __syncthreads();
   if (threadIdx.x == 0) {
     Common& cm = sh.c;
-    cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit;
+    cm.m = P.m; cm.bar = P.bar; cm.bar_base = P.bar_base; cm.status = P.status; cm.abort_flag = P.abort_flag; cm.spin_limit = P.spin_limit; cm.tx_shortfall = P.tx_shortfall;
     cm.sp = nullptr; cm.out = P.out; cm.trace = P.trace;
   }
   TestProgram prog{P};
@@ -1666,8 +1677,10 @@ RUAI_API int ruai_matmul_q_stream(ruai_ctx* c, const float* x_dev, const ruai_qw
   P.x = x_dev; P.acc = reinterpret_cast<long long*>(c->partial); P.poison = reinterpret_cast<int*>(c->ps_sync + 2); P.out = out_dev;
   P.bar = c->ps_sync; P.bar_base = c->ps_bar_base + c->barrier_skew * (unsigned)grid; P.status = c->status;
   P.abort_flag = reinterpret_cast<int*>(c->ps_sync + 1); P.spin_limit = c->spin_limit;
+  P.tx_shortfall = c->tx_shortfall;
   P.trace = c->trace;
   c->barrier_skew = 0;
+  c->tx_shortfall = 0;
   RUAI_TRY(ruai_pgemv_launch(c, P));
   c->ps_bar_base += (2u * repeat - 1u) * (unsigned)grid;
   return RUAI_OK;
@@ -1676,6 +1689,12 @@ RUAI_API int ruai_matmul_q_stream(ruai_ctx* c, const float* x_dev, const ruai_qw
 RUAI_API int ruai_ctx_set_wait_limit(ruai_ctx* c, unsigned polls) {
   if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
   c->spin_limit = polls ? polls : (1u << 20);
+  return RUAI_OK;
+}
+
+RUAI_API int ruai_ctx_inject_copy_shortfall(ruai_ctx* c, unsigned bytes) {
+  if (!c) return ruai_fail(nullptr, RUAI_ERR_ARG, "ctx is NULL");
+  c->tx_shortfall = bytes;
   return RUAI_OK;
 }
 

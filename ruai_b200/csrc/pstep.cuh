@@ -71,6 +71,7 @@ struct StepParams {
   int* status;              // context status word: 3 = a bounded wait ran out
   int* abort_flag;          // set by the first CTA that gives up; everyone else leaves at its next wait
   unsigned spin_limit;      // polls of a grid-barrier wait
+  unsigned tx_shortfall;    // failure injection (host-made): the first stage's copy is announced this many bytes too large
   int want_argmax;
   unsigned long long* trace;  // profiling builds (RUAI_B200_TRACE): per-stage clock stamps of CTA 0, else unused
 };
@@ -85,6 +86,7 @@ struct GemvTestParams {
   int* poison;           // [kMaxRows]
   float* out;            // f32 [m][n]
   unsigned* bar; unsigned bar_base; int* status; int* abort_flag; unsigned spin_limit;
+  unsigned tx_shortfall;
   unsigned long long* trace;
 };
 

@@ -52,6 +52,9 @@ class Device:
     def inject_barrier_skew(self, grids):
         self.check(self.L.ruai_ctx_inject_barrier_skew(self.ctx, grids))
 
+    def inject_copy_shortfall(self, nbytes):
+        self.check(self.L.ruai_ctx_inject_copy_shortfall(self.ctx, nbytes))
+
     def timer_start(self):
         self.check(self.L.ruai_timer_start(self.ctx))
 

@@ -183,7 +183,7 @@ def test_matmul_grid_f32(dev, m, k, n, bits):
 
 
 # the Llama-3-8B widths (hidden 4096, q/k/v 6144, MLP 14336) at prefill-sized row counts, ragged and full tiles
-WIDE = [(17, 4096, 14336), (64, 4096, 6144), (128, 14336, 4096), (512, 4096, 4096)]
+WIDE = [(17, 4096, 14336), (64, 4096, 6144), (128, 14336, 4096), (512, 4096, 4096), (17, 4096, 28672), (64, 4096, 28672), (512, 14336, 4096)]
 
 
 @pytest.mark.parametrize("bits", [8, 4])
@@ -205,6 +205,19 @@ def test_matmul_grid_8b_widths(dev, m, k, n, bits):
     assert err <= 1e-2 and err <= 1e-3 * np.abs(want).max(), (err, np.abs(want).max())
     loose = ~(np.abs(want - y) <= 1e-4 * (1 + np.abs(want)))
     assert loose.mean() <= 1e-4, f"{loose.sum()} of {loose.size} outputs beyond the tests/devices.rs tolerance"
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("m", [17, 64])
+def test_matmul_head_width_int8(dev, m):
+    """The 8B head [4096 -> 128256], int8 as the reference keeps it, at more than 16 rows (the GEMM path)."""
+    k, n = 4096, 128256
+    x = oracle.synth_normal(15, m, (m, k), 1.0)
+    q, s = oracle.quantize_int8(oracle.synth_normal(15, 3, (k, n)))
+    want = oracle.matmul_int8(x, q, s)
+    _, y = run_matmul(dev, x, nn.QWeight.int8(dev, q, s), "f32")
+    err = np.abs(want.astype(np.float64) - y).max()
+    assert err <= 1e-2 and err <= 1e-3 * np.abs(want).max(), (err, np.abs(want).max())
 
 
 @pytest.mark.parametrize("bits", [8, 4])

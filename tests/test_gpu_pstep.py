@@ -142,6 +142,29 @@ def test_bounded_wait_runs_out_and_the_context_survives(dev):
     dev.synchronize()
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+def test_copy_that_never_completes_runs_the_stage_wait_out(dev, bits):
+    """The same for a shared-memory barrier: the first bulk copy is announced larger than it is (on the host), the
+    barrier it signals never completes, the consumers' bounded wait for that stage runs out, the kernel leaves in
+    order (tensor memory freed, no copy in flight), RUAI_ERR_TIMEOUT is reported and the next call is correct."""
+    q, s, w = make_weight(dev, bits, 576, 576, 2)
+    x = oracle.synth_normal(3, 2, (1, 576), 1.0)
+    xt = nn.Tensor.from_numpy(dev, x)
+    want = ref_matmul(bits, x, q, s)
+    same(want, nn.matmul_q_stream(xt, w).numpy())
+    dev.set_wait_limit(4000)
+    dev.inject_copy_shortfall(16)
+    try:
+        with pytest.raises(nn.RuaiError, match="bounded wait") as e:
+            nn.matmul_q_stream(xt, w)
+            dev.synchronize()
+        assert e.value.code == 4  # RUAI_ERR_TIMEOUT
+    finally:
+        dev.set_wait_limit(0)
+    same(want, nn.matmul_q_stream(xt, w).numpy())
+    dev.synchronize()
+
+
 # ---- the whole step -----------------------------------------------------------------------------------------
 
 def close(want, got, what=""):
@@ -218,11 +241,13 @@ def test_persistent_step_attention_geometries(dev, H, KV, hd):
         tok = np.argmax(want, axis=1).astype(np.int32).reshape(2, 1)
 
 
-def test_persistent_greedy_tokens_and_device_argmax_ties(dev):
-    """Greedy generation through the persistent step equals the checker's; with two identical head columns the device
-    pick takes the larger index (generation.rs:6-8, the last maximum)."""
+@pytest.mark.parametrize("persistent", [True, False])
+def test_greedy_tokens_and_device_argmax_ties(dev, persistent):
+    """Greedy generation through either implementation of the step equals the checker's; with two identical head columns
+    the device pick (the persistent kernel's pick phase; the chain's fused pick of the head GEMV) takes the larger index
+    (generation.rs:6-8, the last maximum)."""
     oc, gc = llama_cfgs(**SMALL)
-    om, gm = build_pair(dev, (oc, gc), 4, 4)
+    om, gm = build_pair(dev, (oc, gc), 4, 4, persistent=persistent)
     prompt = oracle.synth_tokens(0, 0x20000000, 9, SMALL["V"])
     assert gm.generate(prompt, 40).tolist() == om.generate(prompt, 40).tolist()
     # a model whose lm_head is zero except for two identical columns: the largest logit is always shared by several
@@ -243,7 +268,7 @@ def test_persistent_greedy_tokens_and_device_argmax_ties(dev):
     gm2.set_f32(0x10000001, head)
     gm2.set_f32(0x40000000, np.ones(c["d"], np.float32))
     gm2.quantize_int8()
-    gm2.use_persistent_step(True)
+    gm2.use_persistent_step(persistent)
     logits = gm2.forward_cached(np.array([[5]], np.int32))
     assert logits[0, 17] == logits[0, 300]
     best = float(logits.max())
@@ -253,6 +278,11 @@ def test_persistent_greedy_tokens_and_device_argmax_ties(dev):
     gm2.cache_clear()
     nxt = gm2.decode_step(1, ids.ptr)
     assert nxt[0] == ties[-1], (nxt, ties)
+    # several sequences at once (the chain's separate argmax kernel; the persistent pick for two rows)
+    for B in (2,) if persistent else (2, 5):
+        gm2.cache_clear()
+        idsB = nn.Tensor.from_numpy(dev, np.full(B, 5, np.int32))
+        assert gm2.decode_step(B, idsB.ptr).tolist() == [int(ties[-1])] * B
 
 
 @pytest.mark.parametrize("persistent", [True, False])

@@ -76,3 +76,27 @@ def test_a_rank_that_skips_a_step_times_the_peer_out_and_both_recover():
     prompt = np.array([(i * 37 + 11) % 1024 for i in range(12)], np.int32)
     want = om.generate(prompt, 24)
     assert outs[0]["ids"].tolist() == want.tolist() and outs[1]["ids"].tolist() == want.tolist()
+
+
+def test_vocabulary_parallel_argmax_tie_goes_to_the_larger_index():
+    """Two identical head columns, one in each rank's half of the vocabulary (17 and 900): the exchanged pick is the
+    last maximum globally (generation.rs:6-8), for one and for several sequences, on both ranks."""
+    if _lib.load().ruai_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    with tempfile.TemporaryDirectory() as d:
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), d, "8", "argmax_tie"], env=env)
+                 for r in range(world)]
+        try:
+            for p in procs:
+                assert p.wait(timeout=300) == 0
+        finally:
+            for p in procs:
+                if p.poll() is None:
+                    p.kill()
+        outs = [np.load(os.path.join(d, f"out{r}.npz")) for r in range(world)]
+    for o in outs:
+        # the largest logit is shared by the two columns, or (if negative) by all the zero columns: the last of them wins
+        assert set(o["ids"].tolist()) <= {900, 1023} and len(set(o["ids"].tolist())) == 1, o["ids"]
+    assert outs[0]["ids"].tolist() == outs[1]["ids"].tolist()

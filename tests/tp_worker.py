@@ -31,7 +31,24 @@ def main():
         dev.set_wait_limit(250000)  # about 0.1 s per wait for a peer instead of half a second; before the first step
     cfg = nn.LlamaConfig(1024, 512, 1536, 3, 8, 4, 64, 256, 1e-5, 10000.0, 0)
     m = nn.Llama(dev, cfg, nn.TP(rank, world))
-    m.load_synthetic(3, bits, 32)
+    if scenario == "argmax_tie":
+        # a head that is zero except for two identical columns, one in each rank's half of the vocabulary
+        import oracle
+        V, dm, ffn, L, H, KV, hd = 1024, 512, 1536, 3, 8, 4, 64
+        shapes = {0: (dm, H * hd), 1: (dm, KV * hd), 2: (dm, KV * hd), 3: (H * hd, dm), 4: (dm, ffn), 5: (dm, ffn), 6: (ffn, dm)}
+        for layer in range(L):
+            for kind, shp in shapes.items():
+                m.set_f32(layer * 16 + kind, oracle.synth_normal(7, layer * 16 + kind, shp))
+            m.set_f32(0x50000000 + layer, np.ones(dm, np.float32))
+            m.set_f32(0x52000000 + layer, np.ones(dm, np.float32))
+        m.set_f32(0x10000000, oracle.synth_normal(7, 0x10000000, (V, dm)))
+        head = np.zeros((dm, V), np.float32)
+        head[:, 17] = head[:, 900] = oracle.synth_normal(7, 99, (dm,))
+        m.set_f32(0x10000001, head)
+        m.set_f32(0x40000000, np.ones(dm, np.float32))
+        m.quantize_int8()
+    else:
+        m.load_synthetic(3, bits, 32)
     with open(os.path.join(d, f"h{rank}.tmp"), "wb") as f:
         f.write(m.tp_export())
     os.rename(os.path.join(d, f"h{rank}.tmp"), os.path.join(d, f"h{rank}"))
@@ -46,6 +63,14 @@ def main():
         handles.append(open(p, "rb").read())
     m.tp_connect(handles)
     prompt = np.array([(i * 37 + 11) % 1024 for i in range(12)], np.int32)
+    if scenario == "argmax_tie":
+        picks = []
+        for B in (1, 3):
+            m.cache_clear()
+            t = nn.Tensor.from_numpy(dev, np.full(B, 5, np.int32))
+            picks.append(m.decode_step(B, t.ptr).tolist())
+        np.savez(os.path.join(d, f"out{rank}.npz"), ids=np.array(sum(picks, []), np.int32), steps=np.zeros((1, 1), np.int32))
+        return
     if scenario == "peer_skips_a_step":
         # Failure made on the host: rank 1 leaves out one step (between steps, nothing of its own in flight).  Rank 0's
         # waits for the peer run out, its call reports RUAI_ERR_TIMEOUT, nothing hangs.  Then both resynchronise.
