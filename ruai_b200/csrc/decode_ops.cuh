@@ -33,6 +33,8 @@ int ruai_rope_table(ruai_ctx* c, const float* inv_freq, uint32_t half, uint32_t 
 int ruai_rope_kv(ruai_ctx* c, float* qkv, uint32_t qkv_ld, uint32_t k_off, uint32_t v_off, const float2* table, const int32_t* len, uint32_t rows,
                  uint32_t T, uint32_t Hq, uint32_t KV, uint32_t hd, uint32_t cap, float* kcache, float* vcache);
 int ruai_attention(ruai_ctx* c, const AttnParams& p, uint32_t B, uint32_t rep, uint32_t splits);
+// Many query positions at once, queries in tiles (attn_prefill.cu).  1: launched; 0: not taken for this shape; < 0: error.
+int ruai_attention_prefill(ruai_ctx* c, const AttnParams& p, uint32_t B, uint32_t rep);
 int ruai_argmax(ruai_ctx* c, const float* logits, uint32_t ld, uint32_t rows, uint32_t n, int32_t* out, uint32_t out_offset);
 // Sampler::sample (generation.rs:38-73) on one row of device logits; the token is left at token_dev (sample.cu).
 int ruai_sample_device(ruai_ctx* c, const float* logits_dev, uint32_t vocab, float temperature, uint32_t top_k, float top_p, uint64_t* rng_state,

@@ -26,7 +26,8 @@ constexpr int kCols = 128;        // columns of W per CTA = MMA M = TMEM lanes
 constexpr int kRows = 128;        // rows of x per CTA = MMA N
 constexpr int kStageGroups = 2;   // groups of 32 k per pipeline stage
 constexpr int kBStages = 3;       // ring of B stages in shared memory
-constexpr int kThreads = kCols + 64;
+constexpr int kWorkers = 2 * kCols;  // eight warps: thread = (column, half); a half expands one of a stage's two groups and reads out half the rows
+constexpr int kThreads = kWorkers + 64;
 constexpr uint32_t kBGroupBytes = 2 * 2 * kRows * 32;  // pieces x k-steps x rows x 32 B = 16 KB per group of 32 k
 
 // ---- activations -> two bf16 pieces in B-operand layout --------------------------------------------
@@ -123,13 +124,14 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
   unsigned char* bring = smem + off_b;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t j0 = blockIdx.x * kCols, j = j0 + tid, rb = blockIdx.y, row0 = rb * kRows;
-  const bool active = tid < kCols && j < p.n;
+  const uint32_t col = (uint32_t)tid & (kCols - 1), half = (uint32_t)tid >> 7;  // workers only
+  const uint32_t j0 = blockIdx.x * kCols, j = j0 + col, rb = blockIdx.y, row0 = rb * kRows;
+  const bool active = tid < kWorkers && j < p.n;
   const uint32_t nst = (p.groups + kStageGroups - 1) / kStageGroups;
 
   if (tid == 0) {
     for (int s = 0; s < kBStages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&a_ready[s], kCols / 32); mbar_init(&mma_done[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&a_ready[s], kWorkers / 32); mbar_init(&mma_done[s], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_abort = 0;
   }
@@ -142,28 +144,29 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
 
   // packed weights of this thread's column, one stage ahead (they do not depend on the predecessor kernel)
   constexpr int kChunksPerGroup = BITS == 4 ? 1 : 2;
-  uint4 wq[kStageGroups][kChunksPerGroup];
-  float sq[kStageGroups];
+  uint4 wq[kChunksPerGroup];   // this thread's group (number `half`) of the stage
+  float sq[kStageGroups];      // the column's scales of both groups (the read-out needs both)
   auto load_stage = [&](uint32_t i) {
+    const uint32_t g = i * kStageGroups + half;
+#pragma unroll
+    for (int h = 0; h < kChunksPerGroup; ++h) {
+      const uint32_t c = g * kChunksPerGroup + h;
+      const bool in = active && c < p.chunks;
+      wq[h] = in ? __ldg(&p.w[(size_t)c * p.n + j]) : (BITS == 4 ? make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u) : make_uint4(0, 0, 0, 0));
+    }
 #pragma unroll
     for (int u = 0; u < kStageGroups; ++u) {
-      const uint32_t g = i * kStageGroups + u;
-      sq[u] = 0.0f;
-#pragma unroll
-      for (int h = 0; h < kChunksPerGroup; ++h) {
-        const uint32_t c = g * kChunksPerGroup + h;
-        const bool in = active && c < p.chunks;
-        wq[u][h] = in ? __ldg(&p.w[(size_t)c * p.n + j]) : (BITS == 4 ? make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u) : make_uint4(0, 0, 0, 0));
-      }
-      if (BITS == 4) sq[u] = (active && g < p.groups) ? __ldg(&p.scale[(size_t)g * p.n + j]) : 0.0f;
+      const uint32_t gu = i * kStageGroups + u;
+      sq[u] = (BITS == 4 && active && gu < p.groups) ? __ldg(&p.scale[(size_t)gu * p.n + j]) : 0.0f;
     }
   };
-  if (tid < kCols) load_stage(0);
+  if (tid < kWorkers) load_stage(0);
   grid_dependency_wait();
   grid_launch_dependents();
 
-  float acc[kRows];  // epilogue threads: this column's sums for the 128 rows
-  if (warp == kCols / 32) {
+  constexpr int kHalfRows = kRows / 2;
+  float acc[kHalfRows];  // worker threads: this column's sums for the thread's 64 rows
+  if (warp == kWorkers / 32) {
     // ===== MMA issuer =====
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_bf16(kRows);
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
         umma_commit(&b_empty[i % kBStages]);
       }
     }
-  } else if (warp == kCols / 32 + 1) {
+  } else if (warp == kWorkers / 32 + 1) {
     // ===== B producer: bulk copies of the split activations =====
     if (lane == 0) {
       for (uint32_t i = 0; i < nst; ++i) {
@@ -203,10 +206,10 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       }
     }
   } else {
-    // ===== four warps: packed weights -> bf16 A tile; accumulators -> scaled sums =====
+    // ===== eight warps: packed weights -> bf16 A tile; accumulators -> scaled sums =====
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) acc[r] = 0.0f;
-    {  // per-row RMS factor of this CTA's rows (needed only in the epilogue)
+    for (int r = 0; r < kHalfRows; ++r) acc[r] = 0.0f;
+    if (tid < kRows) {  // per-row RMS factor of this CTA's rows (needed only in the epilogue)
       float rs = 1.0f;
       if (p.rstd_sumsq && row0 + tid < p.m) {
         float ss = 0.0f;
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       }
       s_rstd[tid] = rs;
     }
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     float sv_prev[kStageGroups] = {0.f, 0.f};
     auto drain = [&](uint32_t s, const float (&sv)[kStageGroups]) -> bool {  // int4: stage s's accumulators into acc
       if (!mbar_wait(&mma_done[s & 1], (s >> 1) & 1u)) return false;
@@ -225,9 +228,9 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       for (int u = 0; u < kStageGroups; ++u) {
         if ((uint32_t)u < ng) {
 #pragma unroll
-          for (int q = 0; q < kRows / 32; ++q) {
+          for (int q = 0; q < kHalfRows / 32; ++q) {
             float d[32];
-            tmem_ld32(tmem_base + lane_base + ((s & 1) * kStageGroups + u) * kRows + 32 * q, d);
+            tmem_ld32(tmem_base + lane_base + ((s & 1) * kStageGroups + u) * kRows + half * kHalfRows + 32 * q, d);
             tmem_ld_wait();
 #pragma unroll
             for (int t = 0; t < 32; ++t) acc[32 * q + t] = fmaf(d[t], sv[u], acc[32 * q + t]);
@@ -244,12 +247,12 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       if (i >= 2 && BITS == 8) { if (!mbar_wait(&mma_done[i & 1], ((i - 2) >> 1) & 1u)) { ok = false; break; } }
       float sv_cur[kStageGroups];
 #pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) {
-        sv_cur[u] = sq[u];
-        unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + u) * kAGroupBytes + (size_t)tid * 16;
+      for (int u = 0; u < kStageGroups; ++u) sv_cur[u] = sq[u];
+      {
+        unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + half) * kAGroupBytes + (size_t)col * 16;
         if (BITS == 4) {
           // 32 nibbles (value + 8) -> 32 bf16: (128 + u) has the bit pattern 0x4300 | u; subtract 136 in bf16 pairs
-          const uint32_t wd[4] = {wq[u][0].x, wq[u][0].y, wq[u][0].z, wq[u][0].w};
+          const uint32_t wd[4] = {wq[0].x, wq[0].y, wq[0].z, wq[0].w};
           const __nv_bfloat162 off = __floats2bfloat162_rn(136.0f, 136.0f);
           uint32_t o[16];
 #pragma unroll
@@ -275,7 +278,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
           // int8: chunk h of the group is k-step h; 16 bytes -> 16 bf16
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint32_t wd[4] = {wq[u][h].x, wq[u][h].y, wq[u][h].z, wq[u][h].w};
+            const uint32_t wd[4] = {wq[h].x, wq[h].y, wq[h].z, wq[h].w};
             uint32_t o[8];
 #pragma unroll
             for (int w4 = 0; w4 < 4; ++w4) {
@@ -309,9 +312,9 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
           tc_fence_after_sync();
           const float cs = active ? p.scale[j] : 0.0f;
 #pragma unroll
-          for (int q = 0; q < kRows / 32; ++q) {
+          for (int q = 0; q < kHalfRows / 32; ++q) {
             float d[32];
-            tmem_ld32(tmem_base + lane_base + 32 * q, d);
+            tmem_ld32(tmem_base + lane_base + half * kHalfRows + 32 * q, d);
             tmem_ld_wait();
 #pragma unroll
             for (int t = 0; t < 32; ++t) acc[32 * q + t] = d[t] * cs;
@@ -322,15 +325,15 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
     }
     if (!ok) s_abort = 1;
     // ---- epilogue: per-row RMS factor, bias, activation, residual, store (one row at a time: coalesced) ----
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // s_rstd of all four warps
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // s_rstd is written by the first four warps, read by all eight
     if (ok) {
       const GemvEpilogue& e = p.epi;
       const float bias = (e.bias && active) ? e.bias[j] : 0.0f;
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        const uint32_t row = row0 + r;
+      for (int r = 0; r < kHalfRows; ++r) {
+        const uint32_t row = row0 + half * kHalfRows + r;
         if (row >= p.m) break;
-        float v = acc[r] * s_rstd[r];
+        float v = acc[r] * s_rstd[half * kHalfRows + r];
         if (e.bias) v += bias;
         if (e.act == ACT_SWIGLU) {
           const float other = __shfl_xor_sync(0xFFFFFFFFu, v, 1);

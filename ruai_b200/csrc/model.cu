@@ -564,7 +564,11 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
     ap.fuse = fuse ? 1 : 0; ap.table = table; ap.k_off = nql; ap.v_off = nql + nkvl;
     ap.T = T; ap.KV = m->KVl; ap.hd = hd; ap.cap = m->cap; ap.scale = 1.0f / sqrtf((float)hd);
     ap.out = att; ap.out_ld = nql; ap.scratch = m->attn_scratch.as<float>(); ap.counters = m->attn_counters.as<unsigned>(); ap.status = c->status;
-    RUAI_TRY(ruai_attention(c, ap, B, rep, splits));
+    {
+      const int took = ruai_attention_prefill(c, ap, B, rep);  // many query positions: queries in tiles
+      if (took < 0) return RUAI_ERR_CUDA;
+      if (took == 0) RUAI_TRY(ruai_attention(c, ap, B, rep, splits));
+    }
     GemvEpilogue eo;
     eo.bias = Ly.o.bias.as<float>();
     if (!tp) {
