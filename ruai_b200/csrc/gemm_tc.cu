@@ -26,7 +26,9 @@ constexpr int kCols = 128;        // columns of W per CTA = MMA M = TMEM lanes
 constexpr int kRows = 128;        // rows of x per CTA = MMA N
 constexpr int kStageGroups = 2;   // groups of 32 k per pipeline stage
 constexpr int kBStages = 3;       // ring of B stages in shared memory
-constexpr int kWorkers = 2 * kCols;  // eight warps: thread = (column, half); a half expands one of a stage's two groups and reads out half the rows
+constexpr int kParts = 4;             // worker threads per column
+constexpr int kWorkers = kParts * kCols;  // sixteen warps: thread = (column, part); a part expands one k-step of one of a stage's two groups
+                                          // (16 of the group's 32 rows of W) and reads a quarter of the rows of x out of tensor memory
 constexpr int kThreads = kWorkers + 64;
 constexpr uint32_t kBGroupBytes = 2 * 2 * kRows * 32;  // pieces x k-steps x rows x 32 B = 16 KB per group of 32 k
 
@@ -124,7 +126,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
   unsigned char* bring = smem + off_b;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t col = (uint32_t)tid & (kCols - 1), half = (uint32_t)tid >> 7;  // workers only
+  const uint32_t col = (uint32_t)tid & (kCols - 1), part = (uint32_t)tid >> 7;  // workers only
+  const uint32_t pg = part >> 1, pstep = part & 1u;  // the group of the stage and the k-step of the group this thread expands
   const uint32_t j0 = blockIdx.x * kCols, j = j0 + col, rb = blockIdx.y, row0 = rb * kRows;
   const bool active = tid < kWorkers && j < p.n;
   const uint32_t nst = (p.groups + kStageGroups - 1) / kStageGroups;
@@ -144,16 +147,13 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
 
   // packed weights of this thread's column, one stage ahead (they do not depend on the predecessor kernel)
   constexpr int kChunksPerGroup = BITS == 4 ? 1 : 2;
-  uint4 wq[kChunksPerGroup];   // this thread's group (number `half`) of the stage
+  uint4 wq;                    // int4: the chunk of this thread's group; int8: the chunk that is its k-step of the group
   float sq[kStageGroups];      // the column's scales of both groups (the read-out needs both)
   auto load_stage = [&](uint32_t i) {
-    const uint32_t g = i * kStageGroups + half;
-#pragma unroll
-    for (int h = 0; h < kChunksPerGroup; ++h) {
-      const uint32_t c = g * kChunksPerGroup + h;
-      const bool in = active && c < p.chunks;
-      wq[h] = in ? __ldg(&p.w[(size_t)c * p.n + j]) : (BITS == 4 ? make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u) : make_uint4(0, 0, 0, 0));
-    }
+    const uint32_t g = i * kStageGroups + pg;
+    const uint32_t c = BITS == 4 ? g : g * kChunksPerGroup + pstep;
+    const bool in = active && c < p.chunks;
+    wq = in ? __ldg(&p.w[(size_t)c * p.n + j]) : (BITS == 4 ? make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u) : make_uint4(0, 0, 0, 0));
 #pragma unroll
     for (int u = 0; u < kStageGroups; ++u) {
       const uint32_t gu = i * kStageGroups + u;
@@ -164,8 +164,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
   grid_dependency_wait();
   grid_launch_dependents();
 
-  constexpr int kHalfRows = kRows / 2;
-  float acc[kHalfRows];  // worker threads: this column's sums for the thread's 64 rows
+  constexpr int kHalfRows = kRows / kParts;
+  float acc[kHalfRows];  // worker threads: this column's sums for the thread's 32 rows
   if (warp == kWorkers / 32) {
     // ===== MMA issuer =====
     if (lane == 0) {
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       }
     }
   } else {
-    // ===== eight warps: packed weights -> bf16 A tile; accumulators -> scaled sums =====
+    // ===== sixteen warps: packed weights -> bf16 A tile; accumulators -> scaled sums =====
 #pragma unroll
     for (int r = 0; r < kHalfRows; ++r) acc[r] = 0.0f;
     if (tid < kRows) {  // per-row RMS factor of this CTA's rows (needed only in the epilogue)
@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
 #pragma unroll
           for (int q = 0; q < kHalfRows / 32; ++q) {
             float d[32];
-            tmem_ld32(tmem_base + lane_base + ((s & 1) * kStageGroups + u) * kRows + half * kHalfRows + 32 * q, d);
+            tmem_ld32(tmem_base + lane_base + ((s & 1) * kStageGroups + u) * kRows + part * kHalfRows + 32 * q, d);
             tmem_ld_wait();
 #pragma unroll
             for (int t = 0; t < 32; ++t) acc[32 * q + t] = fmaf(d[t], sv[u], acc[32 * q + t]);
@@ -249,49 +249,37 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
 #pragma unroll
       for (int u = 0; u < kStageGroups; ++u) sv_cur[u] = sq[u];
       {
-        unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + half) * kAGroupBytes + (size_t)col * 16;
+        unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + pg) * kAGroupBytes + (size_t)col * 16 + pstep * 4096;
+        const uint32_t wd[4] = {wq.x, wq.y, wq.z, wq.w};
+        uint32_t o[8];
         if (BITS == 4) {
-          // 32 nibbles (value + 8) -> 32 bf16: (128 + u) has the bit pattern 0x4300 | u; subtract 136 in bf16 pairs
-          const uint32_t wd[4] = {wq[0].x, wq[0].y, wq[0].z, wq[0].w};
+          // 16 nibbles (value + 8) -> 16 bf16: (128 + u) has the bit pattern 0x4300 | u; subtract 136 in bf16 pairs.
+          // The low nibbles of the chunk are rows 0..15 of the group (k-step 0), the high nibbles rows 16..31 (k-step 1).
           const __nv_bfloat162 off = __floats2bfloat162_rn(136.0f, 136.0f);
-          uint32_t o[16];
 #pragma unroll
           for (int w4 = 0; w4 < 4; ++w4) {
-            const uint32_t lo = wd[w4] & 0x0F0F0F0Fu, hi = (wd[w4] >> 4) & 0x0F0F0F0Fu;  // rows 4w..4w+3 and 16+4w..
-            const uint32_t pl[2] = {__byte_perm(lo, 0x43434343u, 0x4140), __byte_perm(lo, 0x43434343u, 0x4342)};
-            const uint32_t ph[2] = {__byte_perm(hi, 0x43434343u, 0x4140), __byte_perm(hi, 0x43434343u, 0x4342)};
+            const uint32_t nib = (pstep ? (wd[w4] >> 4) : wd[w4]) & 0x0F0F0F0Fu;  // rows 4w..4w+3 of the k-step
+            const uint32_t pl[2] = {__byte_perm(nib, 0x43434343u, 0x4140), __byte_perm(nib, 0x43434343u, 0x4342)};
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               __nv_bfloat162 a2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pl[h]), off);
-              __nv_bfloat162 b2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&ph[h]), off);
-              o[2 * w4 + h] = *reinterpret_cast<uint32_t*>(&a2);      // rows 4w + 2h, +1
-              o[8 + 2 * w4 + h] = *reinterpret_cast<uint32_t*>(&b2);  // rows 16 + 4w + 2h, +1
+              o[2 * w4 + h] = *reinterpret_cast<uint32_t*>(&a2);  // rows 4w + 2h, +1
             }
           }
-          // k-step s, k-chunk c holds rows 16s + 8c .. +7 = o[8s + 4c .. +3]
-#pragma unroll
-          for (int s = 0; s < 2; ++s)
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              *reinterpret_cast<uint4*>(a + s * 4096 + c * 2048) = make_uint4(o[8 * s + 4 * c], o[8 * s + 4 * c + 1], o[8 * s + 4 * c + 2], o[8 * s + 4 * c + 3]);
         } else {
-          // int8: chunk h of the group is k-step h; 16 bytes -> 16 bf16
+          // int8: the chunk is the k-step; 16 bytes -> 16 bf16
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t wd[4] = {wq[h].x, wq[h].y, wq[h].z, wq[h].w};
-            uint32_t o[8];
-#pragma unroll
-            for (int w4 = 0; w4 < 4; ++w4) {
-              const int b0 = (int)(signed char)(wd[w4] & 0xFF), b1 = (int)(signed char)((wd[w4] >> 8) & 0xFF);
-              const int b2 = (int)(signed char)((wd[w4] >> 16) & 0xFF), b3 = (int)(signed char)(wd[w4] >> 24);
-              __nv_bfloat162 p0 = __floats2bfloat162_rn((float)b0, (float)b1), p1 = __floats2bfloat162_rn((float)b2, (float)b3);
-              o[2 * w4] = *reinterpret_cast<uint32_t*>(&p0);
-              o[2 * w4 + 1] = *reinterpret_cast<uint32_t*>(&p1);
-            }
-            *reinterpret_cast<uint4*>(a + h * 4096) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(a + h * 4096 + 2048) = make_uint4(o[4], o[5], o[6], o[7]);
+          for (int w4 = 0; w4 < 4; ++w4) {
+            const int b0 = (int)(signed char)(wd[w4] & 0xFF), b1 = (int)(signed char)((wd[w4] >> 8) & 0xFF);
+            const int b2 = (int)(signed char)((wd[w4] >> 16) & 0xFF), b3 = (int)(signed char)(wd[w4] >> 24);
+            __nv_bfloat162 p0 = __floats2bfloat162_rn((float)b0, (float)b1), p1 = __floats2bfloat162_rn((float)b2, (float)b3);
+            o[2 * w4] = *reinterpret_cast<uint32_t*>(&p0);
+            o[2 * w4 + 1] = *reinterpret_cast<uint32_t*>(&p1);
           }
         }
+        // k-chunk c of the k-step holds its rows 8c .. 8c+7 = o[4c .. 4c+3]
+        *reinterpret_cast<uint4*>(a) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(a + 2048) = make_uint4(o[4], o[5], o[6], o[7]);
       }
       load_stage(i + 1);
       fence_proxy_async_smem();
@@ -314,7 +302,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
 #pragma unroll
           for (int q = 0; q < kHalfRows / 32; ++q) {
             float d[32];
-            tmem_ld32(tmem_base + lane_base + half * kHalfRows + 32 * q, d);
+            tmem_ld32(tmem_base + lane_base + part * kHalfRows + 32 * q, d);
             tmem_ld_wait();
 #pragma unroll
             for (int t = 0; t < 32; ++t) acc[32 * q + t] = d[t] * cs;
@@ -325,15 +313,15 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
     }
     if (!ok) s_abort = 1;
     // ---- epilogue: per-row RMS factor, bias, activation, residual, store (one row at a time: coalesced) ----
-    asm volatile("bar.sync 1, 256;" ::: "memory");  // s_rstd is written by the first four warps, read by all eight
+    asm volatile("bar.sync 1, 512;" ::: "memory");  // s_rstd is written by the first four warps, read by all sixteen
     if (ok) {
       const GemvEpilogue& e = p.epi;
       const float bias = (e.bias && active) ? e.bias[j] : 0.0f;
 #pragma unroll
       for (int r = 0; r < kHalfRows; ++r) {
-        const uint32_t row = row0 + half * kHalfRows + r;
+        const uint32_t row = row0 + part * kHalfRows + r;
         if (row >= p.m) break;
-        float v = acc[r] * s_rstd[half * kHalfRows + r];
+        float v = acc[r] * s_rstd[part * kHalfRows + r];
         if (e.bias) v += bias;
         if (e.act == ACT_SWIGLU) {
           const float other = __shfl_xor_sync(0xFFFFFFFFu, v, 1);
