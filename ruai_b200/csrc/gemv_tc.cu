@@ -49,7 +49,17 @@ constexpr int n_of(int mt) { return mt <= 4 ? 16 : 32; }
 // about 52 KB of shared memory and 72 registers, so that three CTAs fit an SM; it serves launches of few stages per CTA.
 constexpr bool small_of(int mt, int ahead) { return mt <= 2 && ahead == 2; }
 constexpr int bufs_of(int mt, int ahead) { return mt <= 4 && !small_of(mt, ahead) ? 4 : 2; }
-constexpr int tmem_cols_of(int mt, int ahead) { return bufs_of(mt, ahead) * kStageGroups * n_of(mt); }  // 256 or 128
+// The standard variant for up to four rows keeps its A operand in TENSOR memory: an expanding thread's 32 bytes of a
+// group (its column's 32 rows of W) are exactly the 8 words of its lane there (lane = row of A, column c, byte b =
+// A[row][4 c + b]), so one tcgen05.st replaces the two 16-byte shared-memory stores, the proxy fence, and the tensor
+// core's own read of 16 KB of shared memory per stage.  Tensor memory per CTA stays 256 columns (two CTAs per SM): four
+// A buffers (4 x 4 groups x 8 columns) and two accumulator buffers (2 x 4 groups x 16 columns).
+constexpr bool a_in_tmem(int mt, int ahead) { return mt <= 4 && !small_of(mt, ahead); }
+constexpr int acc_bufs_of(int mt, int ahead) { return a_in_tmem(mt, ahead) ? 2 : bufs_of(mt, ahead); }
+constexpr int tmem_cols_of(int mt, int ahead) {  // 256 or 128
+  return a_in_tmem(mt, ahead) ? acc_bufs_of(mt, ahead) * kStageGroups * n_of(mt) + bufs_of(mt, ahead) * kStageGroups * 8
+                              : bufs_of(mt, ahead) * kStageGroups * n_of(mt);
+}
 
 struct Params {
   const uint4* w;
@@ -68,7 +78,7 @@ struct Smem {
   static constexpr int kN = n_of(MT);
   static constexpr int kBufs = bufs_of(MT, AHEAD);
   static constexpr size_t off_a = 0;
-  static constexpr size_t off_b = off_a + (size_t)kBufs * kStageGroups * kCols * 32;
+  static constexpr size_t off_b = off_a + (a_in_tmem(MT, AHEAD) ? 0 : (size_t)kBufs * kStageGroups * kCols * 32);  // no A buffers in shared memory where A is in tensor memory
   static constexpr size_t off_meta = off_b + 2 * (size_t)kRoundGroups * kN * 32;
   static constexpr size_t off_red = off_meta + 2 * (size_t)kRoundGroups * MT * 8;
   static size_t bytes(uint32_t splits) { return off_red + (size_t)splits * MT * kCols * 4 + 128; }
@@ -100,6 +110,11 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
   constexpr int kN = n_of(MT);
   constexpr int kBufs = bufs_of(MT, kAhead);
   constexpr int kTmemCols = tmem_cols_of(MT, kAhead);
+  constexpr bool kATmem = a_in_tmem(MT, kAhead);
+  constexpr int kAccBufs = acc_bufs_of(MT, kAhead);
+  constexpr uint32_t kATmemCol0 = kAccBufs * kStageGroups * kN;  // first column of the A buffers (kATmem)
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32, "tensor memory is allotted in powers of two");
+  static_assert(kRoundStages % kAccBufs == 0, "accumulator buffers must divide a round");
   static_assert(MT * kLimbs <= kN, "rows x limbs must fit the MMA N");
   static_assert((kBufs & (kBufs - 1)) == 0 && kRoundStages % kBufs == 0, "stage buffers must divide a round");
   using L = Smem<MT, kAhead>;
@@ -157,7 +172,8 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
   if (warp > kCols / 32) {
     // ===== expanding warps: packed weights -> A operand.  Nothing here depends on the predecessor kernel, so
     // these warps do not wait for it: the first kBufs stages are in place before the activations exist. =====
-    const int te = tid - kExpand0;
+    // (A in tensor memory: a warp reaches only the lanes 32 (warp % 4) .., so its threads take those columns)
+    const int te = kATmem ? (warp & 3) * 32 + lane : tid - kExpand0;
     const uint32_t je = j0 + te;
     const bool in_col = je < p.n;
     uint4 wq[kAhead][kStageGroups];
@@ -190,12 +206,24 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
           lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
           lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
           lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
-          unsigned char* dst = abuf + ((size_t)b * kStageGroups + u) * (kCols * 32) + (size_t)te * 16;
-          *reinterpret_cast<uint4*>(dst) = lo;
-          *reinterpret_cast<uint4*>(dst + kCols * 16) = hi;
+          if constexpr (kATmem) {
+            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + kATmemCol0 + (b * kStageGroups + u) * 8u;
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                         "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                         : "memory");
+          } else {
+            unsigned char* dst = abuf + ((size_t)b * kStageGroups + u) * (kCols * 32) + (size_t)te * 16;
+            *reinterpret_cast<uint4*>(dst) = lo;
+            *reinterpret_cast<uint4*>(dst + kCols * 16) = hi;
+          }
         }
         load_stage(i + kAhead, wq[a]);  // the stage kAhead further on, into the registers just consumed
-        fence_proxy_async_smem();
+        if constexpr (kATmem) {
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before_sync();
+        } else {
+          fence_proxy_async_smem();
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_ready[b]);
       }
@@ -225,7 +253,8 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
         const uint32_t b = i & (kBufs - 1), q = i / kBufs;
         bool ok = !s_abort;
         if (ok && (i % kRoundStages) == 0) ok = mbar_wait(&b_ready[(i / kRoundStages) & 1u], (i / (2 * kRoundStages)) & 1u);  // digits of the round
-        if (ok && q > 0) ok = mbar_wait(&acc_free[b], (q - 1) & 1u);  // the sums these MMAs overwrite have been read
+        const uint32_t ab = i & (kAccBufs - 1), aq = i / kAccBufs;  // accumulator buffer of this stage
+        if (ok && aq > 0) ok = mbar_wait(&acc_free[ab], (aq - 1) & 1u);  // the sums these MMAs overwrite have been read
         if (ok) ok = mbar_wait(&a_ready[b], q & 1u);
         if (!ok) { s_abort = 1; break; }
         tc_fence_after_sync();
@@ -233,14 +262,17 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
         const uint32_t gb = (i & (2 * kRoundStages - 1)) * kStageGroups;   // first group in the two rounds of digits
         const uint64_t ad = umma_desc_advance(ad0, slot * (kCols * 32));
         const uint64_t bd = umma_desc_advance(bd0, gb * (kN * 32));
-        const uint32_t d = tmem_base + slot * kN;
+        const uint32_t d = tmem_base + ab * kStageGroups * kN;
+        const uint32_t at = tmem_base + kATmemCol0 + slot * 8u;  // kATmem: the stage's A buffer in tensor memory
+        auto mma = [&](uint32_t u) {
+          if constexpr (kATmem) umma_i8_ts(d + u * kN, at + u * 8u, umma_desc_advance(bd, u * (kN * 32)), idesc, 0u);
+          else umma_i8(d + u * kN, umma_desc_advance(ad, u * (kCols * 32)), umma_desc_advance(bd, u * (kN * 32)), idesc, 0u);
+        };
         if (left >= (uint32_t)kStageGroups) {
 #pragma unroll
-          for (uint32_t u = 0; u < (uint32_t)kStageGroups; ++u)
-            umma_i8(d + u * kN, umma_desc_advance(ad, u * (kCols * 32)), umma_desc_advance(bd, u * (kN * 32)), idesc, 0u);
+          for (uint32_t u = 0; u < (uint32_t)kStageGroups; ++u) mma(u);
         } else {
-          for (uint32_t u = 0; u < left; ++u)
-            umma_i8(d + u * kN, umma_desc_advance(ad, u * (kCols * 32)), umma_desc_advance(bd, u * (kN * 32)), idesc, 0u);
+          for (uint32_t u = 0; u < left; ++u) mma(u);
         }
         umma_commit(&mma_done[b]);
       }
@@ -363,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
           int32_t d[kBatch][kQ * 4];
 #pragma unroll
           for (int ub = 0; ub < kBatch; ++ub) {
-            const uint32_t col = tmem_base + lane_base + (b * kStageGroups + u0 + ub) * kN;
+            const uint32_t col = tmem_base + lane_base + ((a & (kAccBufs - 1)) * kStageGroups + u0 + ub) * kN;
 #pragma unroll
             for (int q4 = 0; q4 < kQ; ++q4) {
               int32_t t4[4];
@@ -375,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
           if (u0 + kBatch >= kStageGroups) {  // the last sums of the stage are out: the next MMAs into this buffer may go
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_free[b]);
+            if (lane == 0) mbar_arrive(&acc_free[a & (kAccBufs - 1)]);
           }
 #pragma unroll
           for (int ub = 0; ub < kBatch; ++ub) {
