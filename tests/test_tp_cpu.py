@@ -72,3 +72,81 @@ def test_sharded_linears_sum_to_the_unsharded_result(tmp_path, bits):
     assert np.abs(r["y"] - r["y_full"]).max() <= 1e-4 * (1 + np.abs(r["y_full"]).max())
     # ties: every rank's slice has 7.0 at its first and last column; the global pick is the last column of the last rank
     assert r["idx"].tolist() == [int(r["V"]) - 1] * 3
+
+
+# ---- the flag / parity protocol of the exchange, modelled on the host ------------------------------------------------
+
+class _Rank:
+    """What one rank's side of allreduce_push_kernel (tp.cu) does, step by step, on shared host arrays: slots and flags
+    are double-buffered by the parity of a sequence number; a rank pushes its part into every peer's slot, releases
+    the flag with the sequence number, and waits (bounded) for every peer's flag to reach the same number."""
+
+    def __init__(self, rank, world, slots, flags, limit):
+        self.rank, self.world, self.slots, self.flags, self.limit, self.seq = rank, world, slots, flags, limit, 0
+
+    def exchange(self, part):
+        import time
+        seq = self.seq + 1
+        par = seq & 1
+        for p in range(self.world):
+            if p != self.rank:
+                self.slots[p][par][self.rank][:] = part
+                self.flags[p][par][self.rank] = seq          # release after the data
+        ok = True
+        for p in range(self.world):
+            if p == self.rank:
+                continue
+            t0 = time.time()
+            while self.flags[self.rank][par][p] != seq:
+                if time.time() - t0 > self.limit:
+                    ok = False
+                    break
+                time.sleep(0.0005)
+        self.seq = seq                                        # advances whether or not the wait ran out (as on the device)
+        if not ok:
+            return None
+        total = np.zeros_like(part)
+        for p in range(self.world):                           # rank order: identical bits everywhere
+            total = total + (part if p == self.rank else self.slots[self.rank][par][p])
+        return total
+
+    def resync(self):
+        self.seq = 0
+        for par in range(2):
+            self.flags[self.rank][par][:] = 0
+
+
+def test_exchange_protocol_with_a_rank_that_never_posts():
+    """Host model of the exchange: both ranks agree for several steps (the double buffering by parity holds when one
+    rank runs a step ahead); a rank that leaves a step out makes the other's bounded wait run out (no result, no
+    hang); the sequence numbers then disagree, so a later exchange fails as well until both sides resynchronise."""
+    import threading
+    world, n = 2, 64
+    slots = [np.zeros((2, world, n), np.float32) for _ in range(world)]
+    flags = [np.zeros((2, world), np.int64) for _ in range(world)]
+    ranks = [_Rank(r, world, slots, flags, 0.2) for r in range(world)]
+    parts = lambda step, r: np.full(n, 10.0 * step + r + 1, np.float32)
+
+    def run(step, who):
+        out = {}
+        ts = [threading.Thread(target=lambda r=r: out.__setitem__(r, ranks[r].exchange(parts(step, r)))) for r in who]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        return out
+
+    for step in range(5):
+        out = run(step, (0, 1))
+        want = parts(step, 0) + parts(step, 1)
+        assert np.array_equal(out[0], want) and np.array_equal(out[1], want)
+    out = run(5, (0,))                       # rank 1 leaves the step out
+    assert out[0] is None                    # the wait ran out; nothing hung
+    out = run(6, (0, 1))                     # sequence numbers differ by one now: rank 0 waits for 7, rank 1 posts 6
+    assert out[0] is None
+    # ... while rank 1 finds rank 0's flag of the step it missed and adds that step's stale part: after a time-out
+    # anywhere, every rank has to stop and resynchronise (ruai_tp_resync) before the results mean anything again
+    assert np.array_equal(out[1], parts(5, 0) + parts(6, 1))
+    for r in ranks:
+        r.resync()
+    out = run(7, (0, 1))
+    want = parts(7, 0) + parts(7, 1)
+    assert np.array_equal(out[0], want) and np.array_equal(out[1], want)
