@@ -85,10 +85,13 @@ struct Smem {
 };
 
 // Activations of one round for layouts the 16-byte path cannot take (any dtype, any alignment): one value at a time.
+// For one or two rows it is inlined and unrolled, so that the row array stays in registers (handing it to a function by
+// address puts it, and the fast path's copy with it, into per-thread local memory); for more rows the function call
+// keeps the kernel small and the array is in local memory either way.
 template <int MT>
-static __device__ __noinline__ void fetch_round_scalar(float4* dst, const void* x, int x_dtype, uint32_t x_ld, uint32_t m0, uint32_t rows, uint32_t kidx,
-                                                       uint32_t k, bool in, const float* norm_w) {
-#pragma unroll 1
+static __device__ __forceinline__ void fetch_round_scalar_body(float4* dst, const void* x, int x_dtype, uint32_t x_ld, uint32_t m0, uint32_t rows,
+                                                               uint32_t kidx, uint32_t k, bool in, const float* norm_w) {
+#pragma unroll
   for (int r = 0; r < MT; ++r) {
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (in && r < (int)rows) {
@@ -102,6 +105,17 @@ static __device__ __noinline__ void fetch_round_scalar(float4* dst, const void* 
     }
     dst[r] = make_float4(v[0], v[1], v[2], v[3]);
   }
+}
+template <int MT>
+static __device__ __noinline__ void fetch_round_scalar_call(float4* dst, const void* x, int x_dtype, uint32_t x_ld, uint32_t m0, uint32_t rows,
+                                                            uint32_t kidx, uint32_t k, bool in, const float* norm_w) {
+  fetch_round_scalar_body<MT>(dst, x, x_dtype, x_ld, m0, rows, kidx, k, in, norm_w);
+}
+template <int MT>
+static __device__ __forceinline__ void fetch_round_scalar(float4 (&dst)[MT], const void* x, int x_dtype, uint32_t x_ld, uint32_t m0, uint32_t rows,
+                                                          uint32_t kidx, uint32_t k, bool in, const float* norm_w) {
+  if constexpr (MT <= 2) fetch_round_scalar_body<MT>(dst, x, x_dtype, x_ld, m0, rows, kidx, k, in, norm_w);
+  else fetch_round_scalar_call<MT>(dst, x, x_dtype, x_ld, m0, rows, kidx, k, in, norm_w);
 }
 
 // kAhead: stages of packed weights an expanding thread holds in registers ahead of their use.
