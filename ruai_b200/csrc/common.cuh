@@ -214,6 +214,9 @@ int ruai_gemv_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int
 bool ruai_gemv_tc8_eligible(const ruai_qweight* w, uint32_t m);
 int ruai_gemv_tc8_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                          const GemvEpilogue& epi, const GemvPrologue& pro);
+bool ruai_gemv_wide_eligible(const ruai_ctx* ctx, const ruai_qweight* w, uint32_t m);
+int ruai_gemv_wide_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
+                          const GemvEpilogue& epi, const GemvPrologue& pro);
 bool ruai_gemm_tc_eligible(const ruai_qweight* w, uint32_t m);
 int ruai_gemm_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                         const GemvEpilogue& epi, const GemvPrologue& pro);

@@ -376,6 +376,7 @@ int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dt
   if (m == 0) return RUAI_OK;
   if (c->use_bulk && c->use_tc && ruai_gemm_tc_eligible(w, m) && !epi_in.sumsq && !epi_in.argmax_out)
     return ruai_gemm_tc_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
+  if (c->use_bulk && c->use_tc && ruai_gemv_wide_eligible(c, w, m)) return ruai_gemv_wide_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   if (c->use_bulk && c->use_tc && ruai_gemv_tc8_eligible(w, m) && !(epi_in.argmax_out && m > 8)) return ruai_gemv_tc8_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   if (c->use_bulk && c->use_tc && ruai_gemv_tc_eligible(w, m)) return ruai_gemv_tc_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);
   if (c->use_bulk && ruai_gemv_bulk_eligible(w)) return ruai_gemv_bulk_launch(c, w, x, x_dtype, x_ld, m, out, epi_in, pro);

@@ -117,6 +117,25 @@ def test_causal_and_batched(dev):
     assert np.abs(both[0] - la[0]).max() < 1e-5 and np.abs(both[1] - lb[0]).max() < 1e-5
 
 
+@pytest.mark.parametrize("B", [9, 13, 16])
+@pytest.mark.parametrize("kind,bits", [("llama", 4), ("llama", 8), ("gpt2", 8)])
+def test_steps_of_nine_to_sixteen_sequences(dev, kind, bits, B):
+    """Decode steps of 9..16 sequences (one 16-row tile on the tensor cores, weights read once): logits of every row
+    against the checker, a layer-reduced model of mid width so that the Linears split k and have ragged column tiles."""
+    if kind == "llama":
+        cfgs = llama_cfg(V=1000, d=576, ffn=1568, L=2, H=9, KV=3, hd=64, max_pos=64)
+    else:
+        cfgs = gpt2_cfg(V=1000, n_pos=64, d=192, L=2, H=6)
+    om, gm = build(dev, cfgs, 5, bits, 32)
+    prompts = np.stack([oracle.synth_tokens(5, 0x20000000 + b, 2, 1000) for b in range(B)])
+    lo = om.forward_cached(prompts)
+    close(lo, gm.forward_cached(prompts), "prefill")
+    for step in range(3):
+        nxt = np.array([oracle.argmax(r) for r in lo], np.int32)[:, None]
+        lo = om.forward_cached(nxt)
+        close(lo, gm.forward_cached(nxt), f"{kind} int{bits} B={B} step {step}")
+
+
 @pytest.mark.parametrize("H,KV,hd,B", [(4, 2, 96, 1), (6, 6, 24, 3), (8, 1, 40, 2), (4, 2, 96, 40)])
 def test_attention_geometries(dev, H, KV, hd, B):
     """Head dimensions that are not powers of two, 1 / 2 / 8 query heads per KV head, and enough sequences to take the

@@ -207,6 +207,40 @@ def test_matmul_grid_8b_widths(dev, m, k, n, bits):
     assert loose.mean() <= 1e-4, f"{loose.sum()} of {loose.size} outputs beyond the tests/devices.rs tolerance"
 
 
+# 9..16 rows: the 16-row tile (weights streamed once).  Shapes chosen so that k splits over 1, 2, 4 and 8 CTAs, the last
+# stage and the last column tile are ragged, and k is not a multiple of the group.
+ROWS16 = [(9, 64, 48), (12, 96, 130), (16, 4096, 512), (13, 4096, 6144), (16, 14336, 4096), (10, 4096, 28672), (16, 1000, 130), (11, 1536, 1536)]
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,k,n", ROWS16)
+def test_matmul_nine_to_sixteen_rows(dev, m, k, n, bits):
+    if bits == 4 and k % 32:
+        k = (k // 32) * 32
+    x = oracle.synth_normal(17, 0x32000000 + m * 31 + k, (m, k), 1.0)
+    x[:, ::5] = 0.0
+    w = oracle.synth_normal(17, k * 65537 + n, (k, n))
+    if bits == 8:
+        q, s = oracle.quantize_int8(w)
+        qw, want = nn.QWeight.int8(dev, q, s), oracle.matmul_int8(x, q, s)
+    else:
+        q, s = oracle.quantize_int4(w, 32)
+        qw, want = nn.QWeight.int4(dev, q, s, 32), oracle.matmul_int4(x, q, s)
+    bias = oracle.synth_normal(17, 98, (n,))
+    _, y = run_matmul(dev, x, qw, "f32", bias)
+    want = want + bias
+    # the activations ride as two bf16 pieces (16 significant bits): the stated tolerance of quantized-Linear outputs,
+    # and all but a sliver inside the 1e-4 of tests/devices.rs
+    err = np.abs(want.astype(np.float64) - y).max()
+    assert err <= 1e-2 and err <= 1e-3 * np.abs(want).max(), (err, np.abs(want).max())
+    loose = ~(np.abs(want - y) <= 1e-4 * (1 + np.abs(want)))
+    assert loose.mean() <= 1e-4, f"{loose.sum()} of {loose.size} outputs beyond the tests/devices.rs tolerance"
+    for dtype in ("f16", "bf16"):
+        xf, yh = run_matmul(dev, x, qw, dtype, bias)
+        ref = oracle.matmul_int8(xf, q, s) if bits == 8 else oracle.matmul_int4(xf, q, s)
+        same(round_to(ref + bias, dtype), yh, TOL[dtype])
+
+
 @pytest.mark.slow
 @pytest.mark.parametrize("m", [17, 64])
 def test_matmul_head_width_int8(dev, m):
