@@ -614,9 +614,9 @@ int issue_step(ruai_model* m, uint32_t B, uint32_t T, bool all_positions, bool w
     out_rows = B;
   }
   GemvEpilogue eh;
-  // the pick rides in the head GEMV's epilogue where that runs as one row tile on the tensor-core kernel (up to 8 rows);
-  // beyond, the tensor-core kernel (two row tiles) plus the separate argmax kernel beats the CUDA-core kernel that could fuse it
-  const bool fused_pick = want_argmax && !tp && out_rows <= 8;
+  // the pick rides in the head GEMV's epilogue where that runs as one row tile on a tensor-core kernel (up to 4 rows, or
+  // 5..16 on the 16-row tile); otherwise the separate argmax kernel beats the CUDA-core kernel that could fuse it
+  const bool fused_pick = want_argmax && !tp && (out_rows <= 8 || (c->use_bulk && c->use_tc && ruai_gemv_wide_eligible(c, m->head.w, out_rows)));
   if (fused_pick) {
     eh.argmax_out = m->d_ids.as<int32_t>(); eh.argmax_slots = m->arg_slots.as<int2>(); eh.argmax_counter = m->arg_counter.as<unsigned>();
     eh.len_ptr = len; eh.len_add = (int32_t)T;
