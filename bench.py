@@ -48,6 +48,10 @@ OTHER_WORKLOADS = ["llama3-8b-int8-b1", "llama3-8b-int4-b16", "llama3-8b-int4-b1
 ARITHMETIC = ("f32 in and out; inside the GEMV the activations are block fixed point (int4 weights: 21 bits per group of 32; "
               "int8 weights: 28 bits per row of a CTA's slice), products exact in tcgen05 kind::i8, one f32 scale multiply-add "
               "per group, split-k sums met in 64-bit fixed point")
+# steps of 5..16 sequences (and prefill-sized row counts): another arithmetic
+ARITHMETIC_WIDE = ("f32 in and out; inside the Linears the activations are two bf16 pieces x = hi + lo (16 significant bits), the int4 / "
+                   "int8 weights exact in bf16, products and sums in f32 in tcgen05 kind::f16, one f32 scale multiply-add per group "
+                   "(int8: per column); Linears below 4M weights keep the block-fixed-point kernels")
 
 
 def parse_workload(name):
@@ -395,7 +399,8 @@ def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local
         achieved = lin_bytes / (lin_ms / 1000.0) / 1e9
         traffic = None
         try:
-            with open(os.path.join(ROOT, "profiles", "gemv_traffic.json")) as f:
+            # DRAM bytes per algorithmic byte from one ncu capture per kernel family (narrow: up to 4 rows; 16-row tile: 5..16)
+            with open(os.path.join(ROOT, "profiles", "gemv_traffic.json" if B <= 4 else "gemv_wide_traffic.json")) as f:
                 tr = json.load(f).get(f"int{bits}")
                 if tr and B <= 16:
                     traffic = tr["dram_bytes_per_algorithmic_byte"] * lin_bytes / lin_launches
@@ -403,6 +408,8 @@ def run_workload(nn, dev, name, K, W, regions, rank=0, world=1, dist=None, local
             pass
         if B > 16:
             kname = "gemm_tc_kernel (tcgen05 kind::f16 dequant GEMM, every Linear of the model)"
+        elif B >= 5:
+            kname = f"gemv_wide_kernel<{bits}> + xsplit16_kernel (tcgen05 kind::f16, one 16-row tile, weights streamed once; Linears of 4M weights and more)"
         elif bits == 4:
             kname = f"gemv_tc_int4_kernel<rows<={min(B, 8)}> (tcgen05 kind::i8 fused dequant GEMV; the int8 head runs gemv_tc_int8_kernel)"
         else:
@@ -464,7 +471,7 @@ def main():
     W = max(args.warmup, 3)
     K = max(args.steps, 1)
     config = {"workload": args.workload, "model_shape": model, "layers": dims["L"], "weights": f"int{bits}" + (" group 32, int8 head" if bits == 4 else ""),
-              "batch": B, "context": ctx, "kv_dtype": "f32", "activations": ARITHMETIC,
+              "batch": B, "context": ctx, "kv_dtype": "f32", "activations": ARITHMETIC if B <= 4 else ARITHMETIC_WIDE,
               "parallelism": f"tp{world}" if world > 1 else "single GPU",
               "l2": "every step streams the whole quantized model (far larger than the 126 MB L2), so no flush is needed"}
 
