@@ -29,7 +29,9 @@ constexpr int kBStages = 3;       // ring of B stages in shared memory
 constexpr int kParts = 4;             // worker threads per column
 constexpr int kWorkers = kParts * kCols;  // sixteen warps: thread = (column, part); a part expands one k-step of one of a stage's two groups
                                           // (16 of the group's 32 rows of W) and reads a quarter of the rows of x out of tensor memory
-constexpr int kThreads = kWorkers + 64;
+constexpr int kIssuers = kStageGroups;  // issuing warps, one per group of a stage: a tcgen05.mma costs its issuing thread about 116 clocks (measured,
+                                        // kind::f16 up to N = 128) against the 64 the tensor core needs for 128 x 128 x 16, so one thread cannot keep it busy
+constexpr int kThreads = kWorkers + 32 + 32 * kIssuers;  // workers, the B producer's warp, the issuing warps
 constexpr uint32_t kBGroupBytes = 2 * 2 * kRows * 32;  // pieces x k-steps x rows x 32 B = 16 KB per group of 32 k
 
 // ---- activations -> two bf16 pieces in B-operand layout --------------------------------------------
@@ -112,8 +114,7 @@ constexpr size_t kSmemBytes = off_b + (size_t)kBStages * kStageGroups * kBGroupB
 
 template <int BITS>
 __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
-  constexpr int kAccBufs = BITS == 4 ? 2 * kStageGroups : 1;  // int4: one accumulator per group, two stages; int8: one in all
-  constexpr int kTmemCols = BITS == 4 ? 512 : 128;
+  constexpr int kTmemCols = BITS == 4 ? 512 : kIssuers * kRows;  // int8: one accumulator per issuing warp
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t b_full[kBStages];  // B stage landed
   __shared__ __align__(8) uint64_t b_empty[kBStages]; // MMAs that read a B slot completed
@@ -133,8 +134,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
   const uint32_t nst = (p.groups + kStageGroups - 1) / kStageGroups;
 
   if (tid == 0) {
-    for (int s = 0; s < kBStages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&a_ready[s], kWorkers / 32); mbar_init(&mma_done[s], 1); }
+    for (int s = 0; s < kBStages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], kIssuers); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&a_ready[s], kWorkers / 32); mbar_init(&mma_done[s], kIssuers); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_abort = 0;
   }
@@ -166,23 +167,25 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
 
   constexpr int kHalfRows = kRows / kParts;
   float acc[kHalfRows];  // worker threads: this column's sums for the thread's 32 rows
-  if (warp == kWorkers / 32) {
-    // ===== MMA issuer =====
+  if (warp == kWorkers / 32 || warp > kWorkers / 32 + 1) {
+    // ===== MMA issuers: warp wi takes group wi of every stage =====
+    const uint32_t wi = warp == kWorkers / 32 ? 0u : (uint32_t)warp - kWorkers / 32 - 1;
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_bf16(kRows);
       for (uint32_t i = 0; i < nst; ++i) {
         if (s_abort || !mbar_wait(&a_ready[i & 1], (i >> 1) & 1u) || !mbar_wait(&b_full[i % kBStages], (i / kBStages) & 1u)) { s_abort = 1; break; }
         tc_fence_after_sync();
         const uint32_t ng = min((uint32_t)kStageGroups, p.groups - i * kStageGroups);
-        for (uint32_t u = 0; u < ng; ++u) {
-          const uint32_t d = tmem_base + (BITS == 4 ? ((i & 1) * kStageGroups + u) * kRows : 0u);
+        if (const uint32_t u = wi; u < ng) {
+          // int8: an accumulator per issuing warp (MMAs of two threads are not ordered among themselves)
+          const uint32_t d = tmem_base + (BITS == 4 ? ((i & 1) * kStageGroups + u) * kRows : wi * kRows);
           const unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + u) * kAGroupBytes;
           const unsigned char* b = bring + ((size_t)(i % kBStages) * kStageGroups + u) * kBGroupBytes;
           for (uint32_t s = 0; s < 2; ++s)
             for (uint32_t pc = 0; pc < 2; ++pc) {
               const uint64_t ad = umma_desc_kmajor(smem_u32(a + s * 4096), 2048, 128);
               const uint64_t bd = umma_desc_kmajor(smem_u32(b + pc * 8192 + s * 4096), 2048, 128);
-              const uint32_t accumulate = BITS == 4 ? (s | pc) : ((i | u | s | pc) != 0u ? 1u : 0u);
+              const uint32_t accumulate = BITS == 4 ? (s | pc) : ((i | s | pc) != 0u ? 1u : 0u);
               umma_bf16(d, ad, bd, idesc, accumulate);
             }
         }
@@ -293,7 +296,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
     if (ok && nst > 0) {
       if (BITS == 4) ok = drain(nst - 1, sv_prev);
       else {
-        // int8: the single accumulator, scaled per column (cpu.rs:918-920)
+        // int8: the issuing warps' accumulators (warp u had groups if there are more than u of them), scaled per column (cpu.rs:918-920)
         const uint32_t s = nst - 1;
         if (!mbar_wait(&mma_done[s & 1], (s >> 1) & 1u)) ok = false;
         else {
@@ -301,11 +304,18 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
           const float cs = active ? p.scale[j] : 0.0f;
 #pragma unroll
           for (int q = 0; q < kHalfRows / 32; ++q) {
-            float d[32];
-            tmem_ld32(tmem_base + lane_base + part * kHalfRows + 32 * q, d);
-            tmem_ld_wait();
 #pragma unroll
-            for (int t = 0; t < 32; ++t) acc[32 * q + t] = d[t] * cs;
+            for (int u = 0; u < kIssuers; ++u) {
+              if ((uint32_t)u < p.groups) {
+                float d[32];
+                tmem_ld32(tmem_base + lane_base + u * kRows + part * kHalfRows + 32 * q, d);
+                tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < 32; ++t) acc[32 * q + t] += d[t];
+              }
+            }
+#pragma unroll
+            for (int t = 0; t < 32; ++t) acc[32 * q + t] *= cs;
           }
           tc_fence_before_sync();
         }
