@@ -26,6 +26,7 @@ struct ruai_ctx {
   // split-K scratch: partial sums [splits][m][n] and one arrival counter per column tile
   float* partial = nullptr;
   size_t partial_bytes = 0;
+  unsigned long long scratch_epoch = 0;  // counts reallocations of the scratch: captured graphs hold its address
   unsigned* counters = nullptr;
   size_t counters_n = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -214,6 +215,8 @@ int ruai_gemv_tc_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int
 bool ruai_gemv_tc8_eligible(const ruai_qweight* w, uint32_t m);
 int ruai_gemv_tc8_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                          const GemvEpilogue& epi, const GemvPrologue& pro);
+// Bytes of the context's scratch that a Linear over `w` with m rows may use for its split activations.
+size_t ruai_gemv_xs_bytes(const ruai_qweight* w, uint32_t m);
 bool ruai_gemv_wide_eligible(const ruai_ctx* ctx, const ruai_qweight* w, uint32_t m);
 int ruai_gemv_wide_launch(ruai_ctx* ctx, const ruai_qweight* w, const void* x, int x_dtype, uint32_t x_ld, uint32_t m, void* out,
                           const GemvEpilogue& epi, const GemvPrologue& pro);

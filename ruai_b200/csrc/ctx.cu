@@ -93,6 +93,7 @@ int ruai_ctx_reserve(ruai_ctx* c, size_t partial_bytes, size_t counters) {
     c->partial_bytes = 0;
     RUAI_CUDA(c, cudaMalloc(&c->partial, partial_bytes));
     c->partial_bytes = partial_bytes;
+    c->scratch_epoch++;
   }
   if (counters > c->counters_n) {
     RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
@@ -102,6 +103,7 @@ int ruai_ctx_reserve(ruai_ctx* c, size_t partial_bytes, size_t counters) {
     RUAI_CUDA(c, cudaMalloc(&c->counters, counters * sizeof(unsigned)));
     RUAI_CUDA(c, cudaMemset(c->counters, 0, counters * sizeof(unsigned)));
     c->counters_n = counters;
+    c->scratch_epoch++;
   }
   return RUAI_OK;
 }

@@ -417,6 +417,12 @@ int ruai_gemv_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x_dt
   return RUAI_OK;
 }
 
+size_t ruai_gemv_xs_bytes(const ruai_qweight* w, uint32_t m) {
+  const size_t groups = (w->k + 31) / 32;
+  // up to 16 rows: one 16-row tile, 2 KB per group, whole 64-k tiles; beyond: 16 KB per group and block of 128 rows
+  return m <= 16 ? ((groups + 1) & ~(size_t)1) * 2048 : (size_t)((m + 127) / 128) * groups * 16384;
+}
+
 uint32_t ruai_gemv_tiles(const ruai_ctx* c, const ruai_qweight* w) {
   const uint32_t t = c->use_bulk && ruai_gemv_bulk_eligible(w) ? kGemvBulkTileCols : kGemvTileCols;
   return (w->n + t - 1) / t;

@@ -123,6 +123,7 @@ struct ruai_model {
   // decode graph
   cudaGraphExec_t graph = nullptr;
   uint32_t graph_B = 0, graph_cap = 0, graph_launches = 0;
+  unsigned long long graph_epoch = 0;  // the context's scratch_epoch at capture: the graph holds the scratch's address
   bool len_dirty = true;  // the device copy of `len` may differ from the host's
   PStep ps;
   ruai_tp_state tp;
@@ -1071,14 +1072,19 @@ RUAI_API int ruai_model_cache_assume(ruai_model* m, uint32_t B, uint32_t len) {
 static int run_decode_graph(ruai_model* m, uint32_t B) {
   ruai_ctx* c = m->ctx;
   if (pstep_eligible(m, B)) return pstep_run(m, B);
-  if (!m->graph || m->graph_B != B || m->graph_cap != m->cap) {
+  if (!m->graph || m->graph_B != B || m->graph_cap != m->cap || m->graph_epoch != c->scratch_epoch) {
     drop_graph(m);
     // split-K partials of one GEMV never exceed (3 * SMs + column tiles) * 256 floats per row;
     // reserve before capturing (no allocation inside a capture)
     uint32_t max_n = m->head.w->n;
     for (Layer& L : m->layers) max_n = std::max(max_n, std::max(L.up.w->n, L.qkv.w->n));
     const size_t tiles = (max_n + 255) / 256;
-    RUAI_TRY(ruai_ctx_reserve(c, ((size_t)3 * c->sm_count + tiles + 1) * 256 * B * sizeof(float), tiles * ((B + 15) / 16) + 16));
+    size_t need = ((size_t)3 * c->sm_count + tiles + 1) * 256 * B * sizeof(float);
+    need = std::max(need, ruai_gemv_xs_bytes(m->head.w, B));  // the split activations of the tensor-core tiles live there too
+    for (Layer& L : m->layers)
+      for (const ruai_qweight* w : {L.qkv.w, L.o.w, L.up.w, L.down.w})
+        if (w) need = std::max(need, ruai_gemv_xs_bytes(w, B));
+    RUAI_TRY(ruai_ctx_reserve(c, need, tiles * ((B + 15) / 16) + 16));
     RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
     const unsigned long long before = c->launches;
     cudaGraph_t gr = nullptr;
@@ -1091,7 +1097,7 @@ static int run_decode_graph(ruai_model* m, uint32_t B) {
     e = cudaGraphInstantiate(&m->graph, gr, 0);
     cudaGraphDestroy(gr);
     if (e != cudaSuccess) { m->graph = nullptr; return model_fail(m, RUAI_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e)); }
-    m->graph_B = B; m->graph_cap = m->cap;
+    m->graph_B = B; m->graph_cap = m->cap; m->graph_epoch = c->scratch_epoch;
   }
   RUAI_CUDA(c, cudaGraphLaunch(m->graph, c->stream));
   m->len += 1;

@@ -136,6 +136,36 @@ def test_steps_of_five_to_sixteen_sequences(dev, kind, bits, B):
         close(lo, gm.forward_cached(nxt), f"{kind} int{bits} B={B} step {step}")
 
 
+def test_decode_graph_survives_a_larger_scratch(dev):
+    """The captured decode step holds the address of the context's scratch (split activations of the 16-row tile).  A
+    later prefill of many rows needs a larger scratch, which moves it: the next decode step has to be captured anew, not
+    replayed with the old address."""
+    cfgs = llama_cfg(V=1000, d=576, ffn=1568, L=2, H=9, KV=3, hd=64, max_pos=256)
+    om, gm = build(dev, cfgs, 6, 4, 32)
+    B = 8
+
+    def steps(T, n):
+        prompts = np.stack([oracle.synth_tokens(6, 0x20000000 + b, T, 1000) for b in range(B)])
+        om.cache_clear()
+        gm.cache_clear()
+        lo = om.forward_cached(prompts)
+        close(lo, gm.forward_cached(prompts), f"prefill of {B} x {T}")
+        nxt = np.array([oracle.argmax(r) for r in lo], np.int32)
+        for step in range(n):
+            lo = om.forward_cached(nxt[:, None])
+            want = np.array([oracle.argmax(r) for r in lo], np.int32)
+            ids_dev = nn.Tensor.from_numpy(dev, nxt)  # (kept alive across the call)
+            got = gm.decode_step(B, ids_dev.ptr)
+            srt = np.sort(lo, axis=1)
+            decisive = (srt[:, -1] - srt[:, -2]) > 1e-4
+            assert (got[decisive] == want[decisive]).all(), f"T={T} step {step}"
+            nxt = want
+        close(om.forward_cached(nxt[:, None]), gm.forward_cached(nxt[:, None]), f"T={T} step logits")
+
+    steps(2, 2)     # captures the graph of a step of 8 sequences
+    steps(128, 2)   # 1024 rows through the GEMM: the scratch grows; then steps of 8 sequences again
+
+
 @pytest.mark.parametrize("H,KV,hd,B", [(4, 2, 96, 1), (6, 6, 24, 3), (8, 1, 40, 2), (4, 2, 96, 40)])
 def test_attention_geometries(dev, H, KV, hd, B):
     """Head dimensions that are not powers of two, 1 / 2 / 8 query heads per KV head, and enough sequences to take the
