@@ -161,6 +161,27 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
   const uint32_t nst = (c_end - c_begin + kStageGroups - 1) / kStageGroups;
   const uint32_t nrounds = (nst + kRoundStages - 1) / kRoundStages;
 
+  // The expanding warps' first stages of packed weights are requested before anything else: they depend on nothing,
+  // not on the predecessor kernel and not on this CTA's own set-up (barriers, tensor memory, the zeroed operand rows).
+  const bool expander = warp > kCols / 32;
+  // (A in tensor memory: a warp reaches only the lanes 32 (warp % 4) .., so its threads take those columns)
+  const int te = kATmem ? (warp & 3) * 32 + lane : tid - kExpand0;
+  const uint32_t je = j0 + te;
+  const bool in_col = je < p.n;
+  uint4 wq[kAhead][kStageGroups];
+  auto load_stage = [&](uint32_t i, uint4 (&wv)[kStageGroups]) {
+#pragma unroll
+    for (int u = 0; u < kStageGroups; ++u) {
+      const uint32_t c = c_begin + i * kStageGroups + u;
+      // beyond the slice or the matrix: stored value 8 is weight 0
+      wv[u] = (in_col && c < c_end) ? ldg_stream_u4(&p.w[(size_t)c * p.n + je]) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+    }
+  };
+  if (expander) {
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) load_stage(a, wq[a]);
+  }
+
   if (tid == 0) {
     for (int s = 0; s < kBufs; ++s) { mbar_init(&a_ready[s], kCols / 32); mbar_init(&mma_done[s], 1); mbar_init(&acc_free[s], kCols / 32); }
     mbar_init(&b_ready[0], kCols / 32);
@@ -183,24 +204,9 @@ __global__ void __launch_bounds__(kThreads, small_of(MT, kAhead) ? 3 : 2) gemv_t
   for (int r = 0; r < MT; ++r) { acc[r] = 0.0f; resid_pre[r] = 0.0f; }
   const bool pre = p.epi.resid != nullptr && p.epi.act != ACT_SWIGLU && split == 0 && active;
 
-  if (warp > kCols / 32) {
+  if (expander) {
     // ===== expanding warps: packed weights -> A operand.  Nothing here depends on the predecessor kernel, so
     // these warps do not wait for it: the first kBufs stages are in place before the activations exist. =====
-    // (A in tensor memory: a warp reaches only the lanes 32 (warp % 4) .., so its threads take those columns)
-    const int te = kATmem ? (warp & 3) * 32 + lane : tid - kExpand0;
-    const uint32_t je = j0 + te;
-    const bool in_col = je < p.n;
-    uint4 wq[kAhead][kStageGroups];
-    auto load_stage = [&](uint32_t i, uint4 (&wv)[kStageGroups]) {
-#pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) {
-        const uint32_t c = c_begin + i * kStageGroups + u;
-        // beyond the slice or the matrix: stored value 8 is weight 0
-        wv[u] = (in_col && c < c_end) ? ldg_stream_u4(&p.w[(size_t)c * p.n + je]) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-      }
-    };
-#pragma unroll
-    for (int a = 0; a < kAhead; ++a) load_stage(a, wq[a]);
     bool ok = true;
     // the register queue is addressed statically (stage i sits in wq[i % kAhead]): moving it along would make every
     // stage wait for the newest loads
