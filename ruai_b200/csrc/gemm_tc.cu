@@ -25,7 +25,7 @@ using namespace pipe;
 constexpr int kCols = 128;        // columns of W per CTA = MMA M = TMEM lanes
 constexpr int kRows = 128;        // rows of x per CTA = MMA N
 constexpr int kStageGroups = 2;   // groups of 32 k per pipeline stage
-constexpr int kBStages = 3;       // ring of B stages in shared memory
+constexpr int kBStages = 3;       // ring of B stages in shared memory (five change nothing: measured)
 constexpr int kParts = 4;             // worker threads per column
 constexpr int kWorkers = kParts * kCols;  // sixteen warps: thread = (column, part); a part expands one k-step of one of a stage's two groups
                                           // (16 of the group's 32 rows of W) and reads a quarter of the rows of x out of tensor memory
@@ -146,22 +146,28 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem;
 
-  // packed weights of this thread's column, one stage ahead (they do not depend on the predecessor kernel)
+  // packed weights of this thread's column, kAhead stages ahead of their use in a register queue addressed statically
+  // (they do not depend on the predecessor kernel).  One stage ahead was not enough: a worker is through with a stage long
+  // before the next stage's weights have made their way from the L2 or from HBM, and waited for them every time.
   constexpr int kChunksPerGroup = BITS == 4 ? 1 : 2;
-  uint4 wq;                    // int4: the chunk of this thread's group; int8: the chunk that is its k-step of the group
-  float sq[kStageGroups];      // the column's scales of both groups (the read-out needs both)
-  auto load_stage = [&](uint32_t i) {
+  constexpr int kAhead = BITS == 4 ? 2 : 3;
+  uint4 wq[kAhead];                    // int4: the chunk of this thread's group; int8: the chunk that is its k-step of the group
+  float sq[kAhead][kStageGroups];      // the column's scales of both groups (the read-out needs both)
+  auto load_stage = [&](uint32_t i, uint4& wv, float (&sv)[kStageGroups]) {
     const uint32_t g = i * kStageGroups + pg;
     const uint32_t c = BITS == 4 ? g : g * kChunksPerGroup + pstep;
     const bool in = active && c < p.chunks;
-    wq = in ? __ldg(&p.w[(size_t)c * p.n + j]) : (BITS == 4 ? make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u) : make_uint4(0, 0, 0, 0));
+    wv = in ? __ldg(&p.w[(size_t)c * p.n + j]) : (BITS == 4 ? make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u) : make_uint4(0, 0, 0, 0));
 #pragma unroll
     for (int u = 0; u < kStageGroups; ++u) {
       const uint32_t gu = i * kStageGroups + u;
-      sq[u] = (BITS == 4 && active && gu < p.groups) ? __ldg(&p.scale[(size_t)gu * p.n + j]) : 0.0f;
+      sv[u] = (BITS == 4 && active && gu < p.groups) ? __ldg(&p.scale[(size_t)gu * p.n + j]) : 0.0f;
     }
   };
-  if (tid < kWorkers) load_stage(0);
+  if (tid < kWorkers) {
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) load_stage(a, wq[a], sq[a]);
+  }
   grid_dependency_wait();
   grid_launch_dependents();
 
@@ -244,16 +250,20 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       return true;
     };
     bool ok = true;
-    for (uint32_t i = 0; i < nst && ok; ++i) {
+    for (uint32_t i0 = 0; i0 < nst && ok; i0 += kAhead) {
+#pragma unroll
+     for (int qa = 0; qa < kAhead; ++qa) {
+      const uint32_t i = i0 + qa;
+      if (i >= nst) break;
       if (s_abort) { ok = false; break; }
       // the A buffer of stage i was last read by the MMAs of stage i - 2
       if (i >= 2 && BITS == 8) { if (!mbar_wait(&mma_done[i & 1], ((i - 2) >> 1) & 1u)) { ok = false; break; } }
       float sv_cur[kStageGroups];
 #pragma unroll
-      for (int u = 0; u < kStageGroups; ++u) sv_cur[u] = sq[u];
+      for (int u = 0; u < kStageGroups; ++u) sv_cur[u] = sq[qa][u];
       {
         unsigned char* a = abuf + ((size_t)(i & 1) * kStageGroups + pg) * kAGroupBytes + (size_t)col * 16 + pstep * 4096;
-        const uint32_t wd[4] = {wq.x, wq.y, wq.z, wq.w};
+        const uint32_t wd[4] = {wq[qa].x, wq[qa].y, wq[qa].z, wq[qa].w};
         uint32_t o[8];
         if (BITS == 4) {
           // 16 nibbles (value + 8) -> 16 bf16: (128 + u) has the bit pattern 0x4300 | u; subtract 136 in bf16 pairs.
@@ -284,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
         *reinterpret_cast<uint4*>(a) = make_uint4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<uint4*>(a + 2048) = make_uint4(o[4], o[5], o[6], o[7]);
       }
-      load_stage(i + 1);
+      load_stage(i + kAhead, wq[qa], sq[qa]);  // into the registers just consumed
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -292,6 +302,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tc_kernel(const Params p) {
       if (BITS == 4 && i > 0) ok = drain(i - 1, sv_prev);
 #pragma unroll
       for (int u = 0; u < kStageGroups; ++u) sv_prev[u] = sv_cur[u];
+      if (!ok) break;
+     }
     }
     if (ok && nst > 0) {
       if (BITS == 4) ok = drain(nst - 1, sv_prev);
@@ -393,3 +405,4 @@ int ruai_gemm_tc_launch(ruai_ctx* c, const ruai_qweight* w, const void* x, int x
   if (e != cudaSuccess) return ruai_fail(c, RUAI_ERR_CUDA, "prefill GEMM launch failed: %s", cudaGetErrorString(e));
   return RUAI_OK;
 }
+

@@ -256,7 +256,7 @@ def test_matmul_head_width_int8(dev, m):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
-@pytest.mark.parametrize("m", [1, 2, 5])
+@pytest.mark.parametrize("m", [1, 2, 5, 16, 40])
 def test_matmul_non_finite_activations_propagate(dev, bits, m):
     """A NaN or an infinity in a row of x makes that row of the product non-finite, as f32 arithmetic on the CPU does
     (cpu.rs:1002-1029, 1035-1067); the other rows are unaffected."""
@@ -275,8 +275,8 @@ def test_matmul_non_finite_activations_propagate(dev, bits, m):
         xb[0, 1234] = bad
         _, y = run_matmul(dev, xb, qw, "f32")
         assert not np.isfinite(y[0]).any(), bad
-        if m > 1:
-            same(want[1:], y[1:], 1e-4)
+        if m > 1:  # (five rows and more: activations as two bf16 pieces, see test_matmul_five_to_sixteen_rows)
+            same(want[1:], y[1:], 1e-4 if m < 5 else 3e-4)
 
 
 @pytest.mark.parametrize("bits", [8, 4])
