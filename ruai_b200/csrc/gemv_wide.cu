@@ -494,7 +494,10 @@ cudaError_t launch_one(ruai_ctx* c, const Params& p, dim3 grid) {
 // that splits the activations has paid for itself (135M-parameter shapes, 16 sequences: 1.44 ms per step without, 1.94 with).
 bool ruai_gemv_wide_eligible(const ruai_ctx* c, const ruai_qweight* w, uint32_t m) {
   (void)c;
-  return w->layout == QL_CHUNK16 && ((w->bits == 4 && w->group == 32) || w->bits == 8) && m >= 5 && m <= (uint32_t)gemv_wide::kRows &&
+  // int8 with a long k also at four rows: the narrow int8 kernel converts its whole slice of the activations before its first
+  // MMA, which at 4 x 14336 costs more than this kernel in all (down_proj of the 8B shape: 43 us there, 28 here)
+  const uint32_t from = (w->bits == 8 && w->k >= 8192) ? 4u : 5u;
+  return w->layout == QL_CHUNK16 && ((w->bits == 4 && w->group == 32) || w->bits == 8) && m >= from && m <= (uint32_t)gemv_wide::kRows &&
          (uint64_t)w->k * w->n >= (1ull << 22);
 }
 

@@ -210,7 +210,7 @@ def test_matmul_grid_8b_widths(dev, m, k, n, bits):
 # 5..16 rows: the 16-row tile (weights streamed once).  Shapes chosen so that k splits over 1, 2, 4 and 8 CTAs, the last
 # stage and the last column tile are ragged, and k is not a multiple of the group.
 ROWS16 = [(9, 64, 48), (12, 96, 130), (16, 4096, 512), (13, 4096, 6144), (16, 14336, 4096), (10, 4096, 28672), (16, 1000, 130), (11, 1536, 1536),
-          (5, 4096, 4096), (8, 14336, 4096), (6, 96, 70)]
+          (5, 4096, 4096), (8, 14336, 4096), (6, 96, 70), (4, 14336, 4096)]
 
 
 @pytest.mark.parametrize("bits", [8, 4])
