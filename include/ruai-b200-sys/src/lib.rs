@@ -84,6 +84,7 @@ extern "C" {
     pub fn ruai_ctx_set_wait_limit(ctx: *mut ruai_ctx, polls: c_uint) -> c_int;
     pub fn ruai_ctx_inject_barrier_skew(ctx: *mut ruai_ctx, grids: c_uint) -> c_int;
     pub fn ruai_ctx_inject_copy_shortfall(ctx: *mut ruai_ctx, bytes: c_uint) -> c_int;
+    pub fn ruai_ctx_force_splits(ctx: *mut ruai_ctx, splits: c_uint) -> c_int;
     pub fn ruai_malloc(ctx: *mut ruai_ctx, bytes: usize, out_dev: *mut *mut c_void) -> c_int;
     pub fn ruai_free(ctx: *mut ruai_ctx, ptr_dev: *mut c_void) -> c_int;
     pub fn ruai_memcpy_h2d(ctx: *mut ruai_ctx, dst_dev: *mut c_void, src_host: *const c_void, bytes: usize) -> c_int;

@@ -76,6 +76,11 @@ int ruai_ctx_inject_barrier_skew(ruai_ctx* ctx, unsigned grids);
 /* The same for a shared-memory barrier: the first bulk copy of the next persistent launch is announced `bytes` larger
  * than it is, so the barrier it signals never completes and the consumers' bounded wait for that stage runs out. */
 int ruai_ctx_inject_copy_shortfall(ruai_ctx* ctx, unsigned bytes);
+/* Tuning knob: fixes the split-k count (1..8 CTAs of a cluster share the k of a column tile) of the tensor-core GEMVs
+ * on this context; 0 gives the choice back to the library's cost model.  Results do not depend on it beyond the order
+ * of a few f32 additions.  `python -m ruai_b200.sweep_splits` uses it to compare the cost model with every fixed split
+ * on a list of shapes.  No counterpart in the reference. */
+int ruai_ctx_force_splits(ruai_ctx* ctx, unsigned splits);
 
 /* Device memory for callers without their own allocator (cuda.rs:288-300). */
 int ruai_malloc(ruai_ctx* ctx, size_t bytes, void** out_dev);

@@ -71,6 +71,7 @@ _PROTOS = {
     "ruai_ctx_set_wait_limit": (C.c_int, [vp, C.c_uint]),
     "ruai_ctx_inject_barrier_skew": (C.c_int, [vp, C.c_uint]),
     "ruai_ctx_inject_copy_shortfall": (C.c_int, [vp, C.c_uint]),
+    "ruai_ctx_force_splits": (C.c_int, [vp, C.c_uint]),
     "ruai_dequant_int4": (C.c_int, [vp, vp, vp]),
     "ruai_dequant_int4_ref": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
     "ruai_llama_create": (C.c_int, [vp, C.POINTER(LlamaConfig), C.POINTER(TP), C.POINTER(vp)]),

@@ -174,9 +174,17 @@ RUAI_API int ruai_timer_stop_ms(ruai_ctx* c, float* ms) {
   return RUAI_OK;
 }
 
+// Tuning knob: the split-k count of the tensor-core GEMVs (0 = the chooser decides).
+RUAI_API int ruai_ctx_force_splits(ruai_ctx* c, unsigned splits) {
+  if (!c) return ruai_fail(c, RUAI_ERR_ARG, "NULL argument");
+  if (splits > 8) return ruai_fail(c, RUAI_ERR_ARG, "splits %u: 0 (automatic) or 1..8", splits);
+  c->force_splits = splits;
+  return RUAI_OK;
+}
+
 // Profiling hooks, present only in builds made with RUAI_B200_TRACE=1 (never in the library as shipped).
 #ifdef RUAI_B200_TRACE
-RUAI_API int ruai_debug_force_splits(ruai_ctx* c, unsigned splits) {
+RUAI_API int ruai_debug_force_splits(ruai_ctx* c, unsigned splits) {  // also the profiling bits above the count
   c->force_splits = splits;
   return RUAI_OK;
 }

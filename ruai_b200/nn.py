@@ -55,6 +55,10 @@ class Device:
     def inject_copy_shortfall(self, nbytes):
         self.check(self.L.ruai_ctx_inject_copy_shortfall(self.ctx, nbytes))
 
+    def force_splits(self, splits):
+        """Fix the split-k count of the tensor-core GEMVs (1..8), or 0 to let the library choose."""
+        self.check(self.L.ruai_ctx_force_splits(self.ctx, splits))
+
     def timer_start(self):
         self.check(self.L.ruai_timer_start(self.ctx))
 

@@ -242,6 +242,31 @@ def test_matmul_five_to_sixteen_rows(dev, m, k, n, bits):
         same(round_to(ref + bias, dtype), yh, TOL[dtype])
 
 
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m", [1, 3, 9])
+def test_fixed_split_counts_give_the_same_product(dev, bits, m):
+    """ruai_ctx_force_splits: the product does not depend on how many CTAs share k beyond the order of a few f32 additions
+    (more splits than stages of k leave some CTAs of the cluster without work)."""
+    k, n = 2048, 2304
+    x = oracle.synth_normal(19, m, (m, k), 1.0)
+    w = oracle.synth_normal(19, 2, (k, n))
+    if bits == 8:
+        q, s = oracle.quantize_int8(w)
+        qw, want = nn.QWeight.int8(dev, q, s), oracle.matmul_int8(x, q, s)
+    else:
+        q, s = oracle.quantize_int4(w, 32)
+        qw, want = nn.QWeight.int4(dev, q, s, 32), oracle.matmul_int4(x, q, s)
+    try:
+        for splits in (0, 1, 2, 4, 8):
+            dev.force_splits(splits)
+            _, y = run_matmul(dev, x, qw, "f32")
+            same(want, y, 1e-4 if m < 5 else 3e-4)
+        with pytest.raises(Exception):
+            dev.force_splits(9)
+    finally:
+        dev.force_splits(0)
+
+
 @pytest.mark.slow
 @pytest.mark.parametrize("m", [17, 64])
 def test_matmul_head_width_int8(dev, m):
