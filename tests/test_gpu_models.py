@@ -118,22 +118,36 @@ def test_causal_and_batched(dev):
 
 
 @pytest.mark.parametrize("B", [5, 8, 9, 13, 16])
-@pytest.mark.parametrize("kind,bits", [("llama", 4), ("llama", 8), ("gpt2", 8)])
+@pytest.mark.parametrize("kind,bits", [("llama", 4), ("llama", 8), ("gpt2", 8), ("llama_wide", 4), ("llama_wide", 8)])
 def test_steps_of_five_to_sixteen_sequences(dev, kind, bits, B):
     """Decode steps of 5..16 sequences (one 16-row tile on the tensor cores, weights read once): logits of every row
     against the checker, a layer-reduced model of mid width so that the Linears split k and have ragged column tiles."""
-    if kind == "llama":
+    if kind == "llama_wide":  # every Linear has 4M weights or more: all of them on the 16-row kernel, with its fused epilogues
+        if B in (8, 13):
+            pytest.skip("the wide configuration runs at 5, 9 and 16 sequences")
+        cfgs = llama_cfg(V=4000, d=2048, ffn=5632, L=2, H=32, KV=4, hd=64, max_pos=64)
+    elif kind == "llama":
         cfgs = llama_cfg(V=1000, d=576, ffn=1568, L=2, H=9, KV=3, hd=64, max_pos=64)
     else:
         cfgs = gpt2_cfg(V=1000, n_pos=64, d=192, L=2, H=6)
     om, gm = build(dev, cfgs, 5, bits, 32)
-    prompts = np.stack([oracle.synth_tokens(5, 0x20000000 + b, 2, 1000) for b in range(B)])
+    V = 4000 if kind == "llama_wide" else 1000
+    prompts = np.stack([oracle.synth_tokens(5, 0x20000000 + b, 2, V) for b in range(B)])
     lo = om.forward_cached(prompts)
     close(lo, gm.forward_cached(prompts), "prefill")
     for step in range(3):
         nxt = np.array([oracle.argmax(r) for r in lo], np.int32)[:, None]
         lo = om.forward_cached(nxt)
         close(lo, gm.forward_cached(nxt), f"{kind} int{bits} B={B} step {step}")
+    # the greedy pick fused into the head's launch (one 16-row tile): ids of one more step
+    nxt = np.array([oracle.argmax(r) for r in lo], np.int32)
+    lo = om.forward_cached(nxt[:, None])
+    ids_dev = nn.Tensor.from_numpy(dev, nxt)
+    got = gm.decode_step(B, ids_dev.ptr)
+    srt = np.sort(lo, axis=1)
+    decisive = (srt[:, -1] - srt[:, -2]) > 1e-4
+    want = np.array([oracle.argmax(r) for r in lo], np.int32)
+    assert (got[decisive] == want[decisive]).all(), f"{kind} int{bits} B={B}: fused pick"
 
 
 def test_decode_graph_survives_a_larger_scratch(dev):

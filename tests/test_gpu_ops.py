@@ -210,7 +210,10 @@ def test_matmul_grid_8b_widths(dev, m, k, n, bits):
 # 5..16 rows: the 16-row tile (weights streamed once).  Shapes chosen so that k splits over 1, 2, 4 and 8 CTAs, the last
 # stage and the last column tile are ragged, and k is not a multiple of the group.
 ROWS16 = [(9, 64, 48), (12, 96, 130), (16, 4096, 512), (13, 4096, 6144), (16, 14336, 4096), (10, 4096, 28672), (16, 1000, 130), (11, 1536, 1536),
-          (5, 4096, 4096), (8, 14336, 4096), (6, 96, 70), (4, 14336, 4096)]
+          (5, 4096, 4096), (8, 14336, 4096), (6, 96, 70), (4, 14336, 4096),
+          # 4M weights and more (what the 16-row kernel takes) with ragged edges: a last column tile of 76 / 4 / 2 columns, an
+          # odd number of groups, a last stage of one group, k that is no multiple of 32 (int8), 8 splits of a long k
+          (16, 4128, 1100), (9, 4000, 1100), (12, 8192, 516), (7, 2080, 2052), (16, 4096, 1026), (13, 1000, 4400)]
 
 
 @pytest.mark.parametrize("bits", [8, 4])
