@@ -42,7 +42,7 @@ MODELS = {
 }
 DEFAULT_CTX = {"llama3-8b": 1024, "tinyllama-1.1b": 512, "smollm2-135m": 64, "gpt2-small": 16}
 # measured alongside the default workload and carried in `other_workloads` of its line
-OTHER_WORKLOADS = ["llama3-8b-int8-b1", "llama3-8b-int4-b16", "llama3-8b-int4-b128", "llama3-8b-int4-prefill1024",
+OTHER_WORKLOADS = ["llama3-8b-int8-b1", "llama3-8b-int4-b16", "llama3-8b-int8-b16", "llama3-8b-int4-b128", "llama3-8b-int4-prefill1024",
                    "tinyllama-1.1b-int4-b1", "tinyllama-1.1b-int4-b64", "tinyllama-1.1b-int4-prefill512",
                    "smollm2-135m-int8-b1", "smollm2-135m-int4-b16", "gpt2-small-int8-b1"]
 ARITHMETIC = ("f32 in and out; inside the GEMV the activations are block fixed point (int4 weights: 21 bits per group of 32; "
