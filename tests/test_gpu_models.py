@@ -117,14 +117,17 @@ def test_causal_and_batched(dev):
     assert np.abs(both[0] - la[0]).max() < 1e-5 and np.abs(both[1] - lb[0]).max() < 1e-5
 
 
-@pytest.mark.parametrize("B", [5, 8, 9, 13, 16])
-@pytest.mark.parametrize("kind,bits", [("llama", 4), ("llama", 8), ("gpt2", 8), ("llama_wide", 4), ("llama_wide", 8)])
+STEP_CASES = [(kind, bits, B) for kind, bits in (("llama", 4), ("llama", 8), ("gpt2", 8)) for B in (5, 8, 9, 13, 16)] + \
+             [("llama_wide", bits, B) for bits in (4, 8) for B in (5, 9, 16)]
+
+
+@pytest.mark.parametrize("kind,bits,B", STEP_CASES)
 def test_steps_of_five_to_sixteen_sequences(dev, kind, bits, B):
     """Decode steps of 5..16 sequences (one 16-row tile on the tensor cores, weights read once): logits of every row
-    against the checker, a layer-reduced model of mid width so that the Linears split k and have ragged column tiles."""
-    if kind == "llama_wide":  # every Linear has 4M weights or more: all of them on the 16-row kernel, with its fused epilogues
-        if B in (8, 13):
-            pytest.skip("the wide configuration runs at 5, 9 and 16 sequences")
+    against the checker.  Layer-reduced models: of mid width (small Linears stay on the narrow kernels, two row tiles from
+    nine rows on), and `llama_wide`, where every Linear has 4M weights or more and runs on the 16-row kernel with its fused
+    epilogues and the fused greedy pick."""
+    if kind == "llama_wide":
         cfgs = llama_cfg(V=4000, d=2048, ffn=5632, L=2, H=32, KV=4, hd=64, max_pos=64)
     elif kind == "llama":
         cfgs = llama_cfg(V=1000, d=576, ffn=1568, L=2, H=9, KV=3, hd=64, max_pos=64)
