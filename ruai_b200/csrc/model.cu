@@ -710,6 +710,11 @@ int pstep_run(ruai_model* m, uint32_t B) {
     RUAI_TRY(S.ss.alloc(c, 3 * (size_t)MR * (d / 32) * sizeof(float)));
     RUAI_TRY(S.arg_slots.alloc(c, (size_t)grid * MR * sizeof(int2)));
     RUAI_TRY(S.layers.alloc(c, (size_t)m->L * sizeof(ps::LayerPtrs)));
+    // nothing below is read before the kernel writes it; zeroed all the same, so that no run depends on what an earlier
+    // owner of the memory left there
+    RUAI_CUDA(c, cudaMemsetAsync(S.x.p, 0, S.x.bytes, c->stream));
+    RUAI_CUDA(c, cudaMemsetAsync(S.ss.p, 0, S.ss.bytes, c->stream));
+    RUAI_CUDA(c, cudaMemsetAsync(S.arg_slots.p, 0, S.arg_slots.bytes, c->stream));
     RUAI_TRY(pstep_reset(m));
   }
   // key splits: one (sequence, KV head, split) item per CTA where the cache is long enough to share out
@@ -718,6 +723,7 @@ int pstep_run(ruai_model* m, uint32_t B) {
   if (att_floats * sizeof(float) > S.att_part.bytes) {
     RUAI_CUDA(c, cudaStreamSynchronize(c->stream));
     RUAI_TRY(S.att_part.alloc(c, att_floats * sizeof(float)));
+    RUAI_CUDA(c, cudaMemsetAsync(S.att_part.p, 0, S.att_part.bytes, c->stream));
   }
   if (S.table_cap != m->cap || S.table_B != B) {  // the cache buffers moved (growth) or were made anew
     std::vector<ps::LayerPtrs> t(m->L);
